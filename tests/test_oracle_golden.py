@@ -1,0 +1,151 @@
+"""The CPU oracle against fixtures produced by the reference implementation and
+against the reference's known-answer constants."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import tq_oracle as orc
+
+
+# known-answer constants (negative halves; the codebooks are symmetric)
+KNOWN_CODEBOOKS = {
+    (128, 1): [-0.070524],
+    (128, 2): [-0.133503, -0.040020],
+    (128, 3): [-0.190207, -0.118786, -0.066822, -0.021663],
+    (128, 4): [-0.241572, -0.182926, -0.143066, -0.111083, -0.083332, -0.058081, -0.034319, -0.011355],
+    (64, 1): [-0.099736],
+    (64, 2): [-0.188802, -0.056598],
+    (64, 3): [-0.268993, -0.167989, -0.094501, -0.030637],
+    (64, 4): [-0.341635, -0.258696, -0.202326, -0.157095, -0.117850, -0.082139, -0.048534, -0.016059],
+}
+
+
+@pytest.mark.parametrize("d,bits", sorted(KNOWN_CODEBOOKS))
+def test_codebook_known_answers(d, bits, golden_constants):
+    c = orc.solve_codebook(d, bits)
+    half = len(c) // 2
+    assert np.allclose(c[:half].numpy(), KNOWN_CODEBOOKS[(d, bits)], atol=5e-7)
+    assert torch.equal(c, -c.flip(0)) or abs(float(c.sum())) < 1e-6
+    # the standalone solver (lloyd_max.py:32-86) writes the density with 1/d instead of
+    # sigma**2 and can land one ulp away from the compressors' inline copy
+    assert np.allclose(c.numpy(), golden_constants[f"lm_centroids_d{d}_b{bits}"], rtol=0, atol=6e-8)
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_matrices_match_reference(d, golden_constants):
+    Pi = orc.rotation_matrix(d, 42)
+    S = orc.qjl_matrix(d, 42)
+    assert np.array_equal(Pi.numpy(), golden_constants[f"Pi_seed42_d{d}"])
+    assert np.array_equal(S.numpy(), golden_constants[f"S_seed42_d{d}"])
+    assert np.array_equal(orc.rotation_matrix(d, 10042).numpy(), golden_constants[f"Pi_seed10042_d{d}"])
+    assert torch.allclose(Pi @ Pi.T, torch.eye(d), atol=1e-5)
+    if d == 128:
+        assert np.allclose(Pi[0, :4].numpy(), [0.174885, 0.120727, 0.085467, -0.145567], atol=1e-6)
+        assert np.allclose(S[0, :4].numpy(), [1.190396, -0.725117, 0.403278, 0.173541], atol=1e-6)
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("bits", [2, 3, 4])
+def test_compressor_constants(d, bits, golden_constants):
+    kp = orc.make_key_params(d, bits, 42)
+    vp = orc.make_value_params(d, bits, 10042)
+    assert np.array_equal(kp.centroids.numpy(), golden_constants[f"key_centroids_d{d}_bits{bits}"])
+    assert np.array_equal(kp.boundaries.numpy(), golden_constants[f"key_boundaries_d{d}_bits{bits}"])
+    assert np.array_equal(vp.centroids.numpy(), golden_constants[f"val_centroids_d{d}_bits{bits}"])
+    assert np.array_equal(vp.boundaries.numpy(), golden_constants[f"val_boundaries_d{d}_bits{bits}"])
+    assert orc.layer_seeds(42, 3) == (45, 10045)
+
+
+def test_pack_known_byte():
+    # 4-bit fields (0xA, 0x5) -> byte 0x5A
+    assert orc.pack_bits(np.array([[0xA, 0x5]]), 4).tolist() == [[0x5A]]
+    assert orc.packed_cols(128, 3) == 48 and orc.packed_cols(64, 1) == 8
+
+
+@pytest.mark.parametrize("b", range(1, 9))
+def test_pack_unpack_golden(b, golden_wire):
+    idx = golden_wire[f"idx_b{b}"].astype(np.int32)
+    packed = orc.pack_bits(idx, b)
+    assert np.array_equal(packed, golden_wire[f"packed_b{b}"])
+    assert np.array_equal(orc.unpack_bits(packed, b, idx.shape[1]), idx)
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("b_eff", [1, 2, 3, 4])
+def test_quantize_golden(d, b_eff, golden_wire, golden_constants):
+    rot = torch.from_numpy(golden_wire[f"rot_d{d}_b{b_eff}"])
+    bounds = torch.from_numpy(golden_constants[f"lm_boundaries_d{d}_b{b_eff}"])
+    cents = torch.from_numpy(golden_constants[f"lm_centroids_d{d}_b{b_eff}"])
+    packed = orc.quantize_packed(rot, bounds, b_eff)
+    assert np.array_equal(packed, golden_wire[f"qpacked_d{d}_b{b_eff}"])
+    # first-minimum argmin and boundary counting agree everywhere except where y sits
+    # exactly on a boundary (row 1 of the fixture), the documented tie case: there
+    # |y-c_j| and |y-c_j+1| round independently and either neighbour may win
+    a, s = orc.quantize_indices(rot, cents), orc.quantize_by_boundaries(rot, bounds)
+    keep = torch.ones(rot.shape[0], dtype=torch.bool)
+    keep[0] = keep[1] = False   # row 0 is all zeros: on the middle boundary up to fp64->fp32 rounding
+    assert torch.equal(a[keep], s[keep])
+    assert int((a[:2] - s[:2]).abs().max()) <= 1
+    # with the compressors' own fp32 midpoints a zero vector is an exact tie and both
+    # rules send it to the lower neighbour
+    c32 = orc.solve_codebook(d, b_eff)
+    b32 = (c32[:-1] + c32[1:]) / 2
+    z = torch.zeros(1, d)
+    assert torch.equal(orc.quantize_indices(z, c32), orc.quantize_by_boundaries(z, b32))
+    deq = orc.dequantize_packed(packed, cents, b_eff, d)
+    assert np.array_equal(deq.half().numpy(), golden_wire[f"deq_d{d}_b{b_eff}"])
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("bits", [2, 3, 4])
+def test_compress_and_scores_golden(d, bits, golden_comp):
+    tag = f"d{d}_bits{bits}"
+    k = torch.from_numpy(golden_comp[f"k_d{d}"])
+    v = torch.from_numpy(golden_comp[f"v_d{d}"])
+    q = torch.from_numpy(golden_comp[f"q_d{d}"])
+    kp = orc.make_key_params(d, bits, 42)
+    vp = orc.make_value_params(d, bits, 10042)
+    ck = orc.key_compress(k, kp)
+    assert np.array_equal(ck["k_mse"].numpy(), golden_comp[f"k_mse_{tag}"])
+    assert np.array_equal(ck["qjl_signs"].numpy(), golden_comp[f"qjl_signs_{tag}"])
+    assert np.array_equal(ck["residual_norm"].numpy(), golden_comp[f"residual_norm_{tag}"])
+    assert np.array_equal(ck["packed_key_indices"], golden_comp[f"packed_idx_{tag}"])
+    assert np.array_equal(ck["packed_qjl_signs"], golden_comp[f"packed_sgn_{tag}"])
+    sc = orc.scores_literal(q, ck, kp)
+    assert np.allclose(sc.numpy(), golden_comp[f"scores_{tag}"], rtol=0, atol=1e-5)
+    cv = orc.value_compress(v, vp)
+    assert np.array_equal(cv["indices"].numpy(), golden_comp[f"v_indices_{tag}"])
+    assert np.array_equal(cv["vec_norms"].numpy(), golden_comp[f"v_norms_{tag}"])
+    assert np.allclose(orc.value_decompress(cv, vp).numpy(), golden_comp[f"v_recon_{tag}"], atol=1e-6)
+    # fp32 evaluation from the packed bytes vs the reference's fp16-table packed path
+    sp = orc.scores_from_packed(q, ck["packed_key_indices"], ck["packed_qjl_signs"],
+                                ck["vec_norms"], ck["residual_norm"], kp, ck["shape"])
+    ref_p = torch.from_numpy(golden_comp[f"packed_scores_{tag}"])
+    rel = (sp - ref_p).norm() / ref_p.norm()
+    assert rel < 2e-3, rel                      # the reference rounds q_rot/S_eff/LUT to fp16
+    rel_lit = (sp - sc).norm() / sc.norm()
+    assert rel_lit < 1e-3, rel_lit              # literal path rounds k_mse to fp16
+    vals = orc.values_from_packed(cv["packed_indices"], cv["vec_norms"], vp, cv["shape"])
+    assert torch.allclose(vals, orc.value_decompress(cv, vp), atol=1e-6)
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4])
+def test_family_forward_golden(bits, golden_family):
+    """attention_core reproduces the reference GPT-2 adapter's forward."""
+    g = golden_family
+    hidden = torch.from_numpy(g["hidden"])
+    qkv = hidden @ torch.from_numpy(g["c_attn_w"]) + torch.from_numpy(g["c_attn_b"])
+    B, T, E = hidden.shape
+    q, k, v = (t.view(B, T, 2, 64).transpose(1, 2) for t in qkv.split(E, dim=2))
+    kp = orc.make_key_params(64, bits, 42)
+    vp = orc.make_value_params(64, bits, 10042)
+    out, _ = orc.attention_core(q, k, v, kp, vp, mask=torch.from_numpy(g["mask"]))
+    out = out.transpose(1, 2).reshape(B, T, E) @ torch.from_numpy(g["c_proj_w"]) + torch.from_numpy(g["c_proj_b"])
+    assert np.allclose(out.numpy(), g[f"out_bits{bits}"], atol=2e-5)
+    # the chunked evaluation is the same arithmetic
+    out_c = orc.attention_core_chunked(q, k, v, kp, vp, causal=True, q_chunk=7)
+    out_l, _ = orc.attention_core(q, k, v, kp, vp, mask=orc.causal_mask(T, T))
+    assert torch.allclose(out_c, out_l, atol=1e-5)
