@@ -1,0 +1,172 @@
+/*
+ * tq_b200.h -- C ABI of the B200 (sm_100a) TurboQuant KV-compression and
+ * compressed-attention library (libtq_b200.so).
+ *
+ * Everything here takes plain pointers and sizes.  All data pointers are DEVICE
+ * pointers on the current CUDA device unless a parameter says "host".  `stream`
+ * is a cudaStream_t passed as void* (NULL = the legacy default stream).  Every
+ * entry point validates its arguments on the host and returns a tq_status; on
+ * anything but TQ_OK no kernel was launched and tq_last_error() describes the
+ * problem.  No entry point allocates or frees device memory; scratch space is
+ * supplied by the caller (see tq_attention_workspace_bytes).
+ *
+ * "Reference" citations are file:line in SrzStephen/transformers-turboquant, the
+ * project whose interfaces these entry points replace.
+ *
+ * Wire format (shared by all entry points; reference
+ * src/turboquant_pytorch/kernels/bit_ops.py:5-7 and compressors.py:132-138,
+ * :281-285).  Vectors are numbered n = (batch*H + head)*S + position.
+ *   packed indices : uint8 [N, ceil(d*b/8)], LSB-first bit stream per row: field i
+ *                    occupies stream bits [i*b, i*b+b); stream bit g is bit g%8 of
+ *                    byte g/8.  Keys use b = bits-1, values use b = bits.
+ *   packed signs   : uint8 [N, d/8], one bit per sketch coordinate, 1 = (>= 0).
+ *   norms          : IEEE fp16 bit patterns, uint16 [N].
+ */
+#ifndef TQ_B200_H
+#define TQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  TQ_OK = 0,
+  TQ_ERR_INVALID_ARG = 1,   /* bad size, unsupported bits/head_dim, NULL or misaligned pointer */
+  TQ_ERR_CUDA = 2,          /* a CUDA runtime call failed; message holds cudaGetErrorString */
+  TQ_ERR_UNSUPPORTED = 3,   /* valid request that this build does not implement */
+  TQ_ERR_WORKSPACE = 4,     /* caller-supplied scratch buffer too small or misaligned */
+  TQ_ERR_DEVICE_WAIT = 5    /* a bounded device-side wait gave up (see tq_device_fault_count) */
+} tq_status;
+
+typedef enum { TQ_F32 = 0, TQ_BF16 = 1, TQ_F16 = 2 } tq_dtype;
+
+/* Arithmetic mode.  TQ_MODE_FP32: every contraction in fp32 on the CUDA cores, the
+ * parity mode.  TQ_MODE_BF16: contractions on the tensor cores (tcgen05) from bf16
+ * operands with fp32 accumulation, the throughput mode. */
+typedef enum { TQ_MODE_FP32 = 0, TQ_MODE_BF16 = 1 } tq_mode;
+
+/* Library version, major*10000 + minor*100 + patch. */
+int tq_version(void);
+
+/* Message of the last failing call made by this host thread ("" if none). */
+const char* tq_last_error(void);
+
+/* Number of bounded device-side waits that have expired since the library was
+ * loaded (0 in a healthy process).  Reads a device counter; synchronises `stream`. */
+int tq_device_fault_count(void* stream, int64_t* count_host);
+
+/* ---- wire-format primitives (test hooks and standalone operators) ------------- */
+
+/* int32 [n, d] -> packed [n, ceil(d*b/8)], 1 <= b <= 8, d*b a multiple of 8.
+ * Replaces pack_bits (src/turboquant_pytorch/kernels/bit_ops.py:173-199, :243-286). */
+int tq_pack_bits(const int32_t* indices, int64_t n, int d, int b, uint8_t* packed, void* stream);
+
+/* Inverse of tq_pack_bits.  Replaces unpack_bits (kernels/bit_ops.py:201-235, :288-326). */
+int tq_unpack_bits(const uint8_t* packed, int64_t n, int d, int b, int32_t* indices, void* stream);
+
+/* fp32 rotated coordinates [n, d] -> packed Lloyd-Max indices.  index = number of
+ * boundaries strictly below the coordinate (first-minimum argmin, lower neighbour
+ * on an exact tie).  `boundaries` holds 2^b_eff - 1 ascending fp32 values.
+ * Replaces lloyd_max_quantize (kernels/quantize.py:201-247, :299-339) and the argmin
+ * of compressors.py:141-142, :288-289. */
+int tq_quantize_rotated(const float* rotated, int64_t n, int d, const float* boundaries, int b_eff,
+                        uint8_t* packed, void* stream);
+
+/* packed indices -> fp32 centroid values [n, d].  `centroids` holds 2^b fp32 values.
+ * Replaces lloyd_max_dequantize (kernels/quantize.py:249-290, :341-369). */
+int tq_dequantize(const uint8_t* packed, int64_t n, int d, const float* centroids, int b,
+                  float* out, void* stream);
+
+/* ---- compression ---------------------------------------------------------------- */
+
+/* Key compression: norm, normalise, rotate by Pi^T, Lloyd-Max index with bits-1 bits,
+ * residual, its norm, and the sign of its QJL sketch, for every vector of
+ * keys[B, H, S, d].  Strides are in elements; the innermost dimension is contiguous
+ * and every row starts on a 16-byte boundary.
+ *   Pi         fp32 [d, d]  rotation (rotated = x @ Pi^T)
+ *   S_eff      fp32 [d, d]  sketch matrix in rotated coordinates, S @ Pi^T
+ *   centroids  fp32 [2^(bits-1)], boundaries fp32 [2^(bits-1) - 1]
+ * Outputs: packed_idx [N, d*(bits-1)/8], packed_signs [N, d/8], vec_norms [N],
+ * residual_norms [N] (fp16 bit patterns), N = B*H*S.
+ * Replaces TurboQuantCompressorV2.compress (compressors.py:98-161) with the packed
+ * result layout of compressors.py:132-138. */
+int tq_compress_keys(const void* keys, int dtype, int64_t B, int64_t H, int64_t S, int d,
+                     int64_t stride_b, int64_t stride_h, int64_t stride_s,
+                     const float* Pi, const float* S_eff, const float* centroids,
+                     const float* boundaries, int bits,
+                     uint8_t* packed_idx, uint8_t* packed_signs, uint16_t* vec_norms,
+                     uint16_t* residual_norms, int mode, void* stream);
+
+/* Value compression: norm, normalise, rotate, Lloyd-Max index with `bits` bits.
+ * Replaces TurboQuantCompressorMSE.compress (compressors.py:270-294), packed layout
+ * of compressors.py:281-285. */
+int tq_compress_values(const void* values, int dtype, int64_t B, int64_t H, int64_t S, int d,
+                       int64_t stride_b, int64_t stride_h, int64_t stride_s,
+                       const float* Pi, const float* boundaries, int bits,
+                       uint8_t* packed_idx, uint16_t* vec_norms, int mode, void* stream);
+
+/* Packed values -> fp32 [N, d]: centroid lookup, back-rotation by Pi, times the norm.
+ * Replaces TurboQuantCompressorMSE.decompress (compressors.py:296-317). */
+int tq_decompress_values(const uint8_t* packed_idx, const uint16_t* vec_norms, int64_t n, int d,
+                         const float* Pi, const float* centroids, int bits, float* out,
+                         void* stream);
+
+/* ---- attention -------------------------------------------------------------------- */
+
+/* Unscaled, unmasked estimator scores, fp32 [B, Hq, Sq, Sk]:
+ *   score = n_k <q Pi^T, C[idx_k]> + sqrt(pi/2)/d * rn_k <q Pi^T S_eff^T, +-1_k>.
+ * Query head h reads key head h / (Hq/Hkv).  Materialises the full matrix: meant for
+ * parity checks and small shapes.  `workspace` must hold tq_attention_workspace_bytes.
+ * Replaces TurboQuantCompressorV2.asymmetric_attention_scores (compressors.py:163-224)
+ * and kernels/attention.py:274-372. */
+int tq_attention_scores(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq, int d,
+                        int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                        int64_t Hkv, int64_t Sk,
+                        const uint8_t* key_idx, const uint8_t* key_signs,
+                        const uint16_t* key_vec_norms, const uint16_t* key_residual_norms,
+                        const float* Pi_k, const float* S_eff, const float* centroids_k, int bits,
+                        float* scores, void* workspace, size_t workspace_bytes, int mode,
+                        void* stream);
+
+/* Query preparation, the per-query half of the estimator: q_cat[n, 0:d] = q Pi^T and
+ * q_cat[n, d:2d] = sqrt(pi/2)/d * q S^T (S = S_eff Pi), row n = (b*Hq + h)*Sq + s.
+ * q_cat is fp32 [N, 2d] in TQ_MODE_FP32 and bf16 [N, 2d] in TQ_MODE_BF16, where
+ * `workspace` must hold 4*d*d bytes (256-byte aligned; unused in fp32 mode).
+ * Replaces the q_rot / S_eff projections of compressors.py:186-189 and the per-query
+ * projection loop of kernels/attention.py:158-167. */
+int tq_prepare_queries(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq, int d,
+                       int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                       const float* Pi_k, const float* S_eff, void* q_cat,
+                       void* workspace, size_t workspace_bytes, int mode, void* stream);
+
+/* Scratch bytes tq_attention_scores / tq_attention_fwd need for the given problem. */
+size_t tq_attention_workspace_bytes(int64_t B, int64_t Hq, int64_t Sq, int d, int mode);
+
+/* Fused compressed attention: out = softmax(scores*sm_scale + mask) @ V_hat, computed
+ * from packed keys and values without materialising scores or decompressed K/V.
+ *   causal != 0 : query i (aligned to the end of the keys) sees keys <= i + Sk - Sq.
+ *   mask        : optional additive fp32 mask, element (b, i, k) at
+ *                 mask[b*mask_stride_b + i*mask_stride_q + k]; NULL for none.
+ *   out         : [B, Hq, Sq, d] of `dtype` with the given element strides.
+ * Replaces the attention core of the family adapters
+ * (src/transformers_turboquant/families/llama.py:100-114, gpt2.py:90-110). */
+int tq_attention_fwd(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq, int d,
+                     int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                     int64_t Hkv, int64_t Sk,
+                     const uint8_t* key_idx, const uint8_t* key_signs,
+                     const uint16_t* key_vec_norms, const uint16_t* key_residual_norms,
+                     const uint8_t* val_idx, const uint16_t* val_vec_norms,
+                     const float* Pi_k, const float* S_eff, const float* centroids_k,
+                     const float* Pi_v, const float* centroids_v, int bits,
+                     float sm_scale, int causal,
+                     const float* mask, int64_t mask_stride_b, int64_t mask_stride_q,
+                     void* out, int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s,
+                     void* workspace, size_t workspace_bytes, int mode, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TQ_B200_H */

@@ -1,0 +1,146 @@
+"""Estimator scores and fused attention on the GPU, fed with the ORACLE's packed bytes so
+that both sides consume identical compressed data.
+
+Tolerances (norm-wise relative error ||a-b||/||b||): 1e-4 in fp32 mode, 1e-2 in bf16 mode."""
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import (device_compressors, oracle_attention_from_packed, oracle_key_dict_to_device, oracle_params,
+                     oracle_value_dict_to_device, rel_err)
+from oracle import tq_oracle as orc
+
+pytestmark = pytest.mark.gpu
+TOL = {"fp32": 1e-4, "bf16": 1e-2}
+
+
+def _case(B, Hq, Hkv, Sq, Sk, d, seed=0, dtype=torch.float32, outliers=True):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(B, Hq, Sq, d, generator=g).to(dtype)
+    k = torch.randn(B, Hkv, Sk, d, generator=g)
+    if outliers:
+        k[..., torch.randperm(d, generator=g)[:4]] *= 8
+    v = torch.randn(B, Hkv, Sk, d, generator=g)
+    return q, k.to(dtype), v.to(dtype)
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("bits", [2, 3, 4])
+def test_scores_match_reference_fixture(d, bits, golden_comp):
+    """Scores from the reference run's own packed bytes vs (a) the fp32 evaluation of the
+    estimator and (b) the reference's literal PyTorch-branch scores (fp16 k_mse storage)."""
+    tag = f"d{d}_bits{bits}"
+    kp, _ = oracle_params(d, bits)
+    q = torch.from_numpy(golden_comp[f"q_d{d}"])
+    k = torch.from_numpy(golden_comp[f"k_d{d}"])
+    ok = orc.key_compress(k, kp)
+    kc, _ = device_compressors(d, bits)
+    sc = kc.asymmetric_attention_scores(q.cuda(), oracle_key_dict_to_device(ok)).cpu()
+    want = orc.scores_from_packed(q, ok["packed_key_indices"], ok["packed_qjl_signs"], ok["vec_norms"],
+                                  ok["residual_norm"], kp, ok["shape"])
+    assert sc.shape == want.shape and sc.dtype == torch.float32
+    assert rel_err(sc, want) < 1e-5
+    assert rel_err(sc, torch.from_numpy(golden_comp[f"scores_{tag}"])) < 1e-3    # fp16 k_mse in the literal path
+    assert float((sc - torch.from_numpy(golden_comp[f"packed_scores_{tag}"])).abs().max()) < 3e-2  # reference's own bar
+
+
+@pytest.mark.parametrize("mode", ["fp32", "bf16"])
+@pytest.mark.parametrize("d,bits", [(128, 3), (128, 2), (128, 4), (64, 3)])
+def test_fused_attention_causal_gqa(mode, d, bits):
+    B, Hq, Hkv, S = 2, 4, 2, 200   # two query heads per KV head, ragged tile edge
+    dtype = torch.float32 if mode == "fp32" else torch.bfloat16
+    q, k, v = _case(B, Hq, Hkv, S, S, d, seed=bits, dtype=dtype)
+    kp, vp = oracle_params(d, bits)
+    ok, ov = orc.key_compress(k, kp), orc.value_compress(v, vp)
+    want = oracle_attention_from_packed(q, ok, ov, kp, vp, causal=True)
+    from turboquant_b200 import fused_attention
+    kc, vc = device_compressors(d, bits, mode=mode)
+    out = fused_attention(q.cuda(), oracle_key_dict_to_device(ok), oracle_value_dict_to_device(ov), kc, vc,
+                          causal=True, mode=mode)
+    assert out.shape == q.shape and out.dtype == dtype
+    assert rel_err(out, want) < TOL[mode], rel_err(out, want)
+
+
+@pytest.mark.parametrize("mode", ["fp32", "bf16"])
+@pytest.mark.parametrize("Sq,Sk", [(1, 1), (7, 7), (129, 129), (64, 300), (1, 513), (256, 256)])
+def test_fused_attention_shapes(mode, Sq, Sk):
+    d, bits = 128, 3
+    dtype = torch.float32 if mode == "fp32" else torch.bfloat16
+    q, k, v = _case(1, 2, 1, Sq, Sk, d, seed=Sq + Sk, dtype=dtype)
+    kp, vp = oracle_params(d, bits)
+    ok, ov = orc.key_compress(k, kp), orc.value_compress(v, vp)
+    want = oracle_attention_from_packed(q, ok, ov, kp, vp, causal=True)
+    from turboquant_b200 import fused_attention
+    kc, vc = device_compressors(d, bits, mode=mode)
+    out = fused_attention(q.cuda(), oracle_key_dict_to_device(ok), oracle_value_dict_to_device(ov), kc, vc, mode=mode)
+    assert rel_err(out, want) < TOL[mode], rel_err(out, want)
+
+
+@pytest.mark.parametrize("mode", ["fp32", "bf16"])
+def test_fused_attention_additive_mask_and_noncausal(mode):
+    """Padding-style additive mask (finite large negative, as HF builds it) and the
+    non-causal path."""
+    d, bits, B, S = 128, 3, 2, 150
+    dtype = torch.float32 if mode == "fp32" else torch.bfloat16
+    q, k, v = _case(B, 2, 2, S, S, d, seed=5, dtype=dtype)
+    kp, vp = oracle_params(d, bits)
+    ok, ov = orc.key_compress(k, kp), orc.value_compress(v, vp)
+    mask = torch.zeros(B, 1, S, S)
+    mask[1, :, :, :17] = torch.finfo(torch.float32).min   # batch 1: first 17 keys are padding
+    from turboquant_b200 import fused_attention
+    kc, vc = device_compressors(d, bits, mode=mode)
+    dk, dv = oracle_key_dict_to_device(ok), oracle_value_dict_to_device(ov)
+    want = oracle_attention_from_packed(q, ok, ov, kp, vp, causal=True, mask=mask)
+    out = fused_attention(q.cuda(), dk, dv, kc, vc, causal=True, attention_mask=mask.cuda(), mode=mode)
+    # rows of batch 1 that only see padding are a uniform average in both implementations
+    assert rel_err(out[:, :, 17:], want[:, :, 17:]) < TOL[mode]
+    want_nc = oracle_attention_from_packed(q, ok, ov, kp, vp, causal=False)
+    out_nc = fused_attention(q.cuda(), dk, dv, kc, vc, causal=False, mode=mode)
+    assert rel_err(out_nc, want_nc) < TOL[mode]
+
+
+@pytest.mark.parametrize("mode", ["fp32", "bf16"])
+def test_prepare_queries(mode):
+    """q_cat = [q Pi^T | coeff q S^T]: the tensor-core row GEMM against fp32 torch."""
+    from turboquant_b200 import _lib as L
+    d = 128
+    kp, _ = oracle_params(d, 3)
+    g = torch.Generator().manual_seed(3)
+    dtype = torch.float32 if mode == "fp32" else torch.bfloat16
+    q = torch.randn(2, 3, 70, d, generator=g).to(dtype)
+    want = torch.cat([q.float() @ kp.Pi.T, orc.qjl_coeff(d) * (q.float() @ kp.S.T)], dim=-1).reshape(-1, 2 * d)
+    kc, _ = device_compressors(d, 3)
+    qd = q.cuda()
+    out = torch.empty((2 * 3 * 70, 2 * d), dtype=dtype, device="cuda")
+    ws = torch.empty(4 * d * d, dtype=torch.uint8, device="cuda")
+    m = L.TQ_MODE_FP32 if mode == "fp32" else L.TQ_MODE_BF16
+    L.check(L.lib.tq_prepare_queries(qd.data_ptr(), 0 if mode == "fp32" else 1, 2, 3, 70, d, qd.stride(0), qd.stride(1),
+                                     qd.stride(2), kc.Pi.data_ptr(), kc.S_eff.data_ptr(), out.data_ptr(),
+                                     ws.data_ptr(), ws.numel(), m, torch.cuda.current_stream().cuda_stream))
+    assert rel_err(out[:, :d], want[:, :d]) < (1e-5 if mode == "fp32" else 6e-3)
+    assert rel_err(out[:, d:], want[:, d:]) < (1e-5 if mode == "fp32" else 6e-3)
+
+
+def test_end_to_end_operator_sequence_vs_reference_fixture(golden_family):
+    """compress -> fused attention through the product API on the reference GPT-2 adapter's
+    inputs, against the reference adapter's output (fp32, bits 2/3/4)."""
+    from turboquant_b200 import TurboQuantCompressorMSE, TurboQuantCompressorV2, fused_attention
+    g = golden_family
+    hidden = torch.from_numpy(g["hidden"]).cuda()
+    qkv = hidden @ torch.from_numpy(g["c_attn_w"]).cuda() + torch.from_numpy(g["c_attn_b"]).cuda()
+    B, T, E = hidden.shape
+    q, k, v = (t.view(B, T, 2, 64).transpose(1, 2) for t in qkv.split(E, dim=2))
+    for bits in (2, 3, 4):
+        kc = TurboQuantCompressorV2(64, bits, seed=42, device="cuda")
+        vc = TurboQuantCompressorMSE(64, bits, seed=10042, device="cuda")
+        out = fused_attention(q, kc.compress(k), vc.compress(v), kc, vc, causal=True,
+                              attention_mask=torch.from_numpy(g["mask"]).cuda())
+        out = out.transpose(1, 2).reshape(B, T, E) @ torch.from_numpy(g["c_proj_w"]).cuda() + torch.from_numpy(g["c_proj_b"]).cuda()
+        # the literal reference stores k_mse in fp16 (2e-4 away from the fp32 estimator)
+        assert rel_err(out, torch.from_numpy(g[f"out_bits{bits}"])) < 2e-3
+
+
+def test_no_device_wait_faults():
+    from turboquant_b200 import device_fault_count
+    assert device_fault_count() == 0

@@ -1,0 +1,108 @@
+"""Fused compression kernels against the reference-generated fixtures and the oracle."""
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import device_compressors, oracle_params
+from oracle import tq_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def _bit_mismatch(a: np.ndarray, b: np.ndarray) -> float:
+    return float(np.unpackbits(np.bitwise_xor(a, b)).mean())
+
+
+def _index_mismatch(packed_a, packed_b, bits, d) -> float:
+    ia = orc.unpack_bits(packed_a, bits, d)
+    ib = orc.unpack_bits(packed_b, bits, d)
+    assert np.abs(ia - ib).max() <= 1, "an index moved by more than one level"
+    return float((ia != ib).mean())
+
+
+def _fp16_close(a: torch.Tensor, b: torch.Tensor, ulps=1) -> bool:
+    """fp16 values equal up to `ulps` units in the last place (norms are reduced in a
+    different order on the GPU)."""
+    ai = a.cpu().contiguous().view(torch.int16).int()
+    bi = b.cpu().contiguous().view(torch.int16).int()
+    return int((ai - bi).abs().max()) <= ulps
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("bits", [2, 3, 4])
+def test_compress_matches_reference_fixture(d, bits, golden_comp):
+    """Same fp32 inputs (zero vector and outlier channel included) as the reference run."""
+    tag = f"d{d}_bits{bits}"
+    k = torch.from_numpy(golden_comp[f"k_d{d}"]).cuda()
+    v = torch.from_numpy(golden_comp[f"v_d{d}"]).cuda()
+    kc, vc = device_compressors(d, bits, mode="fp32")
+    ck, cv = kc.compress(k), vc.compress(v)
+    B, H, S, _ = k.shape
+    assert ck["shape"] == (B, H, S, d) and ck["packed_key_indices"].shape == (B * H * S, d * (bits - 1) // 8)
+    assert ck["packed_qjl_signs"].shape == (B * H * S, d // 8) and ck["vec_norms"].dtype == torch.float16
+    # indices: bit-exact
+    assert np.array_equal(ck["packed_key_indices"].cpu().numpy(), golden_comp[f"packed_idx_{tag}"])
+    ref_v = orc.pack_bits(golden_comp[f"v_indices_{tag}"].astype(np.int32), bits)
+    assert np.array_equal(cv["packed_indices"].cpu().numpy(), ref_v)
+    # QJL sign bits: equal except where the projection is ~0 (the zero vector's 'd' bits are
+    # sign(0) >= 0 on both sides); allow a 1e-4 fraction for near-zero projections
+    assert _bit_mismatch(ck["packed_qjl_signs"].cpu().numpy(), golden_comp[f"packed_sgn_{tag}"]) <= 1e-4
+    assert _fp16_close(ck["residual_norm"], torch.from_numpy(golden_comp[f"residual_norm_{tag}"]))
+    assert _fp16_close(cv["vec_norms"], torch.from_numpy(golden_comp[f"v_norms_{tag}"]))
+    # value decompression
+    rec = vc.decompress(cv)
+    assert rec.shape == (B, H, S, d) and rec.dtype == torch.float32
+    ref = torch.from_numpy(golden_comp[f"v_recon_{tag}"])
+    assert float((rec.cpu() - ref).abs().max()) <= 2e-3 * float(ref.abs().max())  # 1 fp16 ulp of the norm
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("d,bits", [(128, 2), (128, 3), (128, 4), (64, 3)])
+def test_compress_vs_oracle_random(dtype, d, bits):
+    """[2, 4, 257, d] in every input type, with outlier channels; strided (transposed) input."""
+    g = torch.Generator().manual_seed(11)
+    B, H, S = 2, 4, 257
+    k = torch.randn(B, S, H, d, generator=g)
+    k[..., 5] *= 8
+    v = torch.randn(B, S, H, d, generator=g)
+    k, v = k.to(dtype), v.to(dtype)
+    kp, vp = oracle_params(d, bits)
+    ok = orc.key_compress(k.transpose(1, 2), kp)
+    ov = orc.value_compress(v.transpose(1, 2), vp)
+    kc, vc = device_compressors(d, bits, mode="fp32")
+    ck = kc.compress(k.cuda().transpose(1, 2))      # non-contiguous view, read in place
+    cv = vc.compress(v.cuda().transpose(1, 2))
+    n_coord = B * H * S * d
+    mk = _index_mismatch(ck["packed_key_indices"].cpu().numpy(), ok["packed_key_indices"], bits - 1, d)
+    mv = _index_mismatch(cv["packed_indices"].cpu().numpy(), ov["packed_indices"], bits, d)
+    assert mk <= 2.0 / n_coord + 1e-6 and mv <= 2.0 / n_coord + 1e-6, (mk, mv)
+    assert _bit_mismatch(ck["packed_qjl_signs"].cpu().numpy(), ok["packed_qjl_signs"]) <= 5e-5
+    assert _fp16_close(ck["vec_norms"], ok["vec_norms"]) and _fp16_close(ck["residual_norm"], ok["residual_norm"])
+    assert _fp16_close(cv["vec_norms"], ov["vec_norms"])
+
+
+@pytest.mark.parametrize("S", [1, 7, 63, 64, 65, 129])
+def test_compress_ragged_lengths(S):
+    d, bits = 128, 3
+    g = torch.Generator().manual_seed(S)
+    k = torch.randn(1, 3, S, d, generator=g)
+    kp, vp = oracle_params(d, bits)
+    kc, vc = device_compressors(d, bits, mode="fp32")
+    ck, cv = kc.compress(k.cuda()), vc.compress(k.cuda())
+    ok, ov = orc.key_compress(k, kp), orc.value_compress(k, vp)
+    assert np.array_equal(ck["packed_key_indices"].cpu().numpy(), ok["packed_key_indices"])
+    assert np.array_equal(cv["packed_indices"].cpu().numpy(), ov["packed_indices"])
+    assert _bit_mismatch(ck["packed_qjl_signs"].cpu().numpy(), ok["packed_qjl_signs"]) <= 1e-3
+
+
+def test_compress_empty_and_zero_vectors():
+    kc, vc = device_compressors(128, 3, mode="fp32")
+    e = kc.compress(torch.zeros(2, 0, 5, 128, device="cuda"))
+    assert e["packed_key_indices"].shape == (0, 32) and e["shape"] == (2, 0, 5, 128)
+    z = kc.compress(torch.zeros(1, 1, 3, 128, device="cuda"))
+    kp, _ = oracle_params(128, 3)
+    oz = orc.key_compress(torch.zeros(1, 1, 3, 128), kp)
+    assert np.array_equal(z["packed_key_indices"].cpu().numpy(), oz["packed_key_indices"])
+    assert np.array_equal(z["packed_qjl_signs"].cpu().numpy(), oz["packed_qjl_signs"])
+    assert float(z["vec_norms"].float().abs().max()) == 0.0 and float(z["residual_norm"].float().abs().max()) == 0.0

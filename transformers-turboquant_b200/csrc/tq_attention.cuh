@@ -1,0 +1,48 @@
+// Argument block and entry points shared by the fp32 (CUDA-core) and bf16 (tcgen05)
+// implementations of the fused compressed attention.
+#pragma once
+#include "tq_common.cuh"
+
+namespace tq {
+
+struct AttnArgs {
+  const void* q_cat;   // fp32 [n, 2d] (fp32 mode) or bf16 [n, 2d] (bf16 mode), row n = (b*Hq+h)*Sq+s
+  int64_t Hq, Sq, Hkv, Sk;
+  const uint8_t* key_idx;
+  const uint8_t* key_sgn;
+  const uint16_t* key_vn;
+  const uint16_t* key_rn;
+  const uint8_t* val_idx;
+  const uint16_t* val_vn;
+  const float* cen_k;
+  const float* cen_v;
+  const float* Pi_v;
+  float sm_scale;
+  int causal;
+  const float* mask;
+  int64_t mask_stride_b, mask_stride_q;
+  void* out;
+  int out_dtype;
+  int64_t o_stride_b, o_stride_h, o_stride_s;
+};
+
+int check_attention_args(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq, int d, int64_t sb, int64_t sh,
+                         int64_t ss, int64_t Hkv, int64_t Sk, int bits, int mode);
+
+// fp32 mode: query preparation + CUDA-core flash kernel.  `workspace` holds q_cat fp32.
+int attention_fwd_fp32(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq, int d, int64_t sb, int64_t sh,
+                       int64_t ss, const float* Pi_k, const float* S_eff, AttnArgs a, int bits, void* workspace,
+                       cudaStream_t stream);
+
+// bf16 mode: tcgen05 query preparation, tcgen05 flash kernel, tcgen05 back-rotation.
+int attention_fwd_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq, int d, int64_t sb, int64_t sh,
+                       int64_t ss, const float* Pi_k, const float* S_eff, AttnArgs a, int bits, void* workspace,
+                       cudaStream_t stream);
+
+size_t workspace_bytes_bf16(int64_t n_q, int d);
+
+int prepare_queries_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq, int d, int64_t sb, int64_t sh,
+                         int64_t ss, const float* Pi_k, const float* S_eff, void* w_cat_scratch, void* q_cat,
+                         cudaStream_t stream);
+
+}  // namespace tq

@@ -1,0 +1,216 @@
+// Error plumbing, version, and the wire-format primitives: pack, unpack, Lloyd-Max
+// quantise of rotated coordinates, centroid dequantise.  These are HBM-bound byte
+// kernels; each thread owns 8 consecutive fields, i.e. exactly b whole bytes of the
+// row's bit stream, so no atomics or pre-zeroed outputs are needed.
+#include <stdarg.h>
+#include <string.h>
+
+#include "tq_common.cuh"
+
+namespace tq {
+
+static thread_local char t_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(t_error, sizeof(t_error), fmt, ap);
+  va_end(ap);
+}
+
+int fail(tq_status st, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(t_error, sizeof(t_error), fmt, ap);
+  va_end(ap);
+  return st;
+}
+
+// ---- kernels ----------------------------------------------------------------------------
+
+// One thread per group of 8 fields.  groups_per_row = d/8.
+template <int BITS>
+__global__ void pack_kernel(const int32_t* __restrict__ idx, int64_t n_groups, int groups_per_row,
+                            uint8_t* __restrict__ out) {
+  int64_t g = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (g >= n_groups) return;
+  const int4* src = reinterpret_cast<const int4*>(idx + g * 8);
+  int4 a = src[0], b = src[1];
+  int f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+  store_fields8<BITS>(out + g * BITS, f);
+}
+
+template <int BITS>
+__global__ void unpack_kernel(const uint8_t* __restrict__ packed, int64_t n_groups,
+                              int32_t* __restrict__ idx) {
+  int64_t g = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (g >= n_groups) return;
+  uint64_t w = load_fields8<BITS>(packed + g * BITS);
+  int f[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) f[i] = static_cast<int>((w >> (i * BITS)) & ((1u << BITS) - 1));
+  int4* dst = reinterpret_cast<int4*>(idx + g * 8);
+  dst[0] = make_int4(f[0], f[1], f[2], f[3]);
+  dst[1] = make_int4(f[4], f[5], f[6], f[7]);
+}
+
+template <int BITS>
+__global__ void quantize_kernel(const float* __restrict__ rotated, int64_t n_groups,
+                                const float* __restrict__ boundaries, uint8_t* __restrict__ out) {
+  constexpr int NB = (1 << BITS) - 1;
+  float bnd[NB];
+#pragma unroll
+  for (int j = 0; j < NB; ++j) bnd[j] = __ldg(boundaries + j);
+  int64_t g = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (g >= n_groups) return;
+  float y[8];
+  load8<float>(rotated + g * 8, y);
+  int f[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) f[i] = count_below<NB>(y[i], bnd);
+  store_fields8<BITS>(out + g * BITS, f);
+}
+
+template <int BITS>
+__global__ void dequantize_kernel(const uint8_t* __restrict__ packed, int64_t n_groups,
+                                  const float* __restrict__ centroids, float* __restrict__ out) {
+  __shared__ float lut[1 << BITS];
+  if (threadIdx.x < (1 << BITS)) lut[threadIdx.x] = centroids[threadIdx.x];
+  __syncthreads();
+  int64_t g = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (g >= n_groups) return;
+  uint64_t w = load_fields8<BITS>(packed + g * BITS);
+  float v[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = lut[(w >> (i * BITS)) & ((1u << BITS) - 1)];
+  float4* dst = reinterpret_cast<float4*>(out + g * 8);
+  dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+  dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+
+template <template <int> class Launcher, typename... Args>
+static int dispatch_bits(int b, Args... args) {
+  switch (b) {
+    case 1: return Launcher<1>::run(args...);
+    case 2: return Launcher<2>::run(args...);
+    case 3: return Launcher<3>::run(args...);
+    case 4: return Launcher<4>::run(args...);
+    case 5: return Launcher<5>::run(args...);
+    case 6: return Launcher<6>::run(args...);
+    case 7: return Launcher<7>::run(args...);
+    case 8: return Launcher<8>::run(args...);
+  }
+  return fail(TQ_ERR_INVALID_ARG, "bit width %d outside 1..8", b);
+}
+
+static inline unsigned grid_for(int64_t n_groups) { return static_cast<unsigned>((n_groups + 255) / 256); }
+
+template <int BITS>
+struct PackL {
+  static int run(const int32_t* idx, int64_t ng, int gpr, uint8_t* out, cudaStream_t s) {
+    pack_kernel<BITS><<<grid_for(ng), 256, 0, s>>>(idx, ng, gpr, out);
+    return TQ_OK;
+  }
+};
+template <int BITS>
+struct UnpackL {
+  static int run(const uint8_t* p, int64_t ng, int32_t* idx, cudaStream_t s) {
+    unpack_kernel<BITS><<<grid_for(ng), 256, 0, s>>>(p, ng, idx);
+    return TQ_OK;
+  }
+};
+template <int BITS>
+struct QuantL {
+  static int run(const float* r, int64_t ng, const float* b, uint8_t* out, cudaStream_t s) {
+    quantize_kernel<BITS><<<grid_for(ng), 256, 0, s>>>(r, ng, b, out);
+    return TQ_OK;
+  }
+};
+template <int BITS>
+struct DequantL {
+  static int run(const uint8_t* p, int64_t ng, const float* c, float* out, cudaStream_t s) {
+    dequantize_kernel<BITS><<<grid_for(ng), 256, 0, s>>>(p, ng, c, out);
+    return TQ_OK;
+  }
+};
+
+static int check_rows(int64_t n, int d, int b, int bmax) {
+  TQ_REQUIRE(n >= 0, "row count %lld is negative", (long long)n);
+  TQ_REQUIRE(d > 0 && d % 8 == 0, "row length %d must be a positive multiple of 8", d);
+  TQ_REQUIRE(b >= 1 && b <= bmax, "bit width %d outside 1..%d", b, bmax);
+  TQ_REQUIRE(n * (int64_t)(d / 8) < (int64_t)1 << 39, "problem too large");
+  return TQ_OK;
+}
+
+}  // namespace tq
+
+using namespace tq;
+
+extern "C" {
+
+int tq_version(void) { return 100; }
+
+const char* tq_last_error(void) { return t_error; }
+
+int tq_device_fault_count(void* stream, int64_t* count_host) {
+  TQ_REQUIRE(count_host != nullptr, "count_host is NULL");
+  unsigned long long v = 0;
+  TQ_CUDA_OK(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  if (int st = read_wait_faults(&v)) return st;
+  *count_host = static_cast<int64_t>(v);
+  return TQ_OK;
+}
+
+int tq_pack_bits(const int32_t* indices, int64_t n, int d, int b, uint8_t* packed, void* stream) {
+  if (int st = check_rows(n, d, b, 8)) return st;
+  if (n == 0) return TQ_OK;
+  TQ_REQUIRE(indices && packed, "NULL pointer");
+  TQ_REQUIRE(aligned16(indices), "indices must be 16-byte aligned");
+  int st = dispatch_bits<PackL>(b, indices, n * (d / 8), d / 8, packed, static_cast<cudaStream_t>(stream));
+  if (st) return st;
+  TQ_CUDA_OK(cudaGetLastError());
+  return TQ_OK;
+}
+
+int tq_unpack_bits(const uint8_t* packed, int64_t n, int d, int b, int32_t* indices, void* stream) {
+  if (int st = check_rows(n, d, b, 8)) return st;
+  if (n == 0) return TQ_OK;
+  TQ_REQUIRE(indices && packed, "NULL pointer");
+  TQ_REQUIRE(aligned16(indices), "indices must be 16-byte aligned");
+  int st = dispatch_bits<UnpackL>(b, packed, n * (d / 8), indices, static_cast<cudaStream_t>(stream));
+  if (st) return st;
+  TQ_CUDA_OK(cudaGetLastError());
+  return TQ_OK;
+}
+
+int tq_quantize_rotated(const float* rotated, int64_t n, int d, const float* boundaries, int b_eff,
+                        uint8_t* packed, void* stream) {
+  if (int st = check_rows(n, d, b_eff, 4)) return st;
+  if (n == 0) return TQ_OK;
+  TQ_REQUIRE(rotated && boundaries && packed, "NULL pointer");
+  TQ_REQUIRE(aligned16(rotated), "rotated must be 16-byte aligned");
+  const int64_t ng = n * (d / 8);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (b_eff) {  // boundaries live in registers, so only the widths the codebooks use
+    case 1: QuantL<1>::run(rotated, ng, boundaries, packed, s); break;
+    case 2: QuantL<2>::run(rotated, ng, boundaries, packed, s); break;
+    case 3: QuantL<3>::run(rotated, ng, boundaries, packed, s); break;
+    default: QuantL<4>::run(rotated, ng, boundaries, packed, s); break;
+  }
+  TQ_CUDA_OK(cudaGetLastError());
+  return TQ_OK;
+}
+
+int tq_dequantize(const uint8_t* packed, int64_t n, int d, const float* centroids, int b, float* out,
+                  void* stream) {
+  if (int st = check_rows(n, d, b, 8)) return st;
+  if (n == 0) return TQ_OK;
+  TQ_REQUIRE(packed && centroids && out, "NULL pointer");
+  TQ_REQUIRE(aligned16(out), "out must be 16-byte aligned");
+  int st = dispatch_bits<DequantL>(b, packed, n * (d / 8), centroids, out, static_cast<cudaStream_t>(stream));
+  if (st) return st;
+  TQ_CUDA_OK(cudaGetLastError());
+  return TQ_OK;
+}
+
+}  // extern "C"

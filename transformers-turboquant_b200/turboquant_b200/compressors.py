@@ -1,0 +1,272 @@
+"""Key / value compressors backed by the sm_100a CUDA library.
+
+`TurboQuantCompressorV2` and `TurboQuantCompressorMSE` keep the constructor signature,
+attribute names (`Pi, PiT, S, centroids, boundaries, bits, mse_bits, head_dim, device`)
+and methods (`compress`, `asymmetric_attention_scores`, `decompress`) of the reference
+classes (src/turboquant_pytorch/compressors.py:36-317) and always produce its bit-packed
+result layout (compressors.py:132-138, :281-285).  Inputs must live on a CUDA device; there
+is no CPU path.  `fused_attention` is the entry the family adapters call: compressed causal
+attention without the score matrix or decompressed K/V.
+"""
+
+from __future__ import annotations
+
+import math
+import os
+
+import torch
+
+from . import _lib
+from .codebook import lloyd_max_centroids, midpoints
+
+_DTYPES = {torch.float32: _lib.TQ_F32, torch.bfloat16: _lib.TQ_BF16, torch.float16: _lib.TQ_F16}
+_MODES = {"fp32": _lib.TQ_MODE_FP32, "bf16": _lib.TQ_MODE_BF16}
+
+
+def resolve_mode(dtype: torch.dtype, mode: str | None = None) -> int:
+    """Arithmetic mode of a call.  Explicit `mode`, else the TQ_B200_MODE environment
+    variable ("fp32" | "bf16"), else by input type: fp32 inputs run the fp32 parity
+    kernels, 16-bit inputs the tensor-core kernels."""
+    mode = mode or os.environ.get("TQ_B200_MODE") or "auto"
+    if mode == "auto":
+        return _lib.TQ_MODE_FP32 if dtype == torch.float32 else _lib.TQ_MODE_BF16
+    if mode not in _MODES:
+        raise ValueError(f"mode must be 'fp32', 'bf16' or 'auto', got {mode!r}")
+    return _MODES[mode]
+
+
+def _stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _require_cuda(t: torch.Tensor, what: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{what} must be a CUDA tensor: turboquant_b200 has no CPU path")
+
+
+def _rows_view(t: torch.Tensor) -> torch.Tensor:
+    """[B, H, S, D] tensor whose rows the kernels can read in place: supported dtype, unit
+    inner stride, 16-byte aligned rows.  Anything else is copied once."""
+    if t.dtype not in _DTYPES:
+        t = t.float()
+    esz = t.element_size()
+    ok = t.stride(-1) == 1 and t.data_ptr() % 16 == 0 and all((s * esz) % 16 == 0 for s in t.stride()[:-1])
+    return t if ok else t.contiguous()
+
+
+def _haar_rotation(d: int, seed: int) -> torch.Tensor:
+    """Seeded random rotation: Q factor of a Gaussian matrix with the sign convention
+    diag(R) > 0 (compressors.py:50-56).  Generated on the CPU generator so that a seed
+    means the same matrix everywhere."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    q, r = torch.linalg.qr(torch.randn(d, d, generator=g))
+    s = torch.sign(torch.diagonal(r))
+    s[s == 0] = 1.0
+    return q * s
+
+
+class _Constants:
+    """Device-resident fp32 constants of a compressor and their movement between devices."""
+
+    _tensor_attrs: tuple[str, ...] = ()
+
+    def to(self, device):
+        device = torch.device(device)
+        for name in self._tensor_attrs:
+            setattr(self, name, getattr(self, name).to(device=device, dtype=torch.float32).contiguous())
+        self.device = str(device)
+        return self
+
+    def _check_device(self, t: torch.Tensor) -> None:
+        if self.Pi.device != t.device:
+            self.to(t.device)
+
+
+class TurboQuantCompressorV2(_Constants):
+    """Key compressor: (bits-1)-bit Lloyd-Max indices of the rotated unit vector plus a
+    1-bit QJL sketch of the residual (compressors.py:36-224)."""
+
+    _tensor_attrs = ("Pi", "PiT", "S", "S_eff", "centroids", "boundaries")
+
+    def __init__(self, head_dim: int, bits: int, seed: int, device: str = "cuda", use_triton: bool = True,
+                 mode: str | None = None):
+        if head_dim not in (64, 128):
+            raise ValueError(f"head_dim {head_dim} unsupported by the CUDA kernels (64 or 128)")
+        if bits not in (2, 3, 4):
+            raise ValueError(f"bits must be 2, 3 or 4, got {bits}")
+        self.head_dim, self.bits, self.mse_bits = head_dim, bits, max(bits - 1, 1)
+        self.use_triton = use_triton  # accepted for call compatibility; there is one backend
+        self.mode = mode
+        self.Pi = _haar_rotation(head_dim, seed)
+        self.PiT = self.Pi.T.contiguous()
+        self.centroids = lloyd_max_centroids(head_dim, self.mse_bits)
+        self.boundaries = midpoints(self.centroids)
+        g = torch.Generator(device="cpu").manual_seed(seed + 10000)
+        self.S = torch.randn(head_dim, head_dim, generator=g)
+        self.S_eff = self.S @ self.Pi.T  # sketch matrix in rotated coordinates
+        self.to(device)
+
+    @torch.no_grad()
+    def compress(self, states: torch.Tensor) -> dict:
+        """[B, H, S, D] -> packed dict (one fused kernel)."""
+        _require_cuda(states, "states")
+        self._check_device(states)
+        B, H, S, D = states.shape
+        if D != self.head_dim:
+            raise ValueError(f"last dimension {D} != head_dim {self.head_dim}")
+        x = _rows_view(states)
+        n = B * H * S
+        dev = x.device
+        idx = torch.empty((n, D * self.mse_bits // 8), dtype=torch.uint8, device=dev)
+        sgn = torch.empty((n, D // 8), dtype=torch.uint8, device=dev)
+        vn = torch.empty((B, H, S), dtype=torch.float16, device=dev)
+        rn = torch.empty((B, H, S), dtype=torch.float16, device=dev)
+        _lib.check(_lib.lib.tq_compress_keys(
+            x.data_ptr(), _DTYPES[x.dtype], B, H, S, D, x.stride(0), x.stride(1), x.stride(2),
+            self.Pi.data_ptr(), self.S_eff.data_ptr(), self.centroids.data_ptr(), self.boundaries.data_ptr(),
+            self.bits, idx.data_ptr(), sgn.data_ptr(), vn.data_ptr(), rn.data_ptr(),
+            resolve_mode(x.dtype, self.mode), _stream_ptr(dev)))
+        return {"packed_key_indices": idx, "packed_qjl_signs": sgn, "residual_norm": rn, "vec_norms": vn,
+                "shape": (B, H, S, D)}
+
+    @torch.no_grad()
+    def asymmetric_attention_scores(self, queries: torch.Tensor, compressed: dict) -> torch.Tensor:
+        """Unscaled, unmasked estimator scores fp32 [B, Hq, Sq, Sk] (compressors.py:163-224).
+        Materialises the whole matrix; the adapters use `fused_attention` instead."""
+        _require_cuda(queries, "queries")
+        self._check_device(queries)
+        B, Hq, Sq, D = queries.shape
+        Bk, Hkv, Sk, Dk = compressed["shape"]
+        if (Bk, Dk) != (B, D) or D != self.head_dim:
+            raise ValueError(f"queries {tuple(queries.shape)} do not match compressed keys {compressed['shape']}")
+        q = _rows_view(queries)
+        dev = q.device
+        scores = torch.empty((B, Hq, Sq, Sk), dtype=torch.float32, device=dev)
+        ws_bytes = _lib.lib.tq_attention_workspace_bytes(B, Hq, Sq, D, _lib.TQ_MODE_FP32)
+        ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
+        _lib.check(_lib.lib.tq_attention_scores(
+            q.data_ptr(), _DTYPES[q.dtype], B, Hq, Sq, D, q.stride(0), q.stride(1), q.stride(2), Hkv, Sk,
+            compressed["packed_key_indices"].data_ptr(), compressed["packed_qjl_signs"].data_ptr(),
+            compressed["vec_norms"].data_ptr(), compressed["residual_norm"].data_ptr(),
+            self.Pi.data_ptr(), self.S_eff.data_ptr(), self.centroids.data_ptr(), self.bits,
+            scores.data_ptr(), ws.data_ptr(), ws.numel(), _lib.TQ_MODE_FP32, _stream_ptr(dev)))
+        return scores
+
+
+class TurboQuantCompressorMSE(_Constants):
+    """Value compressor: `bits`-bit Lloyd-Max indices of the rotated unit vector
+    (compressors.py:227-317)."""
+
+    _tensor_attrs = ("Pi", "PiT", "centroids", "boundaries")
+
+    def __init__(self, head_dim: int, bits: int, seed: int, device: str = "cuda", use_triton: bool = True,
+                 mode: str | None = None):
+        if head_dim not in (64, 128):
+            raise ValueError(f"head_dim {head_dim} unsupported by the CUDA kernels (64 or 128)")
+        if bits not in (2, 3, 4):
+            raise ValueError(f"bits must be 2, 3 or 4, got {bits}")
+        self.head_dim, self.bits = head_dim, bits
+        self.use_triton = use_triton
+        self.mode = mode
+        self.Pi = _haar_rotation(head_dim, seed)
+        self.PiT = self.Pi.T.contiguous()
+        self.centroids = lloyd_max_centroids(head_dim, bits)
+        self.boundaries = midpoints(self.centroids)
+        self.to(device)
+
+    @torch.no_grad()
+    def compress(self, states: torch.Tensor) -> dict:
+        _require_cuda(states, "states")
+        self._check_device(states)
+        B, H, S, D = states.shape
+        if D != self.head_dim:
+            raise ValueError(f"last dimension {D} != head_dim {self.head_dim}")
+        x = _rows_view(states)
+        n = B * H * S
+        dev = x.device
+        idx = torch.empty((n, D * self.bits // 8), dtype=torch.uint8, device=dev)
+        vn = torch.empty((n,), dtype=torch.float16, device=dev)
+        _lib.check(_lib.lib.tq_compress_values(
+            x.data_ptr(), _DTYPES[x.dtype], B, H, S, D, x.stride(0), x.stride(1), x.stride(2),
+            self.Pi.data_ptr(), self.boundaries.data_ptr(), self.bits, idx.data_ptr(), vn.data_ptr(),
+            resolve_mode(x.dtype, self.mode), _stream_ptr(dev)))
+        return {"packed_indices": idx, "vec_norms": vn, "shape": (B, H, S, D)}
+
+    @torch.no_grad()
+    def decompress(self, compressed: dict) -> torch.Tensor:
+        """packed dict -> fp32 [B, H, S, D] (compressors.py:296-317)."""
+        B, H, S, D = compressed["shape"]
+        idx = compressed["packed_indices"]
+        _require_cuda(idx, "compressed values")
+        self._check_device(idx)
+        out = torch.empty((B, H, S, D), dtype=torch.float32, device=idx.device)
+        _lib.check(_lib.lib.tq_decompress_values(
+            idx.data_ptr(), compressed["vec_norms"].data_ptr(), B * H * S, D, self.Pi.data_ptr(),
+            self.centroids.data_ptr(), self.bits, out.data_ptr(), _stream_ptr(idx.device)))
+        return out
+
+
+@torch.no_grad()
+def fused_attention(q: torch.Tensor, compressed_k: dict, compressed_v: dict,
+                    key_compressor: TurboQuantCompressorV2, val_compressor: TurboQuantCompressorMSE,
+                    causal: bool = True, attention_mask: torch.Tensor | None = None,
+                    sm_scale: float | None = None, mode: str | None = None) -> torch.Tensor:
+    """softmax(scores * sm_scale + mask) @ V_hat from packed K and V: the attention core of
+    the family adapters (families/llama.py:100-114 of the reference) as one fused pass.
+
+    q [B, Hq, Sq, D]; the compressed tensors hold Hkv heads with Hq % Hkv == 0 (query head h
+    reads KV head h // (Hq // Hkv), the `repeat_interleave` grouping).  `attention_mask` is an
+    optional additive mask broadcastable to [B, 1, Sq, Sk].  Returns [B, Hq, Sq, D] in q.dtype.
+    """
+    _require_cuda(q, "q")
+    key_compressor._check_device(q)
+    val_compressor._check_device(q)
+    B, Hq, Sq, D = q.shape
+    Bk, Hkv, Sk, Dk = compressed_k["shape"]
+    if compressed_v["shape"] != compressed_k["shape"] or (Bk, Dk) != (B, D):
+        raise ValueError("q, compressed keys and compressed values disagree on shape")
+    if key_compressor.bits != val_compressor.bits:
+        raise ValueError("key and value compressors must use the same bit width")
+    qv = _rows_view(q)
+    dev = qv.device
+    m = resolve_mode(qv.dtype, mode or key_compressor.mode)
+    out = torch.empty((B, Hq, Sq, D), dtype=qv.dtype, device=dev)
+    ws_bytes = _lib.lib.tq_attention_workspace_bytes(B, Hq, Sq, D, m)
+    ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
+    mask_ptr, msb, msq = None, 0, 0
+    if attention_mask is not None:
+        mk = attention_mask
+        if mk.dim() == 4:
+            if mk.shape[1] != 1:
+                raise ValueError("per-head masks are not supported; expected [B, 1, Sq, Sk]")
+            mk = mk[:, 0]
+        elif mk.dim() == 2:
+            mk = mk.unsqueeze(0)
+        mk = mk.to(device=dev, dtype=torch.float32)
+        if mk.shape[-2:] != (Sq, Sk) or mk.shape[0] not in (1, B):
+            raise ValueError(f"mask shape {tuple(attention_mask.shape)} does not broadcast to [B,1,{Sq},{Sk}]")
+        if mk.stride(-1) != 1:
+            mk = mk.contiguous()
+        mask_ptr, msb, msq = mk.data_ptr(), (mk.stride(0) if mk.shape[0] == B and B > 1 else 0), mk.stride(1)
+    scale = float(sm_scale) if sm_scale is not None else 1.0 / math.sqrt(D)
+    _lib.check(_lib.lib.tq_attention_fwd(
+        qv.data_ptr(), _DTYPES[qv.dtype], B, Hq, Sq, D, qv.stride(0), qv.stride(1), qv.stride(2), Hkv, Sk,
+        compressed_k["packed_key_indices"].data_ptr(), compressed_k["packed_qjl_signs"].data_ptr(),
+        compressed_k["vec_norms"].data_ptr(), compressed_k["residual_norm"].data_ptr(),
+        compressed_v["packed_indices"].data_ptr(), compressed_v["vec_norms"].data_ptr(),
+        key_compressor.Pi.data_ptr(), key_compressor.S_eff.data_ptr(), key_compressor.centroids.data_ptr(),
+        val_compressor.Pi.data_ptr(), val_compressor.centroids.data_ptr(), key_compressor.bits,
+        scale, 1 if causal else 0, mask_ptr, msb, msq,
+        out.data_ptr(), out.stride(0), out.stride(1), out.stride(2),
+        ws.data_ptr(), ws.numel(), m, _stream_ptr(dev)))
+    return out
+
+
+def device_fault_count(device=None) -> int:
+    """Expired bounded device-side waits since the library was loaded (0 when healthy)."""
+    import ctypes
+
+    n = ctypes.c_int64(0)
+    dev = torch.device(device if device is not None else "cuda")
+    _lib.check(_lib.lib.tq_device_fault_count(_stream_ptr(dev), ctypes.byref(n)))
+    return int(n.value)
