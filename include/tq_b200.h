@@ -58,6 +58,23 @@ const char* tq_last_error(void);
  * loaded (0 in a healthy process).  Reads a device counter; synchronises `stream`. */
 int tq_device_fault_count(void* stream, int64_t* count_host);
 
+/* Per-kernel device timing for benchmarks (no counterpart in the reference).  Between
+ * tq_profile_begin and tq_profile_end every launch of the kernel kinds below is bracketed
+ * by CUDA events on its own stream (up to max_records launches per kind, nothing is
+ * synchronised while recording).  tq_profile_end waits for the recorded events and writes,
+ * per kind, the summed milliseconds and the number of launches into two host arrays of
+ * TQ_PROF_KINDS entries.  Process-wide, not thread-safe. */
+enum {
+  TQ_PROF_COMPRESS_KEYS = 0,
+  TQ_PROF_COMPRESS_VALUES = 1,
+  TQ_PROF_PREPARE_QUERIES = 2,
+  TQ_PROF_ATTENTION = 3,
+  TQ_PROF_BACK_ROTATION = 4,
+  TQ_PROF_KINDS = 5
+};
+int tq_profile_begin(int max_records);
+int tq_profile_end(float* ms_sum_host, int* launches_host);
+
 /* ---- wire-format primitives (test hooks and standalone operators) ------------- */
 
 /* int32 [n, d] -> packed [n, ceil(d*b/8)], 1 <= b <= 8, d*b a multiple of 8.

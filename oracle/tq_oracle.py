@@ -81,7 +81,7 @@ def rotation_matrix(d: int, seed: int) -> torch.Tensor:
     q, r = torch.linalg.qr(gauss)
     flip = torch.sign(torch.diag(r))
     flip[flip == 0] = 1.0
-    return q * flip.unsqueeze(0)
+    return (q * flip.unsqueeze(0)).contiguous()  # qr hands back a column-major Q
 
 
 def qjl_matrix(d: int, key_seed: int) -> torch.Tensor:

@@ -26,11 +26,12 @@ def device_compressors(d: int, bits: int, key_seed: int = 42, val_seed: int = 10
     kp, vp = oracle_params(d, bits, key_seed, val_seed)
     kc = TurboQuantCompressorV2(d, bits, key_seed, device="cuda", mode=mode)
     vc = TurboQuantCompressorMSE(d, bits, val_seed, device="cuda", mode=mode)
-    kc.Pi, kc.S, kc.S_eff = kp.Pi.cuda(), kp.S.cuda(), kp.S_eff.contiguous().cuda()
+    # .contiguous(): the Q factor of torch.linalg.qr comes back column-major
+    kc.Pi, kc.S, kc.S_eff = kp.Pi.contiguous().cuda(), kp.S.contiguous().cuda(), kp.S_eff.contiguous().cuda()
     kc.PiT = kc.Pi.T.contiguous()
-    kc.centroids, kc.boundaries = kp.centroids.cuda(), kp.boundaries.contiguous().cuda()
-    vc.Pi, vc.PiT = vp.Pi.cuda(), vp.Pi.T.contiguous().cuda()
-    vc.centroids, vc.boundaries = vp.centroids.cuda(), vp.boundaries.contiguous().cuda()
+    kc.centroids, kc.boundaries = kp.centroids.contiguous().cuda(), kp.boundaries.contiguous().cuda()
+    vc.Pi, vc.PiT = vp.Pi.contiguous().cuda(), vp.Pi.T.contiguous().cuda()
+    vc.centroids, vc.boundaries = vp.centroids.contiguous().cuda(), vp.boundaries.contiguous().cuda()
     return kc, vc
 
 

@@ -438,6 +438,7 @@ static int launch_qprep(const QPrepArgs& a, cudaStream_t stream) {
   TQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int grid = sm_count() * (smem > 110 * 1024 ? 1 : 2);
   if (grid > a.num_tiles) grid = a.num_tiles;
+  ProfScope prof(kProfPrepareQueries, stream);
   kern<<<grid, 16 * (D / 8), smem, stream>>>(a);
   TQ_CUDA_OK(cudaGetLastError());
   return TQ_OK;
@@ -485,6 +486,7 @@ static int launch_attention(const AttnArgs& a, int64_t B, cudaStream_t stream) {
   auto kern = attention_simt_kernel<D, BITS - 1, BITS>;
   TQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid((unsigned)((a.Sq + kRows - 1) / kRows), (unsigned)a.Hq, (unsigned)B);
+  ProfScope prof(kProfAttention, stream);
   kern<<<grid, 256, smem, stream>>>(a);
   TQ_CUDA_OK(cudaGetLastError());
   return TQ_OK;

@@ -481,7 +481,10 @@ static int launch_attention_tc(const AttnArgs& a, int64_t B, __nv_bfloat16* o_ro
   auto kern = attention_tc_kernel<D, BITS>;
   TQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid((unsigned)((a.Sq + kBM - 1) / kBM), (unsigned)a.Hq, (unsigned)B);
-  kern<<<grid, 256, smem, stream>>>(a, o_rot);
+  {
+    ProfScope prof(kProfAttention, stream);
+    kern<<<grid, 256, smem, stream>>>(a, o_rot);
+  }
   TQ_CUDA_OK(cudaGetLastError());
   return TQ_OK;
 }
@@ -499,6 +502,7 @@ int prepare_queries_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_
                          int64_t ss, const float* Pi_k, const float* S_eff, void* w_cat_scratch, void* q_cat,
                          cudaStream_t stream) {
   const int64_t n_q = B * Hq * Sq;
+  ProfScope prof(kProfPrepareQueries, stream);
   __nv_bfloat16* w_cat = static_cast<__nv_bfloat16*>(w_cat_scratch);
   build_wcat_kernel<<<d, d, 0, stream>>>(Pi_k, S_eff, d, sqrtf(1.5707963267948966f) / (float)d, w_cat);
   TQ_CUDA_OK(cudaGetLastError());
@@ -539,6 +543,7 @@ int attention_fwd_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_t 
                      : launch_attention_tc<64, 4>(a, B, o_rot, stream);
   if (st) return st;
 
+  ProfScope prof(kProfBackRotation, stream);
   RowsGemmArgs unrot{o_rot, TQ_BF16, n_q, Hq, Sq, Hq * Sq * d, Sq * d, (int64_t)d, w_unrot, a.out, a.out_dtype,
                      a.o_stride_b, a.o_stride_h, a.o_stride_s, tiles};
   return d == 128 ? launch_rows_gemm<128, 128>(unrot, stream) : launch_rows_gemm<64, 64>(unrot, stream);

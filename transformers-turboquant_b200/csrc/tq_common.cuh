@@ -37,6 +37,18 @@ inline int elem_size(int dtype) { return dtype == TQ_F32 ? 4 : 2; }
 // translation unit) to the host.
 int read_wait_faults(unsigned long long* out);
 
+// ---- optional per-kernel timing (tq_profile_begin / tq_profile_end) ------------------
+enum ProfKind { kProfCompressKeys = 0, kProfCompressValues = 1, kProfPrepareQueries = 2, kProfAttention = 3,
+                kProfBackRotation = 4, kProfKinds = 5 };
+// Record a CUDA event on `stream` before / after a kernel launch when profiling is on.
+void prof_mark(int kind, bool is_end, cudaStream_t stream);
+struct ProfScope {
+  int kind;
+  cudaStream_t stream;
+  ProfScope(int k, cudaStream_t s) : kind(k), stream(s) { prof_mark(kind, false, stream); }
+  ~ProfScope() { prof_mark(kind, true, stream); }
+};
+
 // ---- device helpers -------------------------------------------------------------------
 
 template <typename T>

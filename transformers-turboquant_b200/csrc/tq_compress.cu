@@ -159,7 +159,10 @@ static int launch_compress(const CompressArgs& a, cudaStream_t stream) {
   const int per_sm = smem > 110 * 1024 ? 1 : 2;
   int grid = sm_count() * per_sm;
   if (grid > a.num_tiles) grid = a.num_tiles;
-  kern<<<grid, 16 * (D / 8), smem, stream>>>(a);
+  {
+    ProfScope prof(IS_KEY ? kProfCompressKeys : kProfCompressValues, stream);
+    kern<<<grid, 16 * (D / 8), smem, stream>>>(a);
+  }
   TQ_CUDA_OK(cudaGetLastError());
   return TQ_OK;
 }

@@ -26,6 +26,25 @@ int fail(tq_status st, const char* fmt, ...) {
   return st;
 }
 
+// ---- per-kernel timing ------------------------------------------------------------------
+namespace {
+struct ProfState {
+  bool on = false;
+  int cap = 0;
+  int used[kProfKinds] = {0, 0, 0, 0, 0};
+  cudaEvent_t* ev[kProfKinds] = {nullptr, nullptr, nullptr, nullptr, nullptr};  // 2*cap each: begin,end pairs
+};
+ProfState g_prof;
+}  // namespace
+
+void prof_mark(int kind, bool is_end, cudaStream_t stream) {
+  if (!g_prof.on) return;
+  int& n = g_prof.used[kind];
+  if (n >= g_prof.cap) return;
+  cudaEventRecord(g_prof.ev[kind][2 * n + (is_end ? 1 : 0)], stream);
+  if (is_end) ++n;
+}
+
 // ---- kernels ----------------------------------------------------------------------------
 
 // One thread per group of 8 fields.  groups_per_row = d/8.
@@ -159,6 +178,41 @@ int tq_device_fault_count(void* stream, int64_t* count_host) {
   if (int st = read_wait_faults(&v)) return st;
   *count_host = static_cast<int64_t>(v);
   return TQ_OK;
+}
+
+int tq_profile_begin(int max_records) {
+  TQ_REQUIRE(max_records > 0 && max_records <= 4096, "max_records %d outside 1..4096", max_records);
+  TQ_REQUIRE(!g_prof.on, "profiling already active");
+  for (int k = 0; k < kProfKinds; ++k) {
+    g_prof.ev[k] = new cudaEvent_t[2 * max_records];
+    for (int i = 0; i < 2 * max_records; ++i) TQ_CUDA_OK(cudaEventCreate(&g_prof.ev[k][i]));
+    g_prof.used[k] = 0;
+  }
+  g_prof.cap = max_records;
+  g_prof.on = true;
+  return TQ_OK;
+}
+
+int tq_profile_end(float* ms_sum, int* launches) {
+  TQ_REQUIRE(g_prof.on, "profiling is not active");
+  TQ_REQUIRE(ms_sum && launches, "NULL output pointer");
+  g_prof.on = false;
+  int rc = TQ_OK;
+  for (int k = 0; k < kProfKinds; ++k) {
+    ms_sum[k] = 0.f;
+    launches[k] = g_prof.used[k];
+    for (int i = 0; i < g_prof.used[k]; ++i) {
+      float ms = 0.f;
+      cudaError_t e = cudaEventSynchronize(g_prof.ev[k][2 * i + 1]);
+      if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, g_prof.ev[k][2 * i], g_prof.ev[k][2 * i + 1]);
+      if (e != cudaSuccess) rc = fail(TQ_ERR_CUDA, "event timing failed: %s", cudaGetErrorString(e));
+      ms_sum[k] += ms;
+    }
+    for (int i = 0; i < 2 * g_prof.cap; ++i) cudaEventDestroy(g_prof.ev[k][i]);
+    delete[] g_prof.ev[k];
+    g_prof.ev[k] = nullptr;
+  }
+  return rc;
 }
 
 int tq_pack_bits(const int32_t* indices, int64_t n, int d, int b, uint8_t* packed, void* stream) {
