@@ -1,0 +1,311 @@
+"""Benchmark of the TurboQuant hot path: fused KV compression + compressed causal attention.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--bits 3]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+Workload ("op_level_gqa4_s8192"): bf16 Q [4,32,8192,128], K,V [4,8,8192,128] drawn N(0,1)
+with 4 key channels per head scaled x8, rotation/QJL matrices from seed 42, causal, 3-bit by
+default.  One step = compress K, compress V, fused attention over the whole batch.  With N
+ranks every rank runs this workload on its own (batch x KV-head) shard, no data-path
+collective (weak scaling).  Inputs (402 MB) exceed the 126 MB L2, so no flush between
+steps.  Prints ONE JSON line on rank 0.
+
+`--impl reference` times the CPU restatement of the reference's PyTorch path (oracle/) on the
+host cores, on a bounded sample of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import math
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "transformers-turboquant_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+B, HQ, HKV, S, D = 4, 32, 8, 8192, 128
+METRIC = "fused_tq_attention_keys_per_s"
+UNIT = "keys/s"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--bits", type=int, default=3)
+    ap.add_argument("--seq", type=int, default=S, help="sequence length (default: the named workload)")
+    ap.add_argument("--batch", type=int, default=B)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def make_inputs(batch, seq, device, seed=0):
+    """Synthetic stand-in for the named op-level configuration."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    q = torch.randn(batch, HQ, seq, D, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    k = torch.randn(batch, HKV, seq, D, generator=g, device=device, dtype=torch.float32)
+    v = torch.randn(batch, HKV, seq, D, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    cg = torch.Generator().manual_seed(1)
+    for h in range(HKV):
+        ch = torch.randperm(D, generator=cg)[:4].to(device)
+        k[:, h, :, ch] *= 8.0
+    return q, k.to(torch.bfloat16), v
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop_evt = threading.Event()
+        self.ok = True
+
+    def run(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            names = {nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+                     nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+                     nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+                     nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
+                     nv.nvmlClocksThrottleReasonHwPowerBrakeSlowdown: "hw_power_brake"}
+            while not self._stop_evt.is_set():
+                self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                self.reasons.update(n for bit, n in names.items() if mask & bit)
+                time.sleep(0.01)
+        except Exception as exc:  # NVML missing: report, never fail the run
+            self.ok = False
+            self.error = repr(exc)
+
+    def finish(self):
+        self._stop_evt.set()
+        self.join(timeout=2)
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                    "note": getattr(self, "error", "no samples")}
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+def causal_pairs(batch, seq):
+    return batch * HQ * seq * (seq + 1) // 2
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"tflops": p.get("bf16_tflops_sustained", p.get("bf16_tflops")), "hbm_gbs": p.get("hbm_gbs"),
+                "source": "measured (MEASURED_PEAKS.json, sustained bf16)"}
+    return {"tflops": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+CPU_Q_ROWS = 1024  # query rows of the unit that the CPU sample actually evaluates
+
+
+def cpu_sample(bits, seq, repeats=1, threads=None):
+    """Reference PyTorch path (oracle restatement, literal arithmetic: compress of the
+    GQA-expanded K/V, full-width score rows, fp32 softmax, PV) on one (batch, query-head) unit
+    of the workload.  Compression is timed on all `seq` keys; the score/softmax/PV part on the
+    last CPU_Q_ROWS query rows against all keys and scaled by seq/CPU_Q_ROWS (the reference
+    computes every row at full width whatever the mask).  Returns seconds per unit."""
+    from oracle import tq_oracle as orc
+    threads = threads or os.cpu_count()
+    torch.set_num_threads(threads)
+    kp, vp = orc.make_key_params(D, bits, 42), orc.make_value_params(D, bits, 10042)
+    g = torch.Generator().manual_seed(0)
+    rows = min(CPU_Q_ROWS, seq)
+    q = torch.randn(1, 1, rows, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(1, 1, seq, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(1, 1, seq, D, generator=g).to(torch.bfloat16)
+    mask = orc.causal_mask(seq, seq)[-rows:]
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        ck, cv = orc.key_compress(k, kp), orc.value_compress(v, vp)
+        t1 = time.perf_counter()
+        sc = orc.scores_literal(q, ck, kp) / math.sqrt(D) + mask
+        w = torch.softmax(sc.float(), dim=-1).to(q.dtype)
+        _ = w @ orc.value_decompress(cv, vp).to(q.dtype)
+        t2 = time.perf_counter()
+        best = min(best, (t1 - t0) + (t2 - t1) * (seq / rows))
+    return best, threads
+
+
+def run_reference(args):
+    """The reference arm: CPU, rank 0 only."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    seq, batch = args.seq, args.batch
+    cpu_sample(args.bits, min(seq, 1024))  # warm the thread pool and allocator
+    for _ in range(max(args.warmup - 1, 0)):
+        cpu_sample(args.bits, seq)
+    per_unit = sum(cpu_sample(args.bits, seq)[0] for _ in range(args.steps)) / args.steps
+    units = batch * HQ  # the reference expands K/V to one copy per query head before compressing
+    step_s = per_unit * units
+    keys = batch * HKV * seq
+    value = keys / step_s
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "op_level_gqa4_s8192", "batch": batch, "q_heads": HQ, "kv_heads": HKV,
+                       "seq_len": seq, "head_dim": D, "bits": args.bits, "causal": True},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
+                             "sample": f"per step one (batch, query head) unit of {units}: compress of S={seq} keys and "
+                                       f"values, score/softmax/PV rows for {min(CPU_Q_ROWS, seq)} of {seq} queries "
+                                       "at full width, scaled to the unit and then linearly to the workload"},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import turboquant_b200 as tq
+    from turboquant_b200 import _lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    batch, seq, bits = args.batch, args.seq, args.bits
+    q, k, v = make_inputs(batch, seq, dev, seed=rank)  # every rank owns its own shard of units
+    kc = tq.TurboQuantCompressorV2(D, bits, 42, device=str(dev))
+    vc = tq.TurboQuantCompressorMSE(D, bits, 10042, device=str(dev))
+
+    def step(qd, kd, vd):
+        ck = kc.compress(kd)
+        cv = vc.compress(vd)
+        return tq.fused_attention(qd, ck, cv, kc, vc, causal=True)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(max(args.warmup, 3)):
+        out = step(q, k, v)
+    barrier()
+
+    sampler = ClockSampler(torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ else local)
+    sampler.start()
+    _lib.check(_lib.lib.tq_profile_begin(max(args.steps, 1)))
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        out = step(q, k, v)
+    ev1.record()
+    barrier()
+    ms_sum = (ctypes.c_float * 5)()
+    launches = (ctypes.c_int * 5)()
+    _lib.check(_lib.lib.tq_profile_end(ms_sum, launches))
+    clocks = sampler.finish()
+    elapsed_ms = ev0.elapsed_time(ev1)
+    t = torch.tensor([elapsed_ms], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    elapsed_ms = float(t.item())
+    ms_per_step = elapsed_ms / args.steps
+    keys_per_rank = batch * HKV * seq
+    value = keys_per_rank * world / (ms_per_step * 1e-3)
+
+    # ---- end to end through the public API with pinned host buffers -----------------------
+    e2e = None
+    if not args.no_e2e:
+        hq, hk, hv = (t_.cpu().pin_memory() for t_ in (q, k, v))
+        hout = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+        n_e2e = max(3, min(args.steps, 10))
+
+        def e2e_step():
+            dq, dk, dv = (h.to(dev, non_blocking=True) for h in (hq, hk, hv))
+            hout.copy_(step(dq, dk, dv), non_blocking=True)
+
+        e2e_step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        e1.record()
+        barrier()
+        te = torch.tensor([e0.elapsed_time(e1) / n_e2e], device=dev, dtype=torch.float64)
+        if dist is not None:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e2e = {"value": keys_per_rank * world / (float(te.item()) * 1e-3), "unit": UNIT,
+               "h2d_bytes_per_step": sum(h.numel() * h.element_size() for h in (hq, hk, hv)),
+               "d2h_bytes_per_step": hout.numel() * hout.element_size(), "ms_per_step": float(te.item()),
+               "steps": n_e2e}
+
+    faults = tq.device_fault_count(dev)
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    # ---- roofline of the dominant kernel (fused attention: tensor-core bound) ---------------
+    peaks = measured_peaks()
+    attn_ms = ms_sum[3] / max(launches[3], 1)
+    flops = 6.0 * D * causal_pairs(batch, seq)  # 2d (q.K_hat) + 2d (q_s.sign) + 2d (P.V_hat) per causal pair
+    achieved = flops / (attn_ms * 1e-3) / 1e12 if attn_ms > 0 else None
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                "frac": (achieved / peaks["tflops"]) if achieved else None, "traffic": None,
+                "kernel": "attention_tc_kernel", "ms_per_launch": attn_ms, "peak_source": peaks["source"],
+                "kernel_ms": {"compress_keys": ms_sum[0] / max(launches[0], 1),
+                              "compress_values": ms_sum[1] / max(launches[1], 1),
+                              "prepare_queries": ms_sum[2] / max(launches[2], 1),
+                              "attention": attn_ms, "back_rotation": ms_sum[4] / max(launches[4], 1)}}
+
+    cpu = None
+    if not args.no_cpu_baseline and world == 1:
+        cpu_sample(bits, 1024)
+        sec, threads = cpu_sample(bits, seq, repeats=2)
+        units = batch * HQ
+        cpu = {"value": batch * HKV * seq / (sec * units), "unit": UNIT, "cores": threads, "kind": "port",
+               "sample": f"one (batch, query head) unit of {units}: compress of S={seq} keys and values, "
+                         f"score/softmax/PV rows for {min(CPU_Q_ROWS, seq)} of {seq} queries at full width, scaled to "
+                         f"the unit ({sec:.2f} s) and then linearly to the workload; reference PyTorch path"}
+
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "op_level_gqa4_s8192", "batch_per_gpu": batch, "q_heads": HQ, "kv_heads": HKV,
+                       "seq_len": seq, "head_dim": D, "bits": bits, "causal": True,
+                       "l2": "inputs (402 MB per step) exceed the 126 MB L2; no flush",
+                       "causal_pairs_per_s": causal_pairs(batch, seq) * world / (ms_per_step * 1e-3)},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": int(sum(launches)) + 2 * args.steps,
+            "roofline": roofline, "cpu_baseline": cpu, "device_wait_faults": faults}
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
