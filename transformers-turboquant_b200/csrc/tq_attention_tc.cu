@@ -190,275 +190,387 @@ __global__ void __launch_bounds__(128) rows_gemm_tc_kernel(const RowsGemmArgs a)
   if (warp == 0) tc::tmem_dealloc(tmem, NOUT < 32 ? 32 : NOUT);
 }
 
-// ---- fused attention ---------------------------------------------------------------------
+// ---- fused attention (warp-specialised) ------------------------------------------------------
+//
+// One CTA = 128 query rows of one head.  Nine warps in three roles, coupled only by mbarriers:
+//   warps 0-3  softmax    thread r owns query row r (= tensor-memory lane r): loads its score row,
+//                         scales, masks, keeps the running max / sum, writes P as a bf16 operand
+//                         tile, rescales the output accumulator when the max grew, runs the epilogue
+//   warps 4-7  producers  prefetch the next tile's packed bytes into registers, stage them in shared
+//                         memory, decode indices / sign bits / norms into the K_hat and V_hat
+//                         operand tiles (canonical core-matrix layout)
+//   warp 8     MMA        one thread issues S = Q_cat K_hat^T for tile j+1, then O += P V_hat for tile j
+// Keys advance in tiles of 64.  K_hat, V_hat, P and the score accumulator S are double-buffered, so
+// the tensor pipe works on tile j+1 while the softmax warps handle tile j and the producers decode
+// tile j+2.
+//
+// Barriers (index = tile parity b = j & 1; "use" u = j >> 1 selects the mbarrier phase):
+//   kv_full[b]  128 producer arrivals : K_hat/V_hat/cscale of tile j ready
+//   s_full[b]   tcgen05.commit        : S[b] holds the scores of tile j
+//   s_empty[b]  128 softmax arrivals  : S[b] has been read into registers
+//   p_full[b]   128 softmax arrivals  : P[b] written (and O rescaled if needed)
+//   pv_done[b]  tcgen05.commit        : O += P V_hat of tile j finished (K_hat/V_hat/P of b free)
+//   q_full      128 softmax arrivals  : the Q tile is in shared memory
+//   pk_full[b]  128 producer arrivals : the packed bytes of tile j are staged in shared memory
 
-constexpr int kBM = 128;  // query rows per CTA
-constexpr int kBN = 128;  // keys per tile
+constexpr int kBM = 128;          // query rows per CTA
+constexpr int kBN = 64;           // keys per tile
+constexpr int kWsThreads = 288;   // 4 softmax + 4 producer + 1 MMA warp
 
-template <int D>
-struct AttnSmem {
-  static constexpr int G = D / 8;
+template <int D, int BITS>
+struct WsSmem {
+  static constexpr int G = D / 8, KB = BITS - 1, VB = BITS;
   static constexpr uint32_t kQBytes = kBM * 2 * D * 2;
-  static constexpr uint32_t kKBytes = kBN * 2 * D * 2;
-  static constexpr uint32_t kVBytes = kBN * D * 2;
-  static constexpr uint32_t kPBytes = kBM * kBN * 2;
+  static constexpr uint32_t kKStage = kBN * 2 * D * 2;
+  static constexpr uint32_t kVStage = kBN * D * 2;
+  static constexpr uint32_t kPStage = kBM * kBN * 2;
+  static constexpr uint32_t kIdxK = kBN * G * KB;     // packed key-index bytes per tile
+  static constexpr uint32_t kSgn = kBN * G;
+  static constexpr uint32_t kIdxV = kBN * G * VB;
+  static constexpr uint32_t kPkStage = kIdxK + kSgn + kIdxV;
   static constexpr uint32_t kQOff = 0;
   static constexpr uint32_t kKOff = kQOff + kQBytes;
-  static constexpr uint32_t kVOff = kKOff + kKBytes;
-  static constexpr uint32_t kPOff = kVOff + kVBytes;
-  static constexpr uint32_t kTotal = kPOff + kPBytes;
-  static constexpr uint32_t kSboQK = 2 * G * 128;   // K-major [rows, 2D]
-  static constexpr uint32_t kSboP = (kBN / 8) * 128;  // K-major [rows, kBN]
-  static constexpr uint32_t kSboV = 128;              // MN-major [D, kBN]: 8-coordinate chunks adjacent
-  static constexpr uint32_t kLboV = G * 128;          // ... 8-key groups G core matrices apart
+  static constexpr uint32_t kVOff = kKOff + 2 * kKStage;
+  static constexpr uint32_t kPOff = kVOff + 2 * kVStage;
+  static constexpr uint32_t kPkOff = kPOff + 2 * kPStage;
+  static constexpr uint32_t kTotal = kPkOff + 2 * kPkStage;
+  static constexpr uint32_t kSboQK = 2 * G * 128;       // K-major [rows, 2D]
+  static constexpr uint32_t kSboP = (kBN / 8) * 128;    // K-major [rows, kBN]
+  static constexpr uint32_t kSboV = 128;                // MN-major [D, kBN]: 8-coordinate chunks adjacent
+  static constexpr uint32_t kLboV = G * 128;            // ... 8-key groups G core matrices apart
 };
 
 template <int D, int BITS>
-__global__ void __launch_bounds__(256, 1) attention_tc_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot) {
-  using L = AttnSmem<D>;
-  constexpr int G = L::G, KB = BITS - 1, VB = BITS;
-  constexpr int kTmemCols = 256;  // S: columns [0,128), O: columns [128, 128+D)
+__global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot) {
+  using L = WsSmem<D, BITS>;
+  constexpr int G = L::G, KB = L::KB, VB = L::VB, GP = G / 2;
+  constexpr int kTmemCols = 256;  // S[0]: [0,64)  S[1]: [64,128)  O: [128, 128+D)
   constexpr float kLog2e = 1.4426950408889634f;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* Qs = smem_raw + L::kQOff;
-  uint8_t* Ks = smem_raw + L::kKOff;
-  uint8_t* Vs = smem_raw + L::kVOff;
-  uint8_t* Ps = smem_raw + L::kPOff;
-  __shared__ float cscale[kBN];
-  __shared__ float xmax[2][kBM];
+  __shared__ float cscale[2][kBN];     // n_k * sm_scale * log2(e) per key column
+  __shared__ float rho_s[2][kBN];      // rn_k / n_k
+  __shared__ float nv_s[2][kBN];       // value norms
   __shared__ uint32_t lutK[1 << (2 * KB)];
   __shared__ uint32_t lutV[1 << (2 * VB)];
-  __shared__ __align__(8) uint64_t bars[2];
+  __shared__ __align__(8) uint64_t bars[13];
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
+  volatile int* abort_flag = &s_abort;
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   if (tid == 0) s_abort = poisoned() ? 1 : 0;
   __syncthreads();
   if (s_abort) return;  // an earlier bounded wait expired: do nothing rather than risk another
+
   const int64_t b = blockIdx.z, h = blockIdx.y;
   const int64_t bh = b * a.Hq + h;
   const int64_t kv_base = (b * a.Hkv + h / (a.Hq / a.Hkv)) * a.Sk;
   // heaviest (latest) query tiles first: they have the most key tiles under the causal mask
   const int q0 = (int)(gridDim.x - 1 - blockIdx.x) * kBM;
   const int shift = (int)(a.Sk - a.Sq);
-
-  if (tid == 0) {
-    tc::mbar_init(tc::smem_u32(&bars[0]), 1);
-    tc::mbar_init(tc::smem_u32(&bars[1]), 1);
-    tc::fence_mbar_init();
-  }
-  if (warp == 0) tc::tmem_alloc(tc::smem_u32(&tmem_slot), kTmemCols);
-  for (int e = tid; e < (1 << (2 * KB)); e += 256) {
-    const float c0 = a.cen_k[e & ((1 << KB) - 1)], c1 = a.cen_k[e >> KB];
-    lutK[e] = tc::pack_bf16x2(c0, c1);
-  }
-  for (int e = tid; e < (1 << (2 * VB)); e += 256) {
-    const float c0 = a.cen_v[e & ((1 << VB) - 1)], c1 = a.cen_v[e >> VB];
-    lutV[e] = tc::pack_bf16x2(c0, c1);
-  }
-  {  // Q tile: thread t loads half of row t%128 (2G chunks per row)
-    const int r = tid % kBM, half = tid / kBM;
-    const bool live = q0 + r < a.Sq;
-    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.q_cat) +
-                                                      (bh * a.Sq + q0 + r) * 2 * D);
-    uint8_t* dst = Qs + (r / 8) * L::kSboQK + (r % 8) * 16;
-#pragma unroll 4
-    for (int c = half * G; c < (half + 1) * G; ++c) {
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (live) v = src[c];
-      *reinterpret_cast<uint4*>(dst + c * 128) = v;
-    }
-  }
-  tc::fence_async_smem();
-  tc::fence_before_sync();
-  __syncthreads();
-  tc::fence_after_sync();
-  const uint32_t tmem_s = tmem_slot;
-  const uint32_t tmem_o = tmem_s + kBN;
-  const uint32_t bar_s = tc::smem_u32(&bars[0]), bar_o = tc::smem_u32(&bars[1]);
-  constexpr uint32_t idesc_s = tc::idesc_bf16(kBM, kBN, false, false);
-  constexpr uint32_t idesc_o = tc::idesc_bf16(kBM, D, false, true);
-  const uint64_t qdesc = tc::smem_desc(tc::smem_u32(Qs), 128, L::kSboQK);
-  const uint64_t kdesc = tc::smem_desc(tc::smem_u32(Ks), 128, L::kSboQK);
-  const uint64_t pdesc = tc::smem_desc(tc::smem_u32(Ps), 128, L::kSboP);
-  const uint64_t vdesc = tc::smem_desc(tc::smem_u32(Vs), L::kLboV, L::kSboV);
-
-  // softmax ownership: row = tensor-memory lane; the two warp groups split the columns
-  const int row = (warp % 4) * 32 + lane;
-  const int chalf = warp / 4;
-  const uint32_t lane_base = (uint32_t)((warp % 4) * 32) << 16;
-  const int qi = q0 + row;
-  float m_run = -INFINITY, l_run = 0.f;
-  uint32_t phase_s = 0, phase_o = 0;
-
   int k_end = (int)a.Sk;
   if (a.causal) k_end = min(k_end, min(q0 + kBM - 1, (int)a.Sq - 1) + shift + 1);
   const int n_tiles = (k_end + kBN - 1) / kBN;
 
-  for (int kt = 0; kt < n_tiles; ++kt) {
-    const int k0 = kt * kBN;
-    // ---- (A) decode K_hat, V_hat tiles ---------------------------------------------------
-#pragma unroll 2
-    for (int e = tid; e < kBN * G; e += 256) {
-      const int j = (e % 8) + 8 * (e / (8 * G)), g = (e / 8) % G;
-      uint4 kw = make_uint4(0, 0, 0, 0), sw = kw, vw = kw;
-      if (k0 + j < a.Sk) {
-        const int64_t n = kv_base + k0 + j;
-        const uint64_t wk = load_fields8<KB>(a.key_idx + n * (D * KB / 8) + g * KB);
-        const uint32_t sb = ~static_cast<uint32_t>(a.key_sgn[n * G + g]);
-        const uint64_t wv = load_fields8<VB>(a.val_idx + n * (D * VB / 8) + g * VB);
-        const float nk = fp16_value(a.key_vn[n]);
-        const float rho = nk > 0.f ? fp16_value(a.key_rn[n]) / nk : 0.f;
-        const uint32_t rr = tc::pack_bf16x2(rho, rho);
-        const float nvf = fp16_value(a.val_vn[n]);
-        const __nv_bfloat162 nv2 = __floats2bfloat162_rn(nvf, nvf);
-        uint32_t kq[4], sq[4], vq[4];
-#pragma unroll
-        for (int p = 0; p < 4; ++p) {
-          kq[p] = lutK[(wk >> (2 * p * KB)) & ((1u << (2 * KB)) - 1)];
-          sq[p] = rr ^ (((sb >> (2 * p)) & 1u) << 15) ^ (((sb >> (2 * p + 1)) & 1u) << 31);
-          const uint32_t vv = lutV[(wv >> (2 * p * VB)) & ((1u << (2 * VB)) - 1)];
-          const __nv_bfloat162 prod = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&vv), nv2);
-          vq[p] = *reinterpret_cast<const uint32_t*>(&prod);
-        }
-        kw = make_uint4(kq[0], kq[1], kq[2], kq[3]);
-        sw = make_uint4(sq[0], sq[1], sq[2], sq[3]);
-        vw = make_uint4(vq[0], vq[1], vq[2], vq[3]);
+  const uint32_t bar0 = tc::smem_u32(&bars[0]);
+  auto kv_full = [&](int i) { return bar0 + 8u * i; };
+  auto s_full = [&](int i) { return bar0 + 8u * (2 + i); };
+  auto s_empty = [&](int i) { return bar0 + 8u * (4 + i); };
+  auto p_full = [&](int i) { return bar0 + 8u * (6 + i); };
+  auto pv_done = [&](int i) { return bar0 + 8u * (8 + i); };
+  const uint32_t q_full = bar0 + 8u * 10;
+  auto pk_full = [&](int i) { return bar0 + 8u * (11 + i); };
+
+  if (tid == 0) {
+    for (int i = 0; i < 2; ++i) {
+      tc::mbar_init(kv_full(i), 128);
+      tc::mbar_init(s_full(i), 1);
+      tc::mbar_init(s_empty(i), 128);
+      tc::mbar_init(p_full(i), 128);
+      tc::mbar_init(pv_done(i), 1);
+      tc::mbar_init(pk_full(i), 128);
+    }
+    tc::mbar_init(q_full, 128);
+    tc::fence_mbar_init();
+  }
+  if (warp == 8) tc::tmem_alloc(tc::smem_u32(&tmem_slot), kTmemCols);
+  for (int e = tid; e < (1 << (2 * KB)); e += kWsThreads)
+    lutK[e] = tc::pack_bf16x2(a.cen_k[e & ((1 << KB) - 1)], a.cen_k[e >> KB]);
+  for (int e = tid; e < (1 << (2 * VB)); e += kWsThreads)
+    lutV[e] = tc::pack_bf16x2(a.cen_v[e & ((1 << VB) - 1)], a.cen_v[e >> VB]);
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem_base = tmem_slot;
+  const uint32_t tmem_o = tmem_base + 2 * kBN;
+  bool ok = true;
+
+  if (warp < 4) {
+    // =============================== softmax warps ===============================
+    const int row = tid;
+    const int qi = q0 + row;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    {  // Q tile: row r, 2G chunks of 16 bytes
+      const bool live = qi < a.Sq;
+      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.q_cat) +
+                                                        (bh * a.Sq + qi) * 2 * D);
+      uint8_t* dst = Qs + (row / 8) * L::kSboQK + (row % 8) * 16;
+#pragma unroll 8
+      for (int c = 0; c < 2 * G; ++c) {
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (live) v = src[c];
+        *reinterpret_cast<uint4*>(dst + c * 128) = v;
       }
-      uint8_t* kd = Ks + (j / 8) * L::kSboQK + (j % 8) * 16;
-      *reinterpret_cast<uint4*>(kd + g * 128) = kw;
-      *reinterpret_cast<uint4*>(kd + (G + g) * 128) = sw;
-      *reinterpret_cast<uint4*>(Vs + g * L::kSboV + (j / 8) * L::kLboV + (j % 8) * 16) = vw;
+      tc::fence_async_smem();
+      tc::mbar_arrive(q_full);
     }
-    if (tid < kBN) {
-      const int k = k0 + tid;
-      cscale[tid] = k < a.Sk ? fp16_value(a.key_vn[kv_base + k]) * a.sm_scale * kLog2e : 0.f;
-    }
-    tc::fence_async_smem();
-    tc::fence_before_sync();
-    __syncthreads();
-    // ---- (B) S = Q_cat * K_hat^T ---------------------------------------------------------
-    if (tid == 0) {
+    float m_run = -INFINITY, l_run = 0.f;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int bb = j & 1, u = j >> 1, k0 = j * kBN;
+      if (!(ok = tc::mbar_wait_or_abort(s_full(bb), u & 1, abort_flag))) break;
       tc::fence_after_sync();
-#pragma unroll
-      for (int ks = 0; ks < 2 * D / 16; ++ks)
-        tc::mma_bf16(tmem_s, qdesc + (uint64_t)(ks * 256 >> 4), kdesc + (uint64_t)(ks * 256 >> 4), idesc_s, ks > 0);
-      tc::mma_commit(bar_s);
-    }
-    // ---- (C) online softmax ---------------------------------------------------------------
-    if (!tc::mbar_wait_bounded(bar_s, phase_s)) { record_fault(); s_abort = 1; }
-    phase_s ^= 1;
-    tc::fence_after_sync();
-    float t[64];
-    {
-      uint32_t raw[32];
-      tc::tmem_ld32(tmem_s + lane_base + chalf * 64, raw);
-      tc::wait_ld();
-#pragma unroll
-      for (int c = 0; c < 32; ++c) t[c] = __uint_as_float(raw[c]);
-      tc::tmem_ld32(tmem_s + lane_base + chalf * 64 + 32, raw);
-      tc::wait_ld();
-#pragma unroll
-      for (int c = 0; c < 32; ++c) t[32 + c] = __uint_as_float(raw[c]);
-    }
-    float mx = -INFINITY;
-    const float* mrow = (a.mask != nullptr && qi < a.Sq)
-                            ? a.mask + b * a.mask_stride_b + (int64_t)qi * a.mask_stride_q + k0 + chalf * 64
-                            : nullptr;
-#pragma unroll
-    for (int c = 0; c < 64; ++c) {
-      const int kc = chalf * 64 + c, k = k0 + kc;
-      float v = t[c] * cscale[kc];
-      if (mrow != nullptr && k < a.Sk) v = fmaf(mrow[c], kLog2e, v);
-      if (k >= a.Sk || (a.causal && k > qi + shift)) v = -INFINITY;
-      t[c] = v;
-      mx = fmaxf(mx, v);
-    }
-    xmax[chalf][row] = mx;
-    __syncthreads();
-    if (s_abort) break;
-    const float m_new = fmaxf(m_run, fmaxf(mx, xmax[1 - chalf][row]));
-    const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-    const float alpha = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_use);
-    m_run = m_new;
-    float psum = 0.f;
-    {
-      uint8_t* pd = Ps + (row / 8) * L::kSboP + (row % 8) * 16 + (chalf * 8) * 128;
-#pragma unroll
-      for (int c8 = 0; c8 < 8; ++c8) {
-        uint32_t w[4];
-#pragma unroll
-        for (int p = 0; p < 4; ++p) {
-          const float p0 = exp2f(t[c8 * 8 + 2 * p] - m_use), p1 = exp2f(t[c8 * 8 + 2 * p + 1] - m_use);
-          psum += p0 + p1;
-          w[p] = tc::pack_bf16x2(p0, p1);
-        }
-        *reinterpret_cast<uint4*>(pd + c8 * 128) = make_uint4(w[0], w[1], w[2], w[3]);
-      }
-    }
-    l_run = l_run * alpha + psum;
-    if (kt > 0) {  // rescale this warp group's half of the output accumulator
-#pragma unroll 1
-      for (int c0 = 0; c0 < D / 2; c0 += 32) {
+      float t[kBN];
+      {
         uint32_t raw[32];
-        const uint32_t addr = tmem_o + lane_base + chalf * (D / 2) + c0;
-        tc::tmem_ld32(addr, raw);
+        tc::tmem_ld32(tmem_base + lane_base + bb * kBN, raw);
         tc::wait_ld();
 #pragma unroll
-        for (int c = 0; c < 32; ++c) raw[c] = __float_as_uint(__uint_as_float(raw[c]) * alpha);
-        tc::tmem_st32(addr, raw);
+        for (int c = 0; c < 32; ++c) t[c] = __uint_as_float(raw[c]);
+        tc::tmem_ld32(tmem_base + lane_base + bb * kBN + 32, raw);
+        tc::wait_ld();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) t[32 + c] = __uint_as_float(raw[c]);
       }
-      tc::wait_st();
+      tc::fence_before_sync();
+      tc::mbar_arrive(s_empty(bb));
+      float mx = -INFINITY;
+      const bool edge = (k0 + kBN > a.Sk) || (a.causal && k0 + kBN - 1 > q0 + shift) || a.mask != nullptr;
+      if (!edge) {
+#pragma unroll
+        for (int c4 = 0; c4 < kBN; c4 += 4) {
+          const float4 cs = *reinterpret_cast<const float4*>(&cscale[bb][c4]);
+          t[c4] *= cs.x; t[c4 + 1] *= cs.y; t[c4 + 2] *= cs.z; t[c4 + 3] *= cs.w;
+          mx = fmaxf(mx, fmaxf(fmaxf(t[c4], t[c4 + 1]), fmaxf(t[c4 + 2], t[c4 + 3])));
+        }
+      } else {
+        const float* mrow = (a.mask != nullptr && qi < a.Sq)
+                                ? a.mask + b * a.mask_stride_b + (int64_t)qi * a.mask_stride_q + k0
+                                : nullptr;
+#pragma unroll
+        for (int c = 0; c < kBN; ++c) {
+          const int k = k0 + c;
+          float v = t[c] * cscale[bb][c];
+          if (mrow != nullptr && k < a.Sk) v = fmaf(mrow[c], kLog2e, v);
+          if (k >= a.Sk || (a.causal && k > qi + shift)) v = -INFINITY;
+          t[c] = v;
+          mx = fmaxf(mx, v);
+        }
+      }
+      // running max, raised lazily: rescaling O costs a tensor-memory round trip, so the max only
+      // moves when some row of the warp outgrew it by more than 2^8 (P stays below 256)
+      const float m_cand = fmaxf(m_run, mx);
+      const bool grow = __any_sync(0xffffffffu, m_cand > m_run + 8.f);
+      float alpha = 1.f;
+      if (grow) {
+        alpha = (m_run == -INFINITY) ? 0.f : tc::fast_exp2(m_run - m_cand);
+        m_run = m_cand;
+      }
+      const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
+      if (u >= 1 && !(ok = tc::mbar_wait_or_abort(pv_done(bb), (u - 1) & 1, abort_flag))) break;  // P[bb] free
+      float psum = 0.f;
+      {
+        uint8_t* pd = smem_raw + L::kPOff + bb * L::kPStage + (row / 8) * L::kSboP + (row % 8) * 16;
+#pragma unroll
+        for (int c8 = 0; c8 < kBN / 8; ++c8) {
+          uint32_t w[4];
+#pragma unroll
+          for (int p = 0; p < 4; ++p) {
+            const float p0 = tc::fast_exp2(t[c8 * 8 + 2 * p] - m_use);
+            const float p1 = tc::fast_exp2(t[c8 * 8 + 2 * p + 1] - m_use);
+            psum += p0 + p1;
+            w[p] = tc::pack_bf16x2(p0, p1);
+          }
+          *reinterpret_cast<uint4*>(pd + c8 * 128) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+      l_run = l_run * alpha + psum;
+      if (grow && j >= 1) {
+        // O must be at rest: wait for the previous tile's P V_hat
+        if (!(ok = tc::mbar_wait_or_abort(pv_done((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag))) break;
+        tc::fence_after_sync();
+#pragma unroll 1
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t raw[32];
+          tc::tmem_ld32(tmem_o + lane_base + c0, raw);
+          tc::wait_ld();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) raw[c] = __float_as_uint(__uint_as_float(raw[c]) * alpha);
+          tc::tmem_st32(tmem_o + lane_base + c0, raw);
+        }
+        tc::wait_st();
+      }
+      tc::fence_async_smem();
+      tc::fence_before_sync();
+      tc::mbar_arrive(p_full(bb));
     }
-    tc::fence_async_smem();
-    tc::fence_before_sync();
-    __syncthreads();
-    // ---- (D) O += P * V_hat -----------------------------------------------------------------
-    if (tid == 0) {
+    // ---- epilogue: normalise and store the rotated output row ----
+    if (ok && n_tiles > 0)
+      ok = tc::mbar_wait_or_abort(pv_done((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, abort_flag);
+    if (ok) {
       tc::fence_after_sync();
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      __nv_bfloat16* dst = o_rot + (bh * a.Sq + qi) * D;
+#pragma unroll 1
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t raw[32];
+        tc::tmem_ld32(tmem_o + lane_base + c0, raw);
+        tc::wait_ld();
+        if (qi < a.Sq) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 w;
+            w.x = tc::pack_bf16x2(__uint_as_float(raw[8 * i]) * inv, __uint_as_float(raw[8 * i + 1]) * inv);
+            w.y = tc::pack_bf16x2(__uint_as_float(raw[8 * i + 2]) * inv, __uint_as_float(raw[8 * i + 3]) * inv);
+            w.z = tc::pack_bf16x2(__uint_as_float(raw[8 * i + 4]) * inv, __uint_as_float(raw[8 * i + 5]) * inv);
+            w.w = tc::pack_bf16x2(__uint_as_float(raw[8 * i + 6]) * inv, __uint_as_float(raw[8 * i + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c0 + 8 * i) = w;
+          }
+        }
+      }
+    }
+  } else if (warp < 8) {
+    // =============================== producer warps ===============================
+    const int p = tid - 128;
+    constexpr int UK = L::kIdxK / 8, US = L::kSgn / 8, UV = L::kIdxV / 8;  // 8-byte units per tile
+    constexpr int NK = (UK + 127) / 128, NV = (UV + 127) / 128;
+    uint2 rk[NK], rv[NV], rs;
+    uint32_t rn[3];
+    const uint8_t* gk = a.key_idx + kv_base * (G * KB);
+    const uint8_t* gs = a.key_sgn + kv_base * G;
+    const uint8_t* gv = a.val_idx + kv_base * (G * VB);
+    auto prefetch = [&](int k0) {
+      const uint2 zero = make_uint2(0, 0);
+#pragma unroll
+      for (int i = 0; i < NK; ++i) {
+        const int un = i * 128 + p;
+        rk[i] = (un < UK && k0 + (un * 8) / (G * KB) < a.Sk)
+                    ? *reinterpret_cast<const uint2*>(gk + (int64_t)k0 * (G * KB) + un * 8) : zero;
+      }
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int un = i * 128 + p;
+        rv[i] = (un < UV && k0 + (un * 8) / (G * VB) < a.Sk)
+                    ? *reinterpret_cast<const uint2*>(gv + (int64_t)k0 * (G * VB) + un * 8) : zero;
+      }
+      rs = (p < US && k0 + (p * 8) / G < a.Sk) ? *reinterpret_cast<const uint2*>(gs + (int64_t)k0 * G + p * 8) : zero;
+      if (p < kBN) {
+        const bool live = k0 + p < a.Sk;
+        rn[0] = live ? a.key_vn[kv_base + k0 + p] : 0;
+        rn[1] = live ? a.key_rn[kv_base + k0 + p] : 0;
+        rn[2] = live ? a.val_vn[kv_base + k0 + p] : 0;
+      }
+    };
+    if (n_tiles > 0) prefetch(0);
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int bb = j & 1, u = j >> 1;
+      uint8_t* pk = smem_raw + L::kPkOff + bb * L::kPkStage;
+      // K_hat/V_hat/cscale of parity bb are free once tile j-2's P V_hat has drained
+      if (u >= 1 && !(ok = tc::mbar_wait_or_abort(pv_done(bb), (u - 1) & 1, abort_flag))) break;
+#pragma unroll
+      for (int i = 0; i < NK; ++i)
+        if (i * 128 + p < UK) *reinterpret_cast<uint2*>(pk + (i * 128 + p) * 8) = rk[i];
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+        if (i * 128 + p < UV) *reinterpret_cast<uint2*>(pk + L::kIdxK + L::kSgn + (i * 128 + p) * 8) = rv[i];
+      if (p < US) *reinterpret_cast<uint2*>(pk + L::kIdxK + p * 8) = rs;
+      if (p < kBN) {
+        const float nk = fp16_value((uint16_t)rn[0]);
+        cscale[bb][p] = nk * a.sm_scale * kLog2e;
+        rho_s[bb][p] = nk > 0.f ? fp16_value((uint16_t)rn[1]) / nk : 0.f;
+        nv_s[bb][p] = fp16_value((uint16_t)rn[2]);
+      }
+      // every producer's staged bytes must be visible before anyone decodes (a bounded wait
+      // instead of bar.sync, so that a fault elsewhere cannot strand part of the group)
+      tc::mbar_arrive(pk_full(bb));
+      if (!(ok = tc::mbar_wait_or_abort(pk_full(bb), u & 1, abort_flag))) break;
+      if (j + 1 < n_tiles) prefetch((j + 1) * kBN);  // in flight while this tile is decoded
+      uint8_t* Kd = smem_raw + L::kKOff + bb * L::kKStage;
+      uint8_t* Vd = smem_raw + L::kVOff + bb * L::kVStage;
+#pragma unroll 2
+      for (int e = p; e < kBN * GP; e += 128) {
+        const int key = (e % 8) + 8 * (e / (8 * GP)), gp = (e / 8) % GP;
+        const uint16_t* sk = reinterpret_cast<const uint16_t*>(pk + key * (G * KB) + gp * 2 * KB);
+        const uint16_t* sv = reinterpret_cast<const uint16_t*>(pk + L::kIdxK + L::kSgn + key * (G * VB) + gp * 2 * VB);
+        uint64_t wk = 0, wv = 0;
+#pragma unroll
+        for (int i = 0; i < KB; ++i) wk |= (uint64_t)sk[i] << (16 * i);
+#pragma unroll
+        for (int i = 0; i < VB; ++i) wv |= (uint64_t)sv[i] << (16 * i);
+        const uint32_t sb = ~(uint32_t)*reinterpret_cast<const uint16_t*>(pk + L::kIdxK + key * G + gp * 2);
+        const float rho = rho_s[bb][key], nvf = nv_s[bb][key];
+        const uint32_t rr = tc::pack_bf16x2(rho, rho);
+        const __nv_bfloat162 nv2 = __floats2bfloat162_rn(nvf, nvf);
+        uint32_t kq[8], sq[8], vq[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          kq[q] = lutK[(uint32_t)(wk >> (2 * q * KB)) & ((1u << (2 * KB)) - 1)];
+          sq[q] = rr ^ (((sb >> (2 * q)) & 1u) << 15) ^ (((sb >> (2 * q + 1)) & 1u) << 31);
+          const uint32_t vv = lutV[(uint32_t)(wv >> (2 * q * VB)) & ((1u << (2 * VB)) - 1)];
+          const __nv_bfloat162 prod = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&vv), nv2);
+          vq[q] = *reinterpret_cast<const uint32_t*>(&prod);
+        }
+        uint8_t* kd = Kd + (key / 8) * L::kSboQK + (key % 8) * 16;
+        uint8_t* vd = Vd + (key / 8) * L::kLboV + (key % 8) * 16;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int g = 2 * gp + half;
+          *reinterpret_cast<uint4*>(kd + g * 128) = make_uint4(kq[4 * half], kq[4 * half + 1], kq[4 * half + 2], kq[4 * half + 3]);
+          *reinterpret_cast<uint4*>(kd + (G + g) * 128) = make_uint4(sq[4 * half], sq[4 * half + 1], sq[4 * half + 2], sq[4 * half + 3]);
+          *reinterpret_cast<uint4*>(vd + g * L::kSboV) = make_uint4(vq[4 * half], vq[4 * half + 1], vq[4 * half + 2], vq[4 * half + 3]);
+        }
+      }
+      tc::fence_async_smem();
+      tc::mbar_arrive(kv_full(bb));
+    }
+  } else if (lane == 0) {
+    // =============================== MMA issuer ===============================
+    constexpr uint32_t idesc_s = tc::idesc_bf16(kBM, kBN, false, false);
+    constexpr uint32_t idesc_o = tc::idesc_bf16(kBM, D, false, true);
+    const uint64_t qdesc = tc::smem_desc(tc::smem_u32(Qs), 128, L::kSboQK);
+    auto issue_scores = [&](int j) -> bool {
+      const int bb = j & 1, u = j >> 1;
+      if (!tc::mbar_wait_or_abort(kv_full(bb), u & 1, abort_flag)) return false;
+      if (u >= 1 && !tc::mbar_wait_or_abort(s_empty(bb), (u - 1) & 1, abort_flag)) return false;
+      tc::fence_after_sync();
+      const uint64_t kdesc = tc::smem_desc(tc::smem_u32(smem_raw + L::kKOff + bb * L::kKStage), 128, L::kSboQK);
+#pragma unroll
+      for (int ks = 0; ks < 2 * D / 16; ++ks)
+        tc::mma_bf16(tmem_base + bb * kBN, qdesc + (uint64_t)(ks * 256 >> 4), kdesc + (uint64_t)(ks * 256 >> 4),
+                     idesc_s, ks > 0);
+      tc::mma_commit(s_full(bb));
+      return true;
+    };
+    ok = tc::mbar_wait_or_abort(q_full, 0, abort_flag);
+    if (ok && n_tiles > 0) ok = issue_scores(0);
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int bb = j & 1, u = j >> 1;
+      if (j + 1 < n_tiles && !(ok = issue_scores(j + 1))) break;
+      if (!(ok = tc::mbar_wait_or_abort(p_full(bb), u & 1, abort_flag))) break;
+      tc::fence_after_sync();
+      const uint64_t pdesc = tc::smem_desc(tc::smem_u32(smem_raw + L::kPOff + bb * L::kPStage), 128, L::kSboP);
+      const uint64_t vdesc = tc::smem_desc(tc::smem_u32(smem_raw + L::kVOff + bb * L::kVStage), L::kLboV, L::kSboV);
 #pragma unroll
       for (int ks = 0; ks < kBN / 16; ++ks)
         tc::mma_bf16(tmem_o, pdesc + (uint64_t)(ks * 256 >> 4), vdesc + (uint64_t)(ks * 2 * L::kLboV >> 4), idesc_o,
-                     (kt > 0 || ks > 0) ? 1u : 0u);
-      tc::mma_commit(bar_o);
-    }
-    // ---- (E) operands and accumulator are free again once the MMA has drained -----------------
-    if (!tc::mbar_wait_bounded(bar_o, phase_o)) { record_fault(); s_abort = 1; }
-    phase_o ^= 1;
-    tc::fence_after_sync();
-    __syncthreads();
-    if (s_abort) break;
-  }
-
-  // ---- epilogue: normalise and store the rotated output tile ------------------------------------
-  if (!s_abort) {
-    xmax[chalf][row] = l_run;
-    __syncthreads();
-    const float l_tot = l_run + xmax[1 - chalf][row];
-    const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-    __nv_bfloat16* dst = o_rot + (bh * a.Sq + qi) * D + chalf * (D / 2);
-#pragma unroll 1
-    for (int c0 = 0; c0 < D / 2; c0 += 32) {
-      uint32_t raw[32];
-      tc::tmem_ld32(tmem_o + lane_base + chalf * (D / 2) + c0, raw);
-      tc::wait_ld();
-      if (qi < a.Sq) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint4 w;
-          w.x = tc::pack_bf16x2(__uint_as_float(raw[8 * i]) * inv, __uint_as_float(raw[8 * i + 1]) * inv);
-          w.y = tc::pack_bf16x2(__uint_as_float(raw[8 * i + 2]) * inv, __uint_as_float(raw[8 * i + 3]) * inv);
-          w.z = tc::pack_bf16x2(__uint_as_float(raw[8 * i + 4]) * inv, __uint_as_float(raw[8 * i + 5]) * inv);
-          w.w = tc::pack_bf16x2(__uint_as_float(raw[8 * i + 6]) * inv, __uint_as_float(raw[8 * i + 7]) * inv);
-          *reinterpret_cast<uint4*>(dst + c0 + 8 * i) = w;
-        }
-      }
+                     (j > 0 || ks > 0) ? 1u : 0u);
+      tc::mma_commit(pv_done(bb));
     }
   }
+  if (!ok && atomicExch(&s_abort, 2) != 2) record_fault();  // one fault per CTA
   tc::fence_before_sync();
   __syncthreads();
-  if (warp == 0) tc::tmem_dealloc(tmem_s, kTmemCols);
+  if (warp == 8) tc::tmem_dealloc(tmem_base, kTmemCols);
 }
 
 // ---- host side ---------------------------------------------------------------------------
@@ -477,13 +589,13 @@ static int launch_rows_gemm(const RowsGemmArgs& a, cudaStream_t stream) {
 
 template <int D, int BITS>
 static int launch_attention_tc(const AttnArgs& a, int64_t B, __nv_bfloat16* o_rot, cudaStream_t stream) {
-  constexpr size_t smem = AttnSmem<D>::kTotal;
-  auto kern = attention_tc_kernel<D, BITS>;
+  constexpr size_t smem = WsSmem<D, BITS>::kTotal;
+  auto kern = attention_ws_kernel<D, BITS>;
   TQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid((unsigned)((a.Sq + kBM - 1) / kBM), (unsigned)a.Hq, (unsigned)B);
   {
     ProfScope prof(kProfAttention, stream);
-    kern<<<grid, 256, smem, stream>>>(a, o_rot);
+    kern<<<grid, kWsThreads, smem, stream>>>(a, o_rot);
   }
   TQ_CUDA_OK(cudaGetLastError());
   return TQ_OK;

@@ -66,6 +66,37 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   return true;
 }
 
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// As mbar_wait_bounded, but also gives up as soon as another thread of the CTA has raised
+// `*abort_flag` (shared memory), and raises it itself on expiry.
+__device__ __forceinline__ bool mbar_wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                   long long limit = 400000000ll) {
+  if (mbar_test(bar, parity)) return true;
+  const long long t0 = clock64();
+  int spins = 0;
+  while (!mbar_test(bar, parity)) {
+    if ((++spins & 63) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > limit) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+// Named barrier among `nthreads` threads (ids 1..15; 0 is __syncthreads).
+__device__ __forceinline__ void named_barrier(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // ---- proxies and ordering ----------------------------------------------------------------
 
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
