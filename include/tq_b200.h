@@ -75,6 +75,15 @@ enum {
 int tq_profile_begin(int max_records);
 int tq_profile_end(float* ms_sum_host, int* launches_host);
 
+/* Pipeline trace of the tensor-core attention kernel (diagnostics; no counterpart in the
+ * reference).  While enabled, the CTA that handles the last query tile of (batch 0, head 0)
+ * appends (tag, SM clock) pairs at each stage boundary of its softmax, producer and MMA
+ * roles: tag = role << 32 | event << 16 | key tile.  tq_trace_read synchronises the device
+ * and copies the first max_records slots of the 4096-slot buffer (2 int64 each; each role owns
+ * one third of the slots, unused slots carry tag -1) to the host. */
+int tq_trace_enable(int on);
+int tq_trace_read(int64_t* records_host, int max_records, int* n_host);
+
 /* ---- wire-format primitives (test hooks and standalone operators) ------------- */
 
 /* int32 [n, d] -> packed [n, ceil(d*b/8)], 1 <= b <= 8, d*b a multiple of 8.

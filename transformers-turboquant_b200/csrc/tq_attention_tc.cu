@@ -30,6 +30,23 @@ int read_wait_faults(unsigned long long* out) {
   return TQ_OK;
 }
 
+// Diagnostics: stage timestamps (SM clock) of one CTA of the attention kernel, see tq_trace_read.
+constexpr int kTraceCap = 4096;
+__device__ int g_trace_on = 0;
+__device__ long long g_trace[2 * kTraceCap];
+// One tracer per traced thread: role r appends to its own third of the buffer, no atomics.
+struct Tracer {
+  bool on;
+  int role, n;
+  __device__ Tracer(bool on_, int role_) : on(on_), role(role_), n(0) {}
+  __device__ __forceinline__ void mark(int ev, int tile) {
+    if (!on || n >= kTraceCap / 3) return;
+    const int i = role * (kTraceCap / 3) + n++;
+    g_trace[2 * i] = ((long long)role << 32) | ((long long)ev << 16) | (long long)tile;
+    g_trace[2 * i + 1] = clock64();
+  }
+};
+
 __device__ __forceinline__ bool poisoned() {
   return *reinterpret_cast<volatile unsigned long long*>(&g_wait_faults) != 0ull;
 }
@@ -192,68 +209,82 @@ __global__ void __launch_bounds__(128) rows_gemm_tc_kernel(const RowsGemmArgs a)
 
 // ---- fused attention (warp-specialised) ------------------------------------------------------
 //
-// One CTA = 128 query rows of one head.  Nine warps in three roles, coupled only by mbarriers:
-//   warps 0-3  softmax    thread r owns query row r (= tensor-memory lane r): loads its score row,
-//                         scales, masks, keeps the running max / sum, writes P as a bf16 operand
-//                         tile, rescales the output accumulator when the max grew, runs the epilogue
-//   warps 4-7  producers  prefetch the next tile's packed bytes into registers, stage them in shared
-//                         memory, decode indices / sign bits / norms into the K_hat and V_hat
-//                         operand tiles (canonical core-matrix layout)
-//   warp 8     MMA        one thread issues S = Q_cat K_hat^T for tile j+1, then O += P V_hat for tile j
-// Keys advance in tiles of 64.  K_hat, V_hat, P and the score accumulator S are double-buffered, so
-// the tensor pipe works on tile j+1 while the softmax warps handle tile j and the producers decode
-// tile j+2.
+// One CTA = 128 query rows of one head.  Seventeen warps in three roles, coupled only by mbarriers:
+//   warps 0-7   softmax    two threads per query row (= tensor-memory lane): warp w and w+4 share the
+//                          rows of lane quadrant w%4 and split each 64-key tile into two 32-column
+//                          halves.  Load the scores, scale, mask, exchange the half-row maxima, keep
+//                          the running max / sum, write P (bf16) into tensor memory, rescale the output
+//                          accumulator when the max grew, run the epilogue.
+//   warps 8-15  producers  prefetch the next tile's packed bytes into registers, stage them in shared
+//                          memory, decode indices / sign bits / norms into the K_hat and V_hat
+//                          operand tiles (canonical core-matrix layout), up to kStages tiles ahead
+//   warp 16     MMA        one thread issues S = Q_cat K_hat^T for tile j+1, then O += P V_hat for tile j
+// Both A operands (the query tile and P) live in TENSOR MEMORY: shared-memory bandwidth, the scarcest
+// resource of this kernel, is spent only on the decoded K_hat / V_hat tiles.
+// Keys advance in tiles of 64.  S and P are double-buffered (index = tile parity), K_hat / V_hat /
+// staged bytes form a ring of kStages slots (index = tile % kStages).
 //
-// Barriers (index = tile parity b = j & 1; "use" u = j >> 1 selects the mbarrier phase):
-//   kv_full[b]  128 producer arrivals : K_hat/V_hat/cscale of tile j ready
+// Barriers ("use" = how often the slot has been used before selects the mbarrier phase):
+//   pk_full[s]  256 producer arrivals : the packed bytes of tile j are staged in shared memory
+//   k_full[s]   256 producer arrivals : K_hat and the column scales of tile j are ready
+//   v_full[s]   256 producer arrivals : V_hat of tile j is ready
+//   k_empty[s]  tcgen05.commit        : the score MMA of tile j has consumed K_hat[s]
+//   v_empty[s]  tcgen05.commit        : the P V_hat MMA of tile j has consumed V_hat[s]
 //   s_full[b]   tcgen05.commit        : S[b] holds the scores of tile j
-//   s_empty[b]  128 softmax arrivals  : S[b] has been read into registers
-//   p_full[b]   128 softmax arrivals  : P[b] written (and O rescaled if needed)
-//   pv_done[b]  tcgen05.commit        : O += P V_hat of tile j finished (K_hat/V_hat/P of b free)
-//   q_full      128 softmax arrivals  : the Q tile is in shared memory
-//   pk_full[b]  128 producer arrivals : the packed bytes of tile j are staged in shared memory
+//   s_empty[b]  256 softmax arrivals  : S[b] has been read into registers
+//   p_full[b]   256 softmax arrivals  : P[b] written (and O rescaled if needed)
+//   pv_done[b]  tcgen05.commit        : O += P V_hat of tile j finished (P[b] free, O at rest)
+//   q_full      256 softmax arrivals  : the query tile is in tensor memory
+//   xch[q]      64 arrivals           : the two warps of lane quadrant q exchanged their half-row maxima
 
 constexpr int kBM = 128;          // query rows per CTA
 constexpr int kBN = 64;           // keys per tile
-constexpr int kWsThreads = 288;   // 4 softmax + 4 producer + 1 MMA warp
+constexpr int kStages = 3;        // K_hat / V_hat ring depth
+constexpr int kSoftmaxThreads = 256;
+constexpr int kProducers = 256;
+constexpr int kWsThreads = kSoftmaxThreads + kProducers + 32;
+constexpr int kMmaWarp = kWsThreads / 32 - 1;
 
 template <int D, int BITS>
 struct WsSmem {
   static constexpr int G = D / 8, KB = BITS - 1, VB = BITS;
-  static constexpr uint32_t kQBytes = kBM * 2 * D * 2;
   static constexpr uint32_t kKStage = kBN * 2 * D * 2;
   static constexpr uint32_t kVStage = kBN * D * 2;
-  static constexpr uint32_t kPStage = kBM * kBN * 2;
   static constexpr uint32_t kIdxK = kBN * G * KB;     // packed key-index bytes per tile
   static constexpr uint32_t kSgn = kBN * G;
   static constexpr uint32_t kIdxV = kBN * G * VB;
   static constexpr uint32_t kPkStage = kIdxK + kSgn + kIdxV;
-  static constexpr uint32_t kQOff = 0;
-  static constexpr uint32_t kKOff = kQOff + kQBytes;
-  static constexpr uint32_t kVOff = kKOff + 2 * kKStage;
-  static constexpr uint32_t kPOff = kVOff + 2 * kVStage;
-  static constexpr uint32_t kPkOff = kPOff + 2 * kPStage;
-  static constexpr uint32_t kTotal = kPkOff + 2 * kPkStage;
-  static constexpr uint32_t kSboQK = 2 * G * 128;       // K-major [rows, 2D]
-  static constexpr uint32_t kSboP = (kBN / 8) * 128;    // K-major [rows, kBN]
+  static constexpr uint32_t kKOff = 0;
+  static constexpr uint32_t kVOff = kKOff + kStages * kKStage;
+  static constexpr uint32_t kPkOff = kVOff + kStages * kVStage;
+  static constexpr uint32_t kTotal = kPkOff + kStages * kPkStage;
+  static constexpr uint32_t kSboK = 2 * G * 128;        // K-major [keys, 2D]
   static constexpr uint32_t kSboV = 128;                // MN-major [D, kBN]: 8-coordinate chunks adjacent
   static constexpr uint32_t kLboV = G * 128;            // ... 8-key groups G core matrices apart
+  // tensor-memory columns
+  static constexpr uint32_t kColS = 0;                  // S[2]: 2 x 64
+  static constexpr uint32_t kColO = 128;                // O: D
+  static constexpr uint32_t kColQ = 256;                // Q_cat: 2D bf16 = D columns
+  static constexpr uint32_t kColP = 384;                // P[2]: 2 x 32 (64 bf16 each)
+  static constexpr uint32_t kCols = 512;
 };
 
 template <int D, int BITS>
 __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot) {
   using L = WsSmem<D, BITS>;
   constexpr int G = L::G, KB = L::KB, VB = L::VB, GP = G / 2;
-  constexpr int kTmemCols = 256;  // S[0]: [0,64)  S[1]: [64,128)  O: [128, 128+D)
+  constexpr int HC = kBN / 2;     // score columns per softmax thread
   constexpr float kLog2e = 1.4426950408889634f;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  uint8_t* Qs = smem_raw + L::kQOff;
-  __shared__ float cscale[2][kBN];     // n_k * sm_scale * log2(e) per key column
-  __shared__ float rho_s[2][kBN];      // rn_k / n_k
-  __shared__ float nv_s[2][kBN];       // value norms
+  // n_k * sm_scale * log2(e) per key column.  Written by the producers up to kStages tiles ahead of the score
+  // MMA and read by the softmax warps up to two tiles behind it: 8 slots (tile & 7) can never collide.
+  __shared__ float cscale[8][kBN];
+  __shared__ float rho_s[kStages][kBN];   // rn_k / n_k
+  __shared__ float nv_s[kStages][kBN];    // value norms
+  __shared__ float xmax[2][2][kBM];       // [tile parity][column half][row]: half-row maxima / sums exchanged
   __shared__ uint32_t lutK[1 << (2 * KB)];
   __shared__ uint32_t lutV[1 << (2 * VB)];
-  __shared__ __align__(8) uint64_t bars[13];
+  __shared__ __align__(8) uint64_t bars[5 * kStages + 8 + 4 + 1];
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
   volatile int* abort_flag = &s_abort;
@@ -274,27 +305,37 @@ __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnA
   const int n_tiles = (k_end + kBN - 1) / kBN;
 
   const uint32_t bar0 = tc::smem_u32(&bars[0]);
-  auto kv_full = [&](int i) { return bar0 + 8u * i; };
-  auto s_full = [&](int i) { return bar0 + 8u * (2 + i); };
-  auto s_empty = [&](int i) { return bar0 + 8u * (4 + i); };
-  auto p_full = [&](int i) { return bar0 + 8u * (6 + i); };
-  auto pv_done = [&](int i) { return bar0 + 8u * (8 + i); };
-  const uint32_t q_full = bar0 + 8u * 10;
-  auto pk_full = [&](int i) { return bar0 + 8u * (11 + i); };
+  auto k_full = [&](int i) { return bar0 + 8u * i; };
+  auto v_full = [&](int i) { return bar0 + 8u * (kStages + i); };
+  auto k_empty = [&](int i) { return bar0 + 8u * (2 * kStages + i); };
+  auto v_empty = [&](int i) { return bar0 + 8u * (3 * kStages + i); };
+  auto pk_full = [&](int i) { return bar0 + 8u * (4 * kStages + i); };
+  auto s_full = [&](int i) { return bar0 + 8u * (5 * kStages + i); };
+  auto s_empty = [&](int i) { return bar0 + 8u * (5 * kStages + 2 + i); };
+  auto p_full = [&](int i) { return bar0 + 8u * (5 * kStages + 4 + i); };
+  auto pv_done = [&](int i) { return bar0 + 8u * (5 * kStages + 6 + i); };
+  auto xch = [&](int i) { return bar0 + 8u * (5 * kStages + 8 + i); };
+  const uint32_t q_full = bar0 + 8u * (5 * kStages + 12);
 
   if (tid == 0) {
-    for (int i = 0; i < 2; ++i) {
-      tc::mbar_init(kv_full(i), 128);
-      tc::mbar_init(s_full(i), 1);
-      tc::mbar_init(s_empty(i), 128);
-      tc::mbar_init(p_full(i), 128);
-      tc::mbar_init(pv_done(i), 1);
-      tc::mbar_init(pk_full(i), 128);
+    for (int i = 0; i < kStages; ++i) {
+      tc::mbar_init(k_full(i), kProducers);
+      tc::mbar_init(v_full(i), kProducers);
+      tc::mbar_init(k_empty(i), 1);
+      tc::mbar_init(v_empty(i), 1);
+      tc::mbar_init(pk_full(i), kProducers);
     }
-    tc::mbar_init(q_full, 128);
+    for (int i = 0; i < 2; ++i) {
+      tc::mbar_init(s_full(i), 1);
+      tc::mbar_init(s_empty(i), kSoftmaxThreads);
+      tc::mbar_init(p_full(i), kSoftmaxThreads);
+      tc::mbar_init(pv_done(i), 1);
+    }
+    for (int i = 0; i < 4; ++i) tc::mbar_init(xch(i), 64);
+    tc::mbar_init(q_full, kSoftmaxThreads);
     tc::fence_mbar_init();
   }
-  if (warp == 8) tc::tmem_alloc(tc::smem_u32(&tmem_slot), kTmemCols);
+  if (warp == kMmaWarp) tc::tmem_alloc(tc::smem_u32(&tmem_slot), L::kCols);
   for (int e = tid; e < (1 << (2 * KB)); e += kWsThreads)
     lutK[e] = tc::pack_bf16x2(a.cen_k[e & ((1 << KB) - 1)], a.cen_k[e >> KB]);
   for (int e = tid; e < (1 << (2 * VB)); e += kWsThreads)
@@ -303,128 +344,147 @@ __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnA
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t tmem_base = tmem_slot;
-  const uint32_t tmem_o = tmem_base + 2 * kBN;
+  const uint32_t tmem_o = tmem_base + L::kColO;
   bool ok = true;
+  Tracer tr(g_trace_on != 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 &&
+                (warp == 0 || warp == 8 || warp == kMmaWarp),
+            warp == 0 ? 0 : warp == 8 ? 1 : 2);
 
-  if (warp < 4) {
+  if (warp < 8) {
     // =============================== softmax warps ===============================
-    const int row = tid;
+    const int quad = warp % 4, chalf = warp / 4;
+    const int row = quad * 32 + lane;
     const int qi = q0 + row;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    {  // Q tile: row r, 2G chunks of 16 bytes
+    const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+    {  // query row -> tensor memory: 2D bf16 = D columns, each of the row's two threads stores D/2
       const bool live = qi < a.Sq;
       const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.q_cat) +
-                                                        (bh * a.Sq + qi) * 2 * D);
-      uint8_t* dst = Qs + (row / 8) * L::kSboQK + (row % 8) * 16;
-#pragma unroll 8
-      for (int c = 0; c < 2 * G; ++c) {
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (live) v = src[c];
-        *reinterpret_cast<uint4*>(dst + c * 128) = v;
+                                                        (bh * a.Sq + qi) * 2 * D) + chalf * (D / 8);
+#pragma unroll 1
+      for (int c0 = 0; c0 < D / 2; c0 += 32) {
+        uint32_t w[32];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          uint4 v = make_uint4(0, 0, 0, 0);
+          if (live) v = src[c0 / 4 + i];
+          w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+        }
+        tc::tmem_st32(tmem_base + L::kColQ + lane_base + chalf * (D / 2) + c0, w);
       }
-      tc::fence_async_smem();
+      tc::wait_st();
+      tc::fence_before_sync();
       tc::mbar_arrive(q_full);
     }
     float m_run = -INFINITY, l_run = 0.f;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int bb = j & 1, u = j >> 1, k0 = j * kBN;
+      const int kc0 = k0 + chalf * HC;  // first key column of this thread
+      tr.mark(0, j);
       if (!(ok = tc::mbar_wait_or_abort(s_full(bb), u & 1, abort_flag))) break;
       tc::fence_after_sync();
-      float t[kBN];
+      tr.mark(1, j);
+      float t[HC];
       {
         uint32_t raw[32];
-        tc::tmem_ld32(tmem_base + lane_base + bb * kBN, raw);
+        tc::tmem_ld32(tmem_base + L::kColS + lane_base + bb * kBN + chalf * HC, raw);
         tc::wait_ld();
 #pragma unroll
         for (int c = 0; c < 32; ++c) t[c] = __uint_as_float(raw[c]);
-        tc::tmem_ld32(tmem_base + lane_base + bb * kBN + 32, raw);
-        tc::wait_ld();
-#pragma unroll
-        for (int c = 0; c < 32; ++c) t[32 + c] = __uint_as_float(raw[c]);
       }
       tc::fence_before_sync();
       tc::mbar_arrive(s_empty(bb));
+      tr.mark(2, j);
       float mx = -INFINITY;
       const bool edge = (k0 + kBN > a.Sk) || (a.causal && k0 + kBN - 1 > q0 + shift) || a.mask != nullptr;
       if (!edge) {
 #pragma unroll
-        for (int c4 = 0; c4 < kBN; c4 += 4) {
-          const float4 cs = *reinterpret_cast<const float4*>(&cscale[bb][c4]);
+        for (int c4 = 0; c4 < HC; c4 += 4) {
+          const float4 cs = *reinterpret_cast<const float4*>(&cscale[j & 7][chalf * HC + c4]);
           t[c4] *= cs.x; t[c4 + 1] *= cs.y; t[c4 + 2] *= cs.z; t[c4 + 3] *= cs.w;
           mx = fmaxf(mx, fmaxf(fmaxf(t[c4], t[c4 + 1]), fmaxf(t[c4 + 2], t[c4 + 3])));
         }
       } else {
         const float* mrow = (a.mask != nullptr && qi < a.Sq)
-                                ? a.mask + b * a.mask_stride_b + (int64_t)qi * a.mask_stride_q + k0
+                                ? a.mask + b * a.mask_stride_b + (int64_t)qi * a.mask_stride_q + kc0
                                 : nullptr;
 #pragma unroll
-        for (int c = 0; c < kBN; ++c) {
-          const int k = k0 + c;
-          float v = t[c] * cscale[bb][c];
+        for (int c = 0; c < HC; ++c) {
+          const int k = kc0 + c;
+          float v = t[c] * cscale[j & 7][chalf * HC + c];
           if (mrow != nullptr && k < a.Sk) v = fmaf(mrow[c], kLog2e, v);
           if (k >= a.Sk || (a.causal && k > qi + shift)) v = -INFINITY;
           t[c] = v;
           mx = fmaxf(mx, v);
         }
       }
+      // the other half of the row lives in the partner warp: swap maxima through shared memory
+      // (slots alternate with the tile parity: a slot is rewritten two exchanges later, after the
+      // partner has arrived at the exchange in between, i.e. after it has read this one)
+      xmax[bb][chalf][row] = mx;
+      tc::mbar_arrive(xch(quad));
+      if (!(ok = tc::mbar_wait_or_abort(xch(quad), j & 1, abort_flag))) break;
+      mx = fmaxf(mx, xmax[bb][1 - chalf][row]);
       // running max, raised lazily: rescaling O costs a tensor-memory round trip, so the max only
-      // moves when some row of the warp outgrew it by more than 2^8 (P stays below 256)
+      // moves when some row of the quadrant outgrew it by more than 2^8 (P stays below 256)
       const float m_cand = fmaxf(m_run, mx);
-      const bool grow = __any_sync(0xffffffffu, m_cand > m_run + 8.f);
+      const bool grow = __any_sync(0xffffffffu, m_cand > m_run + 8.f);  // identical in both warps of the quadrant
       float alpha = 1.f;
       if (grow) {
         alpha = (m_run == -INFINITY) ? 0.f : tc::fast_exp2(m_run - m_cand);
         m_run = m_cand;
       }
       const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
-      if (u >= 1 && !(ok = tc::mbar_wait_or_abort(pv_done(bb), (u - 1) & 1, abort_flag))) break;  // P[bb] free
       float psum = 0.f;
-      {
-        uint8_t* pd = smem_raw + L::kPOff + bb * L::kPStage + (row / 8) * L::kSboP + (row % 8) * 16;
+      uint32_t pw[HC / 2];
 #pragma unroll
-        for (int c8 = 0; c8 < kBN / 8; ++c8) {
-          uint32_t w[4];
-#pragma unroll
-          for (int p = 0; p < 4; ++p) {
-            const float p0 = tc::fast_exp2(t[c8 * 8 + 2 * p] - m_use);
-            const float p1 = tc::fast_exp2(t[c8 * 8 + 2 * p + 1] - m_use);
-            psum += p0 + p1;
-            w[p] = tc::pack_bf16x2(p0, p1);
-          }
-          *reinterpret_cast<uint4*>(pd + c8 * 128) = make_uint4(w[0], w[1], w[2], w[3]);
-        }
+      for (int c = 0; c < HC / 2; ++c) {
+        const float p0 = tc::fast_exp2(t[2 * c] - m_use), p1 = tc::fast_exp2(t[2 * c + 1] - m_use);
+        psum += p0 + p1;
+        pw[c] = tc::pack_bf16x2(p0, p1);
       }
       l_run = l_run * alpha + psum;
+      tr.mark(3, j);
+      if (u >= 1 && !(ok = tc::mbar_wait_or_abort(pv_done(bb), (u - 1) & 1, abort_flag))) break;  // P[bb] free
+      tc::fence_after_sync();
+      tr.mark(4, j);
+      tc::tmem_st16(tmem_base + L::kColP + lane_base + bb * (kBN / 2) + chalf * (HC / 2), pw);
       if (grow && j >= 1) {
-        // O must be at rest: wait for the previous tile's P V_hat
+        // O must be at rest: wait for the previous tile's P V_hat; each half rescales D/2 columns
         if (!(ok = tc::mbar_wait_or_abort(pv_done((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag))) break;
         tc::fence_after_sync();
 #pragma unroll 1
-        for (int c0 = 0; c0 < D; c0 += 32) {
+        for (int c0 = 0; c0 < D / 2; c0 += 32) {
           uint32_t raw[32];
-          tc::tmem_ld32(tmem_o + lane_base + c0, raw);
+          const uint32_t addr = tmem_o + lane_base + chalf * (D / 2) + c0;
+          tc::tmem_ld32(addr, raw);
           tc::wait_ld();
 #pragma unroll
           for (int c = 0; c < 32; ++c) raw[c] = __float_as_uint(__uint_as_float(raw[c]) * alpha);
-          tc::tmem_st32(tmem_o + lane_base + c0, raw);
+          tc::tmem_st32(addr, raw);
         }
-        tc::wait_st();
       }
-      tc::fence_async_smem();
+      tc::wait_st();
       tc::fence_before_sync();
       tc::mbar_arrive(p_full(bb));
+      tr.mark(5, j);
     }
     // ---- epilogue: normalise and store the rotated output row ----
     if (ok && n_tiles > 0)
       ok = tc::mbar_wait_or_abort(pv_done((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, abort_flag);
     if (ok) {
+      xmax[n_tiles & 1][chalf][row] = l_run;
+      tc::mbar_arrive(xch(quad));
+      ok = tc::mbar_wait_or_abort(xch(quad), n_tiles & 1, abort_flag);
+    }
+    if (ok) {
       tc::fence_after_sync();
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* dst = o_rot + (bh * a.Sq + qi) * D;
+      const float l_tot = l_run + xmax[n_tiles & 1][1 - chalf][row];
+      const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+      __nv_bfloat16* dst = o_rot + (bh * a.Sq + qi) * D + chalf * (D / 2);
 #pragma unroll 1
-      for (int c0 = 0; c0 < D; c0 += 32) {
+      for (int c0 = 0; c0 < D / 2; c0 += 32) {
         uint32_t raw[32];
-        tc::tmem_ld32(tmem_o + lane_base + c0, raw);
+        tc::tmem_ld32(tmem_o + lane_base + chalf * (D / 2) + c0, raw);
         tc::wait_ld();
         if (qi < a.Sq) {
 #pragma unroll
@@ -439,11 +499,12 @@ __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnA
         }
       }
     }
-  } else if (warp < 8) {
+  } else if (warp < kMmaWarp) {
     // =============================== producer warps ===============================
-    const int p = tid - 128;
+    const int p = tid - kSoftmaxThreads;
     constexpr int UK = L::kIdxK / 8, US = L::kSgn / 8, UV = L::kIdxV / 8;  // 8-byte units per tile
-    constexpr int NK = (UK + 127) / 128, NV = (UV + 127) / 128;
+    constexpr int NK = (UK + kProducers - 1) / kProducers, NV = (UV + kProducers - 1) / kProducers;
+    constexpr int NI = (kBN * GP + kProducers - 1) / kProducers;  // (key, 16-coordinate) items per thread
     uint2 rk[NK], rv[NV], rs;
     uint32_t rn[3];
     const uint8_t* gk = a.key_idx + kv_base * (G * KB);
@@ -453,13 +514,13 @@ __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnA
       const uint2 zero = make_uint2(0, 0);
 #pragma unroll
       for (int i = 0; i < NK; ++i) {
-        const int un = i * 128 + p;
+        const int un = i * kProducers + p;
         rk[i] = (un < UK && k0 + (un * 8) / (G * KB) < a.Sk)
                     ? *reinterpret_cast<const uint2*>(gk + (int64_t)k0 * (G * KB) + un * 8) : zero;
       }
 #pragma unroll
       for (int i = 0; i < NV; ++i) {
-        const int un = i * 128 + p;
+        const int un = i * kProducers + p;
         rv[i] = (un < UV && k0 + (un * 8) / (G * VB) < a.Sk)
                     ? *reinterpret_cast<const uint2*>(gv + (int64_t)k0 * (G * VB) + un * 8) : zero;
       }
@@ -471,106 +532,189 @@ __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnA
         rn[2] = live ? a.val_vn[kv_base + k0 + p] : 0;
       }
     };
+    // item i of this thread: key and coordinate-pair group, fixed for the whole kernel
+    int ikey[NI], igp[NI];
+#pragma unroll
+    for (int i = 0; i < NI; ++i) {
+      const int e = i * kProducers + p;
+      ikey[i] = (e % 8) + 8 * (e / (8 * GP));
+      igp[i] = (e / 8) % GP;
+    }
     if (n_tiles > 0) prefetch(0);
     for (int j = 0; j < n_tiles && ok; ++j) {
-      const int bb = j & 1, u = j >> 1;
-      uint8_t* pk = smem_raw + L::kPkOff + bb * L::kPkStage;
-      // K_hat/V_hat/cscale of parity bb are free once tile j-2's P V_hat has drained
-      if (u >= 1 && !(ok = tc::mbar_wait_or_abort(pv_done(bb), (u - 1) & 1, abort_flag))) break;
+      const int st = j % kStages, u = j / kStages;
+      uint8_t* pk = smem_raw + L::kPkOff + st * L::kPkStage;
+      // slot st (staged bytes, column scales, K_hat) is free once tile j-kStages' score MMA has drained;
+      // its V_hat decode by this same thread is long finished
+      tr.mark(0, j);
+      if (u >= 1 && !(ok = tc::mbar_wait_or_abort(k_empty(st), (u - 1) & 1, abort_flag))) break;
+      tr.mark(1, j);
 #pragma unroll
       for (int i = 0; i < NK; ++i)
-        if (i * 128 + p < UK) *reinterpret_cast<uint2*>(pk + (i * 128 + p) * 8) = rk[i];
+        if (i * kProducers + p < UK) *reinterpret_cast<uint2*>(pk + (i * kProducers + p) * 8) = rk[i];
 #pragma unroll
       for (int i = 0; i < NV; ++i)
-        if (i * 128 + p < UV) *reinterpret_cast<uint2*>(pk + L::kIdxK + L::kSgn + (i * 128 + p) * 8) = rv[i];
+        if (i * kProducers + p < UV)
+          *reinterpret_cast<uint2*>(pk + L::kIdxK + L::kSgn + (i * kProducers + p) * 8) = rv[i];
       if (p < US) *reinterpret_cast<uint2*>(pk + L::kIdxK + p * 8) = rs;
       if (p < kBN) {
         const float nk = fp16_value((uint16_t)rn[0]);
-        cscale[bb][p] = nk * a.sm_scale * kLog2e;
-        rho_s[bb][p] = nk > 0.f ? fp16_value((uint16_t)rn[1]) / nk : 0.f;
-        nv_s[bb][p] = fp16_value((uint16_t)rn[2]);
+        cscale[j & 7][p] = nk * a.sm_scale * kLog2e;
+        rho_s[st][p] = nk > 0.f ? fp16_value((uint16_t)rn[1]) / nk : 0.f;
+        nv_s[st][p] = fp16_value((uint16_t)rn[2]);
       }
       // every producer's staged bytes must be visible before anyone decodes (a bounded wait
       // instead of bar.sync, so that a fault elsewhere cannot strand part of the group)
-      tc::mbar_arrive(pk_full(bb));
-      if (!(ok = tc::mbar_wait_or_abort(pk_full(bb), u & 1, abort_flag))) break;
+      tc::mbar_arrive(pk_full(st));
+      if (!(ok = tc::mbar_wait_or_abort(pk_full(st), u & 1, abort_flag))) break;
+      tr.mark(2, j);
       if (j + 1 < n_tiles) prefetch((j + 1) * kBN);  // in flight while this tile is decoded
-      uint8_t* Kd = smem_raw + L::kKOff + bb * L::kKStage;
-      uint8_t* Vd = smem_raw + L::kVOff + bb * L::kVStage;
-#pragma unroll 2
-      for (int e = p; e < kBN * GP; e += 128) {
-        const int key = (e % 8) + 8 * (e / (8 * GP)), gp = (e / 8) % GP;
-        const uint16_t* sk = reinterpret_cast<const uint16_t*>(pk + key * (G * KB) + gp * 2 * KB);
-        const uint16_t* sv = reinterpret_cast<const uint16_t*>(pk + L::kIdxK + L::kSgn + key * (G * VB) + gp * 2 * VB);
-        uint64_t wk = 0, wv = 0;
+      // ---- keys: centroid values and +-rho sign tile ----
+      uint8_t* Kd = smem_raw + L::kKOff + st * L::kKStage;
+      {
+        uint32_t gw[NI][2], sb[NI], rr[NI];
 #pragma unroll
-        for (int i = 0; i < KB; ++i) wk |= (uint64_t)sk[i] << (16 * i);
+        for (int i = 0; i < NI; ++i) {
+          if (i * kProducers + p < kBN * GP) {
+            const uint16_t* sk = reinterpret_cast<const uint16_t*>(pk + ikey[i] * (G * KB) + igp[i] * 2 * KB);
+            uint64_t w = 0;
 #pragma unroll
-        for (int i = 0; i < VB; ++i) wv |= (uint64_t)sv[i] << (16 * i);
-        const uint32_t sb = ~(uint32_t)*reinterpret_cast<const uint16_t*>(pk + L::kIdxK + key * G + gp * 2);
-        const float rho = rho_s[bb][key], nvf = nv_s[bb][key];
-        const uint32_t rr = tc::pack_bf16x2(rho, rho);
-        const __nv_bfloat162 nv2 = __floats2bfloat162_rn(nvf, nvf);
-        uint32_t kq[8], sq[8], vq[8];
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          kq[q] = lutK[(uint32_t)(wk >> (2 * q * KB)) & ((1u << (2 * KB)) - 1)];
-          sq[q] = rr ^ (((sb >> (2 * q)) & 1u) << 15) ^ (((sb >> (2 * q + 1)) & 1u) << 31);
-          const uint32_t vv = lutV[(uint32_t)(wv >> (2 * q * VB)) & ((1u << (2 * VB)) - 1)];
-          const __nv_bfloat162 prod = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&vv), nv2);
-          vq[q] = *reinterpret_cast<const uint32_t*>(&prod);
+            for (int x = 0; x < KB; ++x) w |= (uint64_t)sk[x] << (16 * x);
+            gw[i][0] = (uint32_t)w & ((1u << (8 * KB)) - 1);
+            gw[i][1] = (uint32_t)(w >> (8 * KB));
+            sb[i] = ~(uint32_t)*reinterpret_cast<const uint16_t*>(pk + L::kIdxK + ikey[i] * G + igp[i] * 2);
+            const float rho = rho_s[st][ikey[i]];
+            rr[i] = tc::pack_bf16x2(rho, rho);
+          }
         }
-        uint8_t* kd = Kd + (key / 8) * L::kSboQK + (key % 8) * 16;
-        uint8_t* vd = Vd + (key / 8) * L::kLboV + (key % 8) * 16;
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          const int g = 2 * gp + half;
-          *reinterpret_cast<uint4*>(kd + g * 128) = make_uint4(kq[4 * half], kq[4 * half + 1], kq[4 * half + 2], kq[4 * half + 3]);
-          *reinterpret_cast<uint4*>(kd + (G + g) * 128) = make_uint4(sq[4 * half], sq[4 * half + 1], sq[4 * half + 2], sq[4 * half + 3]);
-          *reinterpret_cast<uint4*>(vd + g * L::kSboV) = make_uint4(vq[4 * half], vq[4 * half + 1], vq[4 * half + 2], vq[4 * half + 3]);
+        for (int i = 0; i < NI; ++i) {
+          if (i * kProducers + p < kBN * GP) {
+            uint8_t* kd = Kd + (ikey[i] / 8) * L::kSboK + (ikey[i] % 8) * 16;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              uint32_t kq[4], sq[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                kq[q] = lutK[(gw[i][half] >> (2 * q * KB)) & ((1u << (2 * KB)) - 1)];
+                sq[q] = rr[i] ^ ((((sb[i] >> (8 * half + 2 * q)) & 3u) * 0x40008000u) & 0x80008000u);  // bit0 -> 15, bit1 -> 31
+              }
+              const int g = 2 * igp[i] + half;
+              *reinterpret_cast<uint4*>(kd + g * 128) = make_uint4(kq[0], kq[1], kq[2], kq[3]);
+              *reinterpret_cast<uint4*>(kd + (G + g) * 128) = make_uint4(sq[0], sq[1], sq[2], sq[3]);
+            }
+          }
         }
       }
       tc::fence_async_smem();
-      tc::mbar_arrive(kv_full(bb));
+      tc::mbar_arrive(k_full(st));
+      tr.mark(3, j);
+      // ---- values: V_hat[st] is free once tile j-kStages' P V_hat has drained ----
+      if (u >= 1 && !(ok = tc::mbar_wait_or_abort(v_empty(st), (u - 1) & 1, abort_flag))) break;
+      tr.mark(4, j);
+      uint8_t* Vd = smem_raw + L::kVOff + st * L::kVStage;
+      {
+        uint32_t gw[NI][2];
+        __nv_bfloat162 nv2[NI];
+#pragma unroll
+        for (int i = 0; i < NI; ++i) {
+          if (i * kProducers + p < kBN * GP) {
+            const uint16_t* sv =
+                reinterpret_cast<const uint16_t*>(pk + L::kIdxK + L::kSgn + ikey[i] * (G * VB) + igp[i] * 2 * VB);
+            uint64_t w = 0;
+#pragma unroll
+            for (int x = 0; x < VB; ++x) w |= (uint64_t)sv[x] << (16 * x);
+            gw[i][0] = (uint32_t)w & (VB == 4 ? 0xffffffffu : ((1u << (8 * (VB & 3))) - 1));
+            gw[i][1] = (uint32_t)(w >> (8 * VB));
+            const float nvf = nv_s[st][ikey[i]];
+            nv2[i] = __floats2bfloat162_rn(nvf, nvf);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < NI; ++i) {
+          if (i * kProducers + p < kBN * GP) {
+            uint8_t* vd = Vd + (ikey[i] / 8) * L::kLboV + (ikey[i] % 8) * 16;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              uint32_t vq[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint32_t vv = lutV[(gw[i][half] >> (2 * q * VB)) & ((1u << (2 * VB)) - 1)];
+                const __nv_bfloat162 prod = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&vv), nv2[i]);
+                vq[q] = *reinterpret_cast<const uint32_t*>(&prod);
+              }
+              *reinterpret_cast<uint4*>(vd + (2 * igp[i] + half) * L::kSboV) = make_uint4(vq[0], vq[1], vq[2], vq[3]);
+            }
+          }
+        }
+      }
+      tc::fence_async_smem();
+      tc::mbar_arrive(v_full(st));
+      tr.mark(5, j);
     }
   } else if (lane == 0) {
     // =============================== MMA issuer ===============================
     constexpr uint32_t idesc_s = tc::idesc_bf16(kBM, kBN, false, false);
     constexpr uint32_t idesc_o = tc::idesc_bf16(kBM, D, false, true);
-    const uint64_t qdesc = tc::smem_desc(tc::smem_u32(Qs), 128, L::kSboQK);
     auto issue_scores = [&](int j) -> bool {
-      const int bb = j & 1, u = j >> 1;
-      if (!tc::mbar_wait_or_abort(kv_full(bb), u & 1, abort_flag)) return false;
+      const int bb = j & 1, u = j >> 1, st = j % kStages;
+      tr.mark(0, j);
+      if (!tc::mbar_wait_or_abort(k_full(st), (j / kStages) & 1, abort_flag)) return false;
+      tr.mark(1, j);
       if (u >= 1 && !tc::mbar_wait_or_abort(s_empty(bb), (u - 1) & 1, abort_flag)) return false;
       tc::fence_after_sync();
-      const uint64_t kdesc = tc::smem_desc(tc::smem_u32(smem_raw + L::kKOff + bb * L::kKStage), 128, L::kSboQK);
+      tr.mark(2, j);
+      const uint64_t kdesc = tc::smem_desc(tc::smem_u32(smem_raw + L::kKOff + st * L::kKStage), 128, L::kSboK);
 #pragma unroll
       for (int ks = 0; ks < 2 * D / 16; ++ks)
-        tc::mma_bf16(tmem_base + bb * kBN, qdesc + (uint64_t)(ks * 256 >> 4), kdesc + (uint64_t)(ks * 256 >> 4),
-                     idesc_s, ks > 0);
+        tc::mma_bf16_ts(tmem_base + L::kColS + bb * kBN, tmem_base + L::kColQ + ks * 8,
+                        kdesc + (uint64_t)(ks * 256 >> 4), idesc_s, ks > 0);
       tc::mma_commit(s_full(bb));
+      tc::mma_commit(k_empty(st));
+      tr.mark(3, j);
       return true;
     };
     ok = tc::mbar_wait_or_abort(q_full, 0, abort_flag);
     if (ok && n_tiles > 0) ok = issue_scores(0);
     for (int j = 0; j < n_tiles && ok; ++j) {
-      const int bb = j & 1, u = j >> 1;
+      const int bb = j & 1, u = j >> 1, st = j % kStages;
       if (j + 1 < n_tiles && !(ok = issue_scores(j + 1))) break;
+      tr.mark(4, j);
+      if (!(ok = tc::mbar_wait_or_abort(v_full(st), (j / kStages) & 1, abort_flag))) break;
       if (!(ok = tc::mbar_wait_or_abort(p_full(bb), u & 1, abort_flag))) break;
       tc::fence_after_sync();
-      const uint64_t pdesc = tc::smem_desc(tc::smem_u32(smem_raw + L::kPOff + bb * L::kPStage), 128, L::kSboP);
-      const uint64_t vdesc = tc::smem_desc(tc::smem_u32(smem_raw + L::kVOff + bb * L::kVStage), L::kLboV, L::kSboV);
+      tr.mark(5, j);
+      const uint64_t vdesc = tc::smem_desc(tc::smem_u32(smem_raw + L::kVOff + st * L::kVStage), L::kLboV, L::kSboV);
 #pragma unroll
       for (int ks = 0; ks < kBN / 16; ++ks)
-        tc::mma_bf16(tmem_o, pdesc + (uint64_t)(ks * 256 >> 4), vdesc + (uint64_t)(ks * 2 * L::kLboV >> 4), idesc_o,
-                     (j > 0 || ks > 0) ? 1u : 0u);
+        tc::mma_bf16_ts(tmem_o, tmem_base + L::kColP + bb * (kBN / 2) + ks * 8,
+                        vdesc + (uint64_t)(ks * 2 * L::kLboV >> 4), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
       tc::mma_commit(pv_done(bb));
+      tc::mma_commit(v_empty(st));
+      tr.mark(6, j);
     }
   }
   if (!ok && atomicExch(&s_abort, 2) != 2) record_fault();  // one fault per CTA
   tc::fence_before_sync();
   __syncthreads();
-  if (warp == 8) tc::tmem_dealloc(tmem_base, kTmemCols);
+  if (warp == kMmaWarp) tc::tmem_dealloc(tmem_base, L::kCols);
+}
+
+int trace_enable(int on) {
+  const int v = on ? 1 : 0;
+  static long long fill[2 * kTraceCap];
+  for (int i = 0; i < 2 * kTraceCap; ++i) fill[i] = -1;
+  TQ_CUDA_OK(cudaMemcpyToSymbol(g_trace, fill, sizeof(fill)));
+  TQ_CUDA_OK(cudaMemcpyToSymbol(g_trace_on, &v, sizeof(v)));
+  return TQ_OK;
+}
+int trace_read(long long* host_buf, int max_records, int* n_out) {
+  // the buffer is copied whole; unused slots hold tag -1
+  int n = kTraceCap < max_records ? kTraceCap : max_records;
+  TQ_CUDA_OK(cudaDeviceSynchronize());
+  TQ_CUDA_OK(cudaMemcpyFromSymbol(host_buf, g_trace, sizeof(long long) * 2 * n));
+  *n_out = n;
+  return TQ_OK;
 }
 
 // ---- host side ---------------------------------------------------------------------------
@@ -589,7 +733,9 @@ static int launch_rows_gemm(const RowsGemmArgs& a, cudaStream_t stream) {
 
 template <int D, int BITS>
 static int launch_attention_tc(const AttnArgs& a, int64_t B, __nv_bfloat16* o_rot, cudaStream_t stream) {
-  constexpr size_t smem = WsSmem<D, BITS>::kTotal;
+  // every CTA takes all 512 tensor-memory columns, so keep it alone on its SM: ask for more than
+  // half of the shared memory even when the tiles (d = 64) would need less
+  constexpr size_t smem = WsSmem<D, BITS>::kTotal > 120 * 1024 ? WsSmem<D, BITS>::kTotal : 120 * 1024;
   auto kern = attention_ws_kernel<D, BITS>;
   TQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid((unsigned)((a.Sq + kBM - 1) / kBM), (unsigned)a.Hq, (unsigned)B);

@@ -180,6 +180,13 @@ int tq_device_fault_count(void* stream, int64_t* count_host) {
   return TQ_OK;
 }
 
+int tq_trace_enable(int on) { return trace_enable(on); }
+
+int tq_trace_read(int64_t* records_host, int max_records, int* n_host) {
+  TQ_REQUIRE(records_host && n_host && max_records > 0, "bad trace buffer");
+  return trace_read(reinterpret_cast<long long*>(records_host), max_records, n_host);
+}
+
 int tq_profile_begin(int max_records) {
   TQ_REQUIRE(max_records > 0 && max_records <= 4096, "max_records %d outside 1..4096", max_records);
   TQ_REQUIRE(!g_prof.on, "profiling already active");
