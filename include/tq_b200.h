@@ -192,6 +192,36 @@ int tq_attention_fwd(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq
                      void* out, int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s,
                      void* workspace, size_t workspace_bytes, int mode, void* stream);
 
+/* tq_attention_fwd for callers that cannot hand over scratch memory (no counterpart in the
+ * reference).  Meant for hosts that may not call cudaMalloc or any other allocator: a plugin
+ * inside a serving process whose device memory belongs to someone else, or a call site that
+ * only holds borrowed input and output buffers.  Same arguments and results as tq_attention_fwd
+ * minus `workspace`: the scratch is a fixed tq_static_scratch_bytes() (32 MiB) array compiled
+ * into the library, resident on every GPU that loads it until the process exits.
+ *   - A problem whose tq_attention_workspace_bytes exceeds that size is rejected with
+ *     TQ_ERR_WORKSPACE and nothing is launched (at d=128 the array covers about 43 000 query
+ *     rows B*Hq*Sq in bf16 mode, 32 000 in fp32 mode).
+ *   - The first call on each device looks up the array's device address (one runtime query,
+ *     no allocation); make that first call outside any stream capture.  No call allocates or
+ *     frees device memory.
+ *   - All calls on a device share the one array.  Every byte a call reads from it was written
+ *     earlier in the same call, so stale contents are harmless and nothing has to be cleared;
+ *     but two calls that overlap on the GPU (different streams, or threads) race on it.
+ *     Serialise them. */
+size_t tq_static_scratch_bytes(void);
+int tq_attention_fwd_static(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq, int d,
+                            int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                            int64_t Hkv, int64_t Sk,
+                            const uint8_t* key_idx, const uint8_t* key_signs,
+                            const uint16_t* key_vec_norms, const uint16_t* key_residual_norms,
+                            const uint8_t* val_idx, const uint16_t* val_vec_norms,
+                            const float* Pi_k, const float* S_eff, const float* centroids_k,
+                            const float* Pi_v, const float* centroids_v, int bits,
+                            float sm_scale, int causal,
+                            const float* mask, int64_t mask_stride_b, int64_t mask_stride_q,
+                            void* out, int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s,
+                            int mode, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -674,3 +674,56 @@ extern "C" int tq_attention_fwd(const void* q, int dtype, int64_t B, int64_t Hq,
   return attention_fwd_bf16(q, dtype, B, Hq, Sq, d, q_stride_b, q_stride_h, q_stride_s, Pi_k, S_eff, a, bits,
                             workspace, s);
 }
+
+// ---- attention without caller-supplied scratch ---------------------------------------------
+//
+// Some hosts of this library may not allocate device memory themselves: a plugin running inside a
+// serving process whose memory pool is owned by another component, a caller that holds only
+// borrowed input and output buffers, or code on a path where cudaMalloc is forbidden (it
+// synchronises the device and can fail late under memory pressure).  For them the scratch that
+// tq_attention_fwd needs lives in this fixed array, which every GPU that loads the library carries
+// until the process exits.
+namespace {
+constexpr size_t kStaticScratchBytes = 32u << 20;  // 32 MiB
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_addr[kMaxDevices] = {nullptr};  // device address of the array, per device
+}  // namespace
+
+extern "C" size_t tq_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+extern "C" int tq_attention_fwd_static(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq, int d,
+                                       int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s, int64_t Hkv,
+                                       int64_t Sk, const uint8_t* key_idx, const uint8_t* key_signs,
+                                       const uint16_t* key_vec_norms, const uint16_t* key_residual_norms,
+                                       const uint8_t* val_idx, const uint16_t* val_vec_norms, const float* Pi_k,
+                                       const float* S_eff, const float* centroids_k, const float* Pi_v,
+                                       const float* centroids_v, int bits, float sm_scale, int causal,
+                                       const float* mask, int64_t mask_stride_b, int64_t mask_stride_q, void* out,
+                                       int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s, int mode,
+                                       void* stream) {
+  if (int st = check_attention_common(q, dtype, B, Hq, Sq, d, q_stride_b, q_stride_h, q_stride_s, Hkv, Sk, bits,
+                                      mode))
+    return st;
+  const size_t need = tq_attention_workspace_bytes(B, Hq, Sq, d, mode);
+  if (need > kStaticScratchBytes)
+    return fail(TQ_ERR_WORKSPACE,
+                "problem needs %zu bytes of scratch but the built-in array holds %zu; use tq_attention_fwd with "
+                "a caller-supplied workspace",
+                need, kStaticScratchBytes);
+  int dev = 0;
+  TQ_CUDA_OK(cudaGetDevice(&dev));
+  TQ_REQUIRE(dev >= 0 && dev < kMaxDevices, "device ordinal %d outside 0..%d", dev, kMaxDevices - 1);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    // In host code the array's name is only a handle; the address kernels may use comes from the
+    // runtime, once per device, with that device current.
+    void* p = nullptr;
+    TQ_CUDA_OK(cudaGetSymbolAddress(&p, g_static_scratch));
+    TQ_REQUIRE(p != nullptr, "could not resolve the built-in scratch array");
+    g_static_scratch_addr[dev] = p;
+  }
+  return tq_attention_fwd(q, dtype, B, Hq, Sq, d, q_stride_b, q_stride_h, q_stride_s, Hkv, Sk, key_idx, key_signs,
+                          key_vec_norms, key_residual_norms, val_idx, val_vec_norms, Pi_k, S_eff, centroids_k, Pi_v,
+                          centroids_v, bits, sm_scale, causal, mask, mask_stride_b, mask_stride_q, out, o_stride_b,
+                          o_stride_h, o_stride_s, g_static_scratch_addr[dev], kStaticScratchBytes, mode, stream);
+}
