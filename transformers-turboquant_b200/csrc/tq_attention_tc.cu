@@ -245,11 +245,28 @@ constexpr int kProducers = 256;
 constexpr int kWsThreads = kSoftmaxThreads + kProducers + 32;
 constexpr int kMmaWarp = kWsThreads / 32 - 1;
 
+// Pair table: entry (i1 << B | i0) holds the bf16x2 word (C[i0], C[i1]).  Small tables of 4-byte
+// entries keep random look-ups (nearly) free of bank conflicts; byte-indexed tables of 8- and
+// 16-byte entries were measured slower.
+template <int B>
+__device__ __forceinline__ void fill_index_lut(uint32_t* lut, const float* __restrict__ cen, int tid, int nthreads) {
+  for (int e = tid; e < (1 << (2 * B)); e += nthreads)
+    lut[e] = tc::pack_bf16x2(cen[e & ((1 << B) - 1)], cen[e >> B]);
+}
+// Decode the B-bit indices of 8 consecutive coordinates (the low 8*B bits of `bits`) into 4 bf16x2 words.
+template <int B>
+__device__ __forceinline__ void decode_group(const uint32_t* lut, uint32_t bits, uint32_t (&out)[4]) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q) out[q] = lut[(bits >> (2 * q * B)) & ((1u << (2 * B)) - 1)];
+}
+
 template <int D, int BITS>
 struct WsSmem {
   static constexpr int G = D / 8, KB = BITS - 1, VB = BITS;
   static constexpr uint32_t kKStage = kBN * 2 * D * 2;
-  static constexpr uint32_t kVStage = kBN * D * 2;
+  static constexpr int DV = D + 16;                   // value coordinates + a 16-wide block whose first
+                                                      // row is all ones: P V_hat then also yields the row sums
+  static constexpr uint32_t kVStage = kBN * DV * 2;
   static constexpr uint32_t kIdxK = kBN * G * KB;     // packed key-index bytes per tile
   static constexpr uint32_t kSgn = kBN * G;
   static constexpr uint32_t kIdxV = kBN * G * VB;
@@ -260,13 +277,14 @@ struct WsSmem {
   static constexpr uint32_t kTotal = kPkOff + kStages * kPkStage;
   static constexpr uint32_t kSboK = 2 * G * 128;        // K-major [keys, 2D]
   static constexpr uint32_t kSboV = 128;                // MN-major [D, kBN]: 8-coordinate chunks adjacent
-  static constexpr uint32_t kLboV = G * 128;            // ... 8-key groups G core matrices apart
+  static constexpr uint32_t kLboV = (G + 2) * 128;      // ... 8-key groups G+2 core matrices apart
   // tensor-memory columns
   static constexpr uint32_t kColS = 0;                  // S[2]: 2 x 64
-  static constexpr uint32_t kColO = 128;                // O: D
-  static constexpr uint32_t kColQ = 256;                // Q_cat: 2D bf16 = D columns
-  static constexpr uint32_t kColP = 384;                // P[2]: 2 x 32 (64 bf16 each)
+  static constexpr uint32_t kColO = 128;                // O: D value columns, then the row sum in column D
+  static constexpr uint32_t kColQ = 128 + DV;           // Q_cat: 2D bf16 = D columns
+  static constexpr uint32_t kColP = kColQ + D;          // P[2]: 2 x 32 (64 bf16 each)
   static constexpr uint32_t kCols = 512;
+  static_assert(kColP + kBN <= kCols, "tensor memory over-subscribed");
 };
 
 template <int D, int BITS>
@@ -281,8 +299,8 @@ __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnA
   __shared__ float cscale[8][kBN];
   __shared__ float rho_s[kStages][kBN];   // rn_k / n_k
   __shared__ float nv_s[kStages][kBN];    // value norms
-  __shared__ float xmax[2][2][kBM];       // [tile parity][column half][row]: half-row maxima / sums exchanged
-  __shared__ uint32_t lutK[1 << (2 * KB)];
+  __shared__ float xmax[2][2][kBM];       // [tile parity][column half][row]: half-row maxima exchanged
+  __shared__ uint32_t lutK[1 << (2 * KB)];  // index pair -> bf16x2 centroids
   __shared__ uint32_t lutV[1 << (2 * VB)];
   __shared__ __align__(8) uint64_t bars[5 * kStages + 8 + 4 + 1];
   __shared__ uint32_t tmem_slot;
@@ -336,10 +354,8 @@ __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnA
     tc::fence_mbar_init();
   }
   if (warp == kMmaWarp) tc::tmem_alloc(tc::smem_u32(&tmem_slot), L::kCols);
-  for (int e = tid; e < (1 << (2 * KB)); e += kWsThreads)
-    lutK[e] = tc::pack_bf16x2(a.cen_k[e & ((1 << KB) - 1)], a.cen_k[e >> KB]);
-  for (int e = tid; e < (1 << (2 * VB)); e += kWsThreads)
-    lutV[e] = tc::pack_bf16x2(a.cen_v[e & ((1 << VB) - 1)], a.cen_v[e >> VB]);
+  fill_index_lut<KB>(lutK, a.cen_k, tid, kWsThreads);
+  fill_index_lut<VB>(lutV, a.cen_v, tid, kWsThreads);
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
@@ -375,7 +391,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnA
       tc::fence_before_sync();
       tc::mbar_arrive(q_full);
     }
-    float m_run = -INFINITY, l_run = 0.f;
+    float m_run = -INFINITY;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int bb = j & 1, u = j >> 1, k0 = j * kBN;
       const int kc0 = k0 + chalf * HC;  // first key column of this thread
@@ -434,15 +450,10 @@ __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnA
         m_run = m_cand;
       }
       const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
-      float psum = 0.f;
       uint32_t pw[HC / 2];
 #pragma unroll
-      for (int c = 0; c < HC / 2; ++c) {
-        const float p0 = tc::fast_exp2(t[2 * c] - m_use), p1 = tc::fast_exp2(t[2 * c + 1] - m_use);
-        psum += p0 + p1;
-        pw[c] = tc::pack_bf16x2(p0, p1);
-      }
-      l_run = l_run * alpha + psum;
+      for (int c = 0; c < HC / 2; ++c)
+        pw[c] = tc::pack_bf16x2(tc::fast_exp2(t[2 * c] - m_use), tc::fast_exp2(t[2 * c + 1] - m_use));
       tr.mark(3, j);
       if (u >= 1 && !(ok = tc::mbar_wait_or_abort(pv_done(bb), (u - 1) & 1, abort_flag))) break;  // P[bb] free
       tc::fence_after_sync();
@@ -462,6 +473,14 @@ __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnA
           for (int c = 0; c < 32; ++c) raw[c] = __float_as_uint(__uint_as_float(raw[c]) * alpha);
           tc::tmem_st32(addr, raw);
         }
+        if (chalf == 1) {  // the row-sum block rides along with the second half
+          uint32_t raw[16];
+          tc::tmem_ld16(tmem_o + lane_base + D, raw);
+          tc::wait_ld();
+#pragma unroll
+          for (int c = 0; c < 16; ++c) raw[c] = __float_as_uint(__uint_as_float(raw[c]) * alpha);
+          tc::tmem_st16(tmem_o + lane_base + D, raw);
+        }
       }
       tc::wait_st();
       tc::fence_before_sync();
@@ -472,13 +491,14 @@ __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnA
     if (ok && n_tiles > 0)
       ok = tc::mbar_wait_or_abort(pv_done((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, abort_flag);
     if (ok) {
-      xmax[n_tiles & 1][chalf][row] = l_run;
-      tc::mbar_arrive(xch(quad));
-      ok = tc::mbar_wait_or_abort(xch(quad), n_tiles & 1, abort_flag);
-    }
-    if (ok) {
       tc::fence_after_sync();
-      const float l_tot = l_run + xmax[n_tiles & 1][1 - chalf][row];
+      float l_tot;
+      {  // column D of the accumulator is sum_k P[row][k] (the ones row of V_hat)
+        uint32_t raw[16];
+        tc::tmem_ld16(tmem_o + lane_base + D, raw);
+        tc::wait_ld();
+        l_tot = __uint_as_float(raw[0]);
+      }
       const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
       __nv_bfloat16* dst = o_rot + (bh * a.Sq + qi) * D + chalf * (D / 2);
 #pragma unroll 1
@@ -540,6 +560,12 @@ __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnA
       ikey[i] = (e % 8) + 8 * (e / (8 * GP));
       igp[i] = (e / 8) % GP;
     }
+    // constant part of every V_hat stage: coordinate row D is all ones (row sums), rows D+1..D+15 zero
+    for (int e = p; e < kStages * kBN * 2; e += kProducers) {
+      const int st = e / (kBN * 2), key = (e / 2) % kBN, blk = e % 2;
+      *reinterpret_cast<uint4*>(smem_raw + L::kVOff + st * L::kVStage + (key / 8) * L::kLboV + (key % 8) * 16 +
+                                (G + blk) * L::kSboV) = make_uint4(blk == 0 ? 0x00003F80u : 0u, 0u, 0u, 0u);
+    }
     if (n_tiles > 0) prefetch(0);
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int st = j % kStages, u = j / kStages;
@@ -593,12 +619,12 @@ __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnA
             uint8_t* kd = Kd + (ikey[i] / 8) * L::kSboK + (ikey[i] % 8) * 16;
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
-              uint32_t kq[4], sq[4];
+              uint32_t kq[4];
+              decode_group<KB>(lutK, gw[i][half], kq);
+              uint32_t sq[4];
 #pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                kq[q] = lutK[(gw[i][half] >> (2 * q * KB)) & ((1u << (2 * KB)) - 1)];
-                sq[q] = rr[i] ^ ((((sb[i] >> (8 * half + 2 * q)) & 3u) * 0x40008000u) & 0x80008000u);  // bit0 -> 15, bit1 -> 31
-              }
+              for (int q = 0; q < 4; ++q)  // sign bit 0 -> bit 15, bit 1 -> bit 31 of the bf16x2 word
+                sq[q] = rr[i] ^ ((((sb[i] >> (8 * half + 2 * q)) & 3u) * 0x40008000u) & 0x80008000u);
               const int g = 2 * igp[i] + half;
               *reinterpret_cast<uint4*>(kd + g * 128) = make_uint4(kq[0], kq[1], kq[2], kq[3]);
               *reinterpret_cast<uint4*>(kd + (G + g) * 128) = make_uint4(sq[0], sq[1], sq[2], sq[3]);
@@ -637,10 +663,10 @@ __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnA
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
               uint32_t vq[4];
+              decode_group<VB>(lutV, gw[i][half], vq);
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
-                const uint32_t vv = lutV[(gw[i][half] >> (2 * q * VB)) & ((1u << (2 * VB)) - 1)];
-                const __nv_bfloat162 prod = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&vv), nv2[i]);
+                const __nv_bfloat162 prod = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&vq[q]), nv2[i]);
                 vq[q] = *reinterpret_cast<const uint32_t*>(&prod);
               }
               *reinterpret_cast<uint4*>(vd + (2 * igp[i] + half) * L::kSboV) = make_uint4(vq[0], vq[1], vq[2], vq[3]);
@@ -655,7 +681,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnA
   } else if (lane == 0) {
     // =============================== MMA issuer ===============================
     constexpr uint32_t idesc_s = tc::idesc_bf16(kBM, kBN, false, false);
-    constexpr uint32_t idesc_o = tc::idesc_bf16(kBM, D, false, true);
+    constexpr uint32_t idesc_o = tc::idesc_bf16(kBM, L::DV, false, true);
     auto issue_scores = [&](int j) -> bool {
       const int bb = j & 1, u = j >> 1, st = j % kStages;
       tr.mark(0, j);
