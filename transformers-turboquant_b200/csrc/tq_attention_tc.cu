@@ -207,42 +207,44 @@ __global__ void __launch_bounds__(128) rows_gemm_tc_kernel(const RowsGemmArgs a)
   if (warp == 0) tc::tmem_dealloc(tmem, NOUT < 32 ? 32 : NOUT);
 }
 
-// ---- fused attention (warp-specialised) ------------------------------------------------------
+// ---- fused attention (warp-specialised, two query tiles per CTA) --------------------------------
 //
-// One CTA = 128 query rows of one head.  Seventeen warps in three roles, coupled only by mbarriers:
-//   warps 0-7   softmax    two threads per query row (= tensor-memory lane): warp w and w+4 share the
-//                          rows of lane quadrant w%4 and split each 64-key tile into two 32-column
-//                          halves.  Load the scores, scale, mask, exchange the half-row maxima, keep
-//                          the running max / sum, write P (bf16) into tensor memory, rescale the output
-//                          accumulator when the max grew, run the epilogue.
-//   warps 8-15  producers  prefetch the next tile's packed bytes into registers, stage them in shared
-//                          memory, decode indices / sign bits / norms into the K_hat and V_hat
-//                          operand tiles (canonical core-matrix layout), up to kStages tiles ahead
-//   warp 16     MMA        one thread issues S = Q_cat K_hat^T for tile j+1, then O += P V_hat for tile j
-// Both A operands (the query tile and P) live in TENSOR MEMORY: shared-memory bandwidth, the scarcest
-// resource of this kernel, is spent only on the decoded K_hat / V_hat tiles.
-// Keys advance in tiles of 64.  S and P are double-buffered (index = tile parity), K_hat / V_hat /
-// staged bytes form a ring of kStages slots (index = tile % kStages).
+// One CTA owns TWO query tiles of 128 rows that read the same KV head -- two query heads of one GQA
+// group at the same positions, or (when the group size is odd) two consecutive position blocks of
+// one head -- so that every decoded K_hat / V_hat tile feeds 256 query rows.  Decoding is CUDA-core
+// work and the scarcest resource here; sharing it halves its cost per MMA.
 //
-// Barriers ("use" = how often the slot has been used before selects the mbarrier phase):
-//   pk_full[s]  256 producer arrivals : the packed bytes of tile j are staged in shared memory
-//   k_full[s]   256 producer arrivals : K_hat and the column scales of tile j are ready
-//   v_full[s]   256 producer arrivals : V_hat of tile j is ready
-//   k_empty[s]  tcgen05.commit        : the score MMA of tile j has consumed K_hat[s]
-//   v_empty[s]  tcgen05.commit        : the P V_hat MMA of tile j has consumed V_hat[s]
-//   s_full[b]   tcgen05.commit        : S[b] holds the scores of tile j
-//   s_empty[b]  256 softmax arrivals  : S[b] has been read into registers
-//   p_full[b]   256 softmax arrivals  : P[b] written (and O rescaled if needed)
-//   pv_done[b]  tcgen05.commit        : O += P V_hat of tile j finished (P[b] free, O at rest)
-//   q_full      256 softmax arrivals  : the query tile is in tensor memory
-//   xch[q]      64 arrivals           : the two warps of lane quadrant q exchanged their half-row maxima
+// Seventeen warps in three roles, coupled only by mbarriers with bounded waits:
+//   warps 0-3 / 4-7  softmax of tile A / B: thread r owns query row r (= tensor-memory lane r).  Load
+//                    the 64 scores of the key tile, scale, mask, running max (raised lazily) and sum,
+//                    write P (bf16) over the score columns, rescale O when the max grew, epilogue.
+//   warps 8-15       producers: prefetch the next key tile's packed bytes into registers, stage them
+//                    in shared memory, decode indices / sign bits / norms into the K_hat and V_hat
+//                    operand tiles (canonical core-matrix layout), up to kStages tiles ahead.
+//   warp 16          MMA: one thread issues, per key tile, S_t = Q_t K_hat^T and O_t += P_t V_hat for
+//                    both tiles, interleaved so that the tensor pipe works for one tile while the
+//                    other tile's softmax runs (ping-pong).
+// Tensor memory (512 columns at d = 128, all of it): rotated queries of A and B (2 x d/2 columns of
+// bf16 pairs, A operand of the first half of the score contraction), scores S_A, S_B (2 x 64 fp32
+// columns; P_t overwrites the first 32 columns of S_t as packed bf16 and is the A operand of P V_hat),
+// outputs O_A, O_B (2 x d fp32 columns).  The sketch half of the queries (q S^T) does not fit in tensor
+// memory any more and is an A operand in shared memory.
+//
+// Barriers (phase = key tile index, or use count of the ring slot):
+//   pk_full[2]  256 producer arrivals : packed bytes of tile j staged          (slot j & 1)
+//   k_full[s]   256 producer arrivals : K_hat and column scales of tile j ready (slot j % kStages)
+//   v_full[s]   256 producer arrivals : V_hat of tile j ready
+//   k_empty[s]  tcgen05.commit        : both score MMAs of tile j have consumed K_hat[s]
+//   v_empty[s]  tcgen05.commit        : both P V_hat MMAs of tile j have consumed V_hat[s]
+//   s_full[t]   tcgen05.commit        : S_t holds the scores of key tile j
+//   p_full[t]   128 softmax arrivals  : P_t written (and O_t rescaled if needed)
+//   pv_done[t]  tcgen05.commit        : O_t += P_t V_hat of key tile j finished
+//   q_full      256 softmax arrivals  : both query tiles are in tensor / shared memory
 
-constexpr int kBM = 128;          // query rows per CTA
+constexpr int kBM = 128;          // query rows per tile (two tiles per CTA)
 constexpr int kBN = 64;           // keys per tile
-constexpr int kStages = 3;        // K_hat / V_hat ring depth
-constexpr int kSoftmaxThreads = 256;
 constexpr int kProducers = 256;
-constexpr int kWsThreads = kSoftmaxThreads + kProducers + 32;
+constexpr int kWsThreads = 256 + kProducers + 32;
 constexpr int kMmaWarp = kWsThreads / 32 - 1;
 
 // Pair table: entry (i1 << B | i0) holds the bf16x2 word (C[i0], C[i1]).  Small tables of 4-byte
@@ -263,46 +265,46 @@ __device__ __forceinline__ void decode_group(const uint32_t* lut, uint32_t bits,
 template <int D, int BITS>
 struct WsSmem {
   static constexpr int G = D / 8, KB = BITS - 1, VB = BITS;
+  static constexpr int kStages = BITS == 4 ? 2 : 3;    // K_hat / V_hat ring depth (shared memory permitting)
+  static constexpr uint32_t kQsBytes = kBM * D * 2;    // sketch half of one query tile, K-major
   static constexpr uint32_t kKStage = kBN * 2 * D * 2;
-  static constexpr int DV = D + 16;                   // value coordinates + a 16-wide block whose first
-                                                      // row is all ones: P V_hat then also yields the row sums
-  static constexpr uint32_t kVStage = kBN * DV * 2;
-  static constexpr uint32_t kIdxK = kBN * G * KB;     // packed key-index bytes per tile
+  static constexpr uint32_t kVStage = kBN * D * 2;
+  static constexpr uint32_t kIdxK = kBN * G * KB;      // packed key-index bytes per tile
   static constexpr uint32_t kSgn = kBN * G;
   static constexpr uint32_t kIdxV = kBN * G * VB;
   static constexpr uint32_t kPkStage = kIdxK + kSgn + kIdxV;
-  static constexpr uint32_t kKOff = 0;
+  static constexpr uint32_t kQsOff = 0;
+  static constexpr uint32_t kKOff = kQsOff + 2 * kQsBytes;
   static constexpr uint32_t kVOff = kKOff + kStages * kKStage;
   static constexpr uint32_t kPkOff = kVOff + kStages * kVStage;
-  static constexpr uint32_t kTotal = kPkOff + kStages * kPkStage;
+  static constexpr uint32_t kTotal = kPkOff + 2 * kPkStage;
+  static constexpr uint32_t kSboQs = G * 128;           // K-major [rows, D]
   static constexpr uint32_t kSboK = 2 * G * 128;        // K-major [keys, 2D]
   static constexpr uint32_t kSboV = 128;                // MN-major [D, kBN]: 8-coordinate chunks adjacent
-  static constexpr uint32_t kLboV = (G + 2) * 128;      // ... 8-key groups G+2 core matrices apart
+  static constexpr uint32_t kLboV = G * 128;            // ... 8-key groups G core matrices apart
   // tensor-memory columns
-  static constexpr uint32_t kColS = 0;                  // S[2]: 2 x 64
-  static constexpr uint32_t kColO = 128;                // O: D value columns, then the row sum in column D
-  static constexpr uint32_t kColQ = 128 + DV;           // Q_cat: 2D bf16 = D columns
-  static constexpr uint32_t kColP = kColQ + D;          // P[2]: 2 x 32 (64 bf16 each)
+  static constexpr uint32_t kColQ = 0;                  // rotated queries: 2 x D/2
+  static constexpr uint32_t kColS = D;                  // S_A, S_B: 2 x 64 (P_t aliases the first 32 of S_t)
+  static constexpr uint32_t kColO = D + 2 * kBN;        // O_A, O_B: 2 x D
   static constexpr uint32_t kCols = 512;
-  static_assert(kColP + kBN <= kCols, "tensor memory over-subscribed");
+  static_assert(kColO + 2 * D <= kCols, "tensor memory over-subscribed");
 };
 
 template <int D, int BITS>
-__global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot) {
+__global__ void __launch_bounds__(kWsThreads, 1)
+attention_ws_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const int pair_heads) {
   using L = WsSmem<D, BITS>;
-  constexpr int G = L::G, KB = L::KB, VB = L::VB, GP = G / 2;
-  constexpr int HC = kBN / 2;     // score columns per softmax thread
+  constexpr int G = L::G, KB = L::KB, VB = L::VB, GP = G / 2, kStages = L::kStages;
   constexpr float kLog2e = 1.4426950408889634f;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // n_k * sm_scale * log2(e) per key column.  Written by the producers up to kStages tiles ahead of the score
-  // MMA and read by the softmax warps up to two tiles behind it: 8 slots (tile & 7) can never collide.
-  __shared__ float cscale[8][kBN];
-  __shared__ float rho_s[kStages][kBN];   // rn_k / n_k
-  __shared__ float nv_s[kStages][kBN];    // value norms
-  __shared__ float xmax[2][2][kBM];       // [tile parity][column half][row]: half-row maxima exchanged
+  // MMA and read by the softmax warps one tile behind it: 8 slots (tile & 7) can never collide.
+  __shared__ __align__(16) float cscale[8][kBN];
+  __shared__ float rho_s[2][kBN];         // rn_k / n_k      (producer-internal, slot j & 1)
+  __shared__ float nv_s[2][kBN];          // value norms
   __shared__ uint32_t lutK[1 << (2 * KB)];  // index pair -> bf16x2 centroids
   __shared__ uint32_t lutV[1 << (2 * VB)];
-  __shared__ __align__(8) uint64_t bars[5 * kStages + 8 + 4 + 1];
+  __shared__ __align__(8) uint64_t bars[4 * kStages + 2 + 6 + 1];
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
   volatile int* abort_flag = &s_abort;
@@ -312,14 +314,22 @@ __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnA
   __syncthreads();
   if (s_abort) return;  // an earlier bounded wait expired: do nothing rather than risk another
 
-  const int64_t b = blockIdx.z, h = blockIdx.y;
-  const int64_t bh = b * a.Hq + h;
-  const int64_t kv_base = (b * a.Hkv + h / (a.Hq / a.Hkv)) * a.Sk;
-  // heaviest (latest) query tiles first: they have the most key tiles under the causal mask
-  const int q0 = (int)(gridDim.x - 1 - blockIdx.x) * kBM;
+  // ---- which two query tiles -------------------------------------------------------------
+  const int64_t b = blockIdx.z;
+  const int xblk = (int)(gridDim.x - 1 - blockIdx.x);  // heaviest (latest) position blocks first
+  int64_t head[2];
+  int q0[2];
+  if (pair_heads) {
+    head[0] = 2 * (int64_t)blockIdx.y; head[1] = head[0] + 1;
+    q0[0] = q0[1] = xblk * kBM;
+  } else {
+    head[0] = head[1] = blockIdx.y;
+    q0[0] = 2 * xblk * kBM; q0[1] = q0[0] + kBM;
+  }
+  const int64_t kv_base = (b * a.Hkv + head[0] / (a.Hq / a.Hkv)) * a.Sk;
   const int shift = (int)(a.Sk - a.Sq);
   int k_end = (int)a.Sk;
-  if (a.causal) k_end = min(k_end, min(q0 + kBM - 1, (int)a.Sq - 1) + shift + 1);
+  if (a.causal) k_end = min(k_end, min(q0[1] + kBM - 1, (int)a.Sq - 1) + shift + 1);
   const int n_tiles = (k_end + kBN - 1) / kBN;
 
   const uint32_t bar0 = tc::smem_u32(&bars[0]);
@@ -328,12 +338,10 @@ __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnA
   auto k_empty = [&](int i) { return bar0 + 8u * (2 * kStages + i); };
   auto v_empty = [&](int i) { return bar0 + 8u * (3 * kStages + i); };
   auto pk_full = [&](int i) { return bar0 + 8u * (4 * kStages + i); };
-  auto s_full = [&](int i) { return bar0 + 8u * (5 * kStages + i); };
-  auto s_empty = [&](int i) { return bar0 + 8u * (5 * kStages + 2 + i); };
-  auto p_full = [&](int i) { return bar0 + 8u * (5 * kStages + 4 + i); };
-  auto pv_done = [&](int i) { return bar0 + 8u * (5 * kStages + 6 + i); };
-  auto xch = [&](int i) { return bar0 + 8u * (5 * kStages + 8 + i); };
-  const uint32_t q_full = bar0 + 8u * (5 * kStages + 12);
+  auto s_full = [&](int i) { return bar0 + 8u * (4 * kStages + 2 + i); };
+  auto p_full = [&](int i) { return bar0 + 8u * (4 * kStages + 4 + i); };
+  auto pv_done = [&](int i) { return bar0 + 8u * (4 * kStages + 6 + i); };
+  const uint32_t q_full = bar0 + 8u * (4 * kStages + 8);
 
   if (tid == 0) {
     for (int i = 0; i < kStages; ++i) {
@@ -341,16 +349,14 @@ __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnA
       tc::mbar_init(v_full(i), kProducers);
       tc::mbar_init(k_empty(i), 1);
       tc::mbar_init(v_empty(i), 1);
-      tc::mbar_init(pk_full(i), kProducers);
     }
     for (int i = 0; i < 2; ++i) {
+      tc::mbar_init(pk_full(i), kProducers);
       tc::mbar_init(s_full(i), 1);
-      tc::mbar_init(s_empty(i), kSoftmaxThreads);
-      tc::mbar_init(p_full(i), kSoftmaxThreads);
+      tc::mbar_init(p_full(i), kBM);
       tc::mbar_init(pv_done(i), 1);
     }
-    for (int i = 0; i < 4; ++i) tc::mbar_init(xch(i), 64);
-    tc::mbar_init(q_full, kSoftmaxThreads);
+    tc::mbar_init(q_full, 2 * kBM);
     tc::fence_mbar_init();
   }
   if (warp == kMmaWarp) tc::tmem_alloc(tc::smem_u32(&tmem_slot), L::kCols);
@@ -360,7 +366,6 @@ __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnA
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t tmem_base = tmem_slot;
-  const uint32_t tmem_o = tmem_base + L::kColO;
   bool ok = true;
   Tracer tr(g_trace_on != 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 &&
                 (warp == 0 || warp == 8 || warp == kMmaWarp),
@@ -368,14 +373,16 @@ __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnA
 
   if (warp < 8) {
     // =============================== softmax warps ===============================
-    const int quad = warp % 4, chalf = warp / 4;
-    const int row = quad * 32 + lane;
-    const int qi = q0 + row;
-    const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
-    {  // query row -> tensor memory: 2D bf16 = D columns, each of the row's two threads stores D/2
+    const int tl = warp / 4;                    // query tile of this warp
+    const int row = (warp % 4) * 32 + lane;
+    const int qi = q0[tl] + row;
+    const int64_t qrow = (b * a.Hq + head[tl]) * a.Sq + qi;
+    const uint32_t lane_base = (uint32_t)((warp % 4) * 32) << 16;
+    const uint32_t tmem_s = tmem_base + L::kColS + tl * kBN;
+    const uint32_t tmem_o = tmem_base + L::kColO + tl * D;
+    {  // query row: rotated half (D bf16 = D/2 columns) -> tensor memory, sketch half -> shared memory
       const bool live = qi < a.Sq;
-      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.q_cat) +
-                                                        (bh * a.Sq + qi) * 2 * D) + chalf * (D / 8);
+      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.q_cat) + qrow * 2 * D);
 #pragma unroll 1
       for (int c0 = 0; c0 < D / 2; c0 += 32) {
         uint32_t w[32];
@@ -385,126 +392,118 @@ __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnA
           if (live) v = src[c0 / 4 + i];
           w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
         }
-        tc::tmem_st32(tmem_base + L::kColQ + lane_base + chalf * (D / 2) + c0, w);
+        tc::tmem_st32(tmem_base + L::kColQ + tl * (D / 2) + lane_base + c0, w);
+      }
+      uint8_t* dst = smem_raw + L::kQsOff + tl * L::kQsBytes + (row / 8) * L::kSboQs + (row % 8) * 16;
+#pragma unroll 8
+      for (int c = 0; c < G; ++c) {
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (live) v = src[G + c];
+        *reinterpret_cast<uint4*>(dst + c * 128) = v;
       }
       tc::wait_st();
+      tc::fence_async_smem();
       tc::fence_before_sync();
       tc::mbar_arrive(q_full);
     }
-    float m_run = -INFINITY;
+    float m_run = -INFINITY, l_run = 0.f;
     for (int j = 0; j < n_tiles && ok; ++j) {
-      const int bb = j & 1, u = j >> 1, k0 = j * kBN;
-      const int kc0 = k0 + chalf * HC;  // first key column of this thread
+      const int k0 = j * kBN;
       tr.mark(0, j);
-      if (!(ok = tc::mbar_wait_or_abort(s_full(bb), u & 1, abort_flag))) break;
+      if (!(ok = tc::mbar_wait_or_abort(s_full(tl), j & 1, abort_flag))) break;
       tc::fence_after_sync();
       tr.mark(1, j);
-      float t[HC];
+      float t[kBN];
       {
         uint32_t raw[32];
-        tc::tmem_ld32(tmem_base + L::kColS + lane_base + bb * kBN + chalf * HC, raw);
+        tc::tmem_ld32(tmem_s + lane_base, raw);
         tc::wait_ld();
 #pragma unroll
         for (int c = 0; c < 32; ++c) t[c] = __uint_as_float(raw[c]);
+        tc::tmem_ld32(tmem_s + lane_base + 32, raw);
+        tc::wait_ld();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) t[32 + c] = __uint_as_float(raw[c]);
       }
-      tc::fence_before_sync();
-      tc::mbar_arrive(s_empty(bb));
       tr.mark(2, j);
       float mx = -INFINITY;
-      const bool edge = (k0 + kBN > a.Sk) || (a.causal && k0 + kBN - 1 > q0 + shift) || a.mask != nullptr;
+      const bool edge = (k0 + kBN > a.Sk) || (a.causal && k0 + kBN - 1 > q0[tl] + shift) || a.mask != nullptr;
       if (!edge) {
 #pragma unroll
-        for (int c4 = 0; c4 < HC; c4 += 4) {
-          const float4 cs = *reinterpret_cast<const float4*>(&cscale[j & 7][chalf * HC + c4]);
+        for (int c4 = 0; c4 < kBN; c4 += 4) {
+          const float4 cs = *reinterpret_cast<const float4*>(&cscale[j & 7][c4]);
           t[c4] *= cs.x; t[c4 + 1] *= cs.y; t[c4 + 2] *= cs.z; t[c4 + 3] *= cs.w;
           mx = fmaxf(mx, fmaxf(fmaxf(t[c4], t[c4 + 1]), fmaxf(t[c4 + 2], t[c4 + 3])));
         }
       } else {
         const float* mrow = (a.mask != nullptr && qi < a.Sq)
-                                ? a.mask + b * a.mask_stride_b + (int64_t)qi * a.mask_stride_q + kc0
+                                ? a.mask + b * a.mask_stride_b + (int64_t)qi * a.mask_stride_q + k0
                                 : nullptr;
 #pragma unroll
-        for (int c = 0; c < HC; ++c) {
-          const int k = kc0 + c;
-          float v = t[c] * cscale[j & 7][chalf * HC + c];
+        for (int c = 0; c < kBN; ++c) {
+          const int k = k0 + c;
+          float v = t[c] * cscale[j & 7][c];
           if (mrow != nullptr && k < a.Sk) v = fmaf(mrow[c], kLog2e, v);
           if (k >= a.Sk || (a.causal && k > qi + shift)) v = -INFINITY;
           t[c] = v;
           mx = fmaxf(mx, v);
         }
       }
-      // the other half of the row lives in the partner warp: swap maxima through shared memory
-      // (slots alternate with the tile parity: a slot is rewritten two exchanges later, after the
-      // partner has arrived at the exchange in between, i.e. after it has read this one)
-      xmax[bb][chalf][row] = mx;
-      tc::mbar_arrive(xch(quad));
-      if (!(ok = tc::mbar_wait_or_abort(xch(quad), j & 1, abort_flag))) break;
-      mx = fmaxf(mx, xmax[bb][1 - chalf][row]);
       // running max, raised lazily: rescaling O costs a tensor-memory round trip, so the max only
-      // moves when some row of the quadrant outgrew it by more than 2^8 (P stays below 256)
+      // moves when some row of the warp outgrew it by more than 2^8 (P stays below 256)
       const float m_cand = fmaxf(m_run, mx);
-      const bool grow = __any_sync(0xffffffffu, m_cand > m_run + 8.f);  // identical in both warps of the quadrant
+      const bool grow = __any_sync(0xffffffffu, m_cand > m_run + 8.f);
       float alpha = 1.f;
       if (grow) {
         alpha = (m_run == -INFINITY) ? 0.f : tc::fast_exp2(m_run - m_cand);
         m_run = m_cand;
       }
       const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
-      uint32_t pw[HC / 2];
+      // P (packed bf16) goes over the first 32 score columns; this row's scores are all in registers
+      float psum = 0.f;
 #pragma unroll
-      for (int c = 0; c < HC / 2; ++c)
-        pw[c] = tc::pack_bf16x2(tc::fast_exp2(t[2 * c] - m_use), tc::fast_exp2(t[2 * c + 1] - m_use));
+      for (int hblk = 0; hblk < 2; ++hblk) {
+        uint32_t pw[16];
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          const float p0 = tc::fast_exp2(t[32 * hblk + 2 * c] - m_use);
+          const float p1 = tc::fast_exp2(t[32 * hblk + 2 * c + 1] - m_use);
+          psum += p0 + p1;
+          pw[c] = tc::pack_bf16x2(p0, p1);
+        }
+        tc::tmem_st16(tmem_s + lane_base + 16 * hblk, pw);
+      }
+      l_run = l_run * alpha + psum;
       tr.mark(3, j);
-      if (u >= 1 && !(ok = tc::mbar_wait_or_abort(pv_done(bb), (u - 1) & 1, abort_flag))) break;  // P[bb] free
-      tc::fence_after_sync();
-      tr.mark(4, j);
-      tc::tmem_st16(tmem_base + L::kColP + lane_base + bb * (kBN / 2) + chalf * (HC / 2), pw);
       if (grow && j >= 1) {
-        // O must be at rest: wait for the previous tile's P V_hat; each half rescales D/2 columns
-        if (!(ok = tc::mbar_wait_or_abort(pv_done((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag))) break;
+        // O_t must be at rest: wait for the previous key tile's P V_hat
+        if (!(ok = tc::mbar_wait_or_abort(pv_done(tl), (j - 1) & 1, abort_flag))) break;
         tc::fence_after_sync();
 #pragma unroll 1
-        for (int c0 = 0; c0 < D / 2; c0 += 32) {
+        for (int c0 = 0; c0 < D; c0 += 32) {
           uint32_t raw[32];
-          const uint32_t addr = tmem_o + lane_base + chalf * (D / 2) + c0;
-          tc::tmem_ld32(addr, raw);
+          tc::tmem_ld32(tmem_o + lane_base + c0, raw);
           tc::wait_ld();
 #pragma unroll
           for (int c = 0; c < 32; ++c) raw[c] = __float_as_uint(__uint_as_float(raw[c]) * alpha);
-          tc::tmem_st32(addr, raw);
-        }
-        if (chalf == 1) {  // the row-sum block rides along with the second half
-          uint32_t raw[16];
-          tc::tmem_ld16(tmem_o + lane_base + D, raw);
-          tc::wait_ld();
-#pragma unroll
-          for (int c = 0; c < 16; ++c) raw[c] = __float_as_uint(__uint_as_float(raw[c]) * alpha);
-          tc::tmem_st16(tmem_o + lane_base + D, raw);
+          tc::tmem_st32(tmem_o + lane_base + c0, raw);
         }
       }
       tc::wait_st();
       tc::fence_before_sync();
-      tc::mbar_arrive(p_full(bb));
-      tr.mark(5, j);
+      tc::mbar_arrive(p_full(tl));
+      tr.mark(4, j);
     }
     // ---- epilogue: normalise and store the rotated output row ----
-    if (ok && n_tiles > 0)
-      ok = tc::mbar_wait_or_abort(pv_done((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, abort_flag);
+    if (ok && n_tiles > 0) ok = tc::mbar_wait_or_abort(pv_done(tl), (n_tiles - 1) & 1, abort_flag);
     if (ok) {
       tc::fence_after_sync();
-      float l_tot;
-      {  // column D of the accumulator is sum_k P[row][k] (the ones row of V_hat)
-        uint32_t raw[16];
-        tc::tmem_ld16(tmem_o + lane_base + D, raw);
-        tc::wait_ld();
-        l_tot = __uint_as_float(raw[0]);
-      }
-      const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-      __nv_bfloat16* dst = o_rot + (bh * a.Sq + qi) * D + chalf * (D / 2);
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      __nv_bfloat16* dst = o_rot + qrow * D;
 #pragma unroll 1
-      for (int c0 = 0; c0 < D / 2; c0 += 32) {
+      for (int c0 = 0; c0 < D; c0 += 32) {
         uint32_t raw[32];
-        tc::tmem_ld32(tmem_o + lane_base + chalf * (D / 2) + c0, raw);
+        tc::tmem_ld32(tmem_o + lane_base + c0, raw);
         tc::wait_ld();
         if (qi < a.Sq) {
 #pragma unroll
@@ -521,7 +520,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnA
     }
   } else if (warp < kMmaWarp) {
     // =============================== producer warps ===============================
-    const int p = tid - kSoftmaxThreads;
+    const int p = tid - 256;
     constexpr int UK = L::kIdxK / 8, US = L::kSgn / 8, UV = L::kIdxV / 8;  // 8-byte units per tile
     constexpr int NK = (UK + kProducers - 1) / kProducers, NV = (UV + kProducers - 1) / kProducers;
     constexpr int NI = (kBN * GP + kProducers - 1) / kProducers;  // (key, 16-coordinate) items per thread
@@ -560,21 +559,12 @@ __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnA
       ikey[i] = (e % 8) + 8 * (e / (8 * GP));
       igp[i] = (e / 8) % GP;
     }
-    // constant part of every V_hat stage: coordinate row D is all ones (row sums), rows D+1..D+15 zero
-    for (int e = p; e < kStages * kBN * 2; e += kProducers) {
-      const int st = e / (kBN * 2), key = (e / 2) % kBN, blk = e % 2;
-      *reinterpret_cast<uint4*>(smem_raw + L::kVOff + st * L::kVStage + (key / 8) * L::kLboV + (key % 8) * 16 +
-                                (G + blk) * L::kSboV) = make_uint4(blk == 0 ? 0x00003F80u : 0u, 0u, 0u, 0u);
-    }
     if (n_tiles > 0) prefetch(0);
     for (int j = 0; j < n_tiles && ok; ++j) {
-      const int st = j % kStages, u = j / kStages;
-      uint8_t* pk = smem_raw + L::kPkOff + st * L::kPkStage;
-      // slot st (staged bytes, column scales, K_hat) is free once tile j-kStages' score MMA has drained;
-      // its V_hat decode by this same thread is long finished
+      const int st = j % kStages, u = j / kStages, ps = j & 1;
+      uint8_t* pk = smem_raw + L::kPkOff + ps * L::kPkStage;
       tr.mark(0, j);
-      if (u >= 1 && !(ok = tc::mbar_wait_or_abort(k_empty(st), (u - 1) & 1, abort_flag))) break;
-      tr.mark(1, j);
+      // staging slot ps was last read by this group's decode of tile j-2 (ordered by pk_full of tile j-1)
 #pragma unroll
       for (int i = 0; i < NK; ++i)
         if (i * kProducers + p < UK) *reinterpret_cast<uint2*>(pk + (i * kProducers + p) * 8) = rk[i];
@@ -586,15 +576,18 @@ __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnA
       if (p < kBN) {
         const float nk = fp16_value((uint16_t)rn[0]);
         cscale[j & 7][p] = nk * a.sm_scale * kLog2e;
-        rho_s[st][p] = nk > 0.f ? fp16_value((uint16_t)rn[1]) / nk : 0.f;
-        nv_s[st][p] = fp16_value((uint16_t)rn[2]);
+        rho_s[ps][p] = nk > 0.f ? fp16_value((uint16_t)rn[1]) / nk : 0.f;
+        nv_s[ps][p] = fp16_value((uint16_t)rn[2]);
       }
       // every producer's staged bytes must be visible before anyone decodes (a bounded wait
       // instead of bar.sync, so that a fault elsewhere cannot strand part of the group)
-      tc::mbar_arrive(pk_full(st));
-      if (!(ok = tc::mbar_wait_or_abort(pk_full(st), u & 1, abort_flag))) break;
-      tr.mark(2, j);
+      tc::mbar_arrive(pk_full(ps));
+      if (!(ok = tc::mbar_wait_or_abort(pk_full(ps), (j >> 1) & 1, abort_flag))) break;
+      tr.mark(1, j);
       if (j + 1 < n_tiles) prefetch((j + 1) * kBN);  // in flight while this tile is decoded
+      // K_hat[st] is free once both score MMAs of tile j-kStages have drained
+      if (u >= 1 && !(ok = tc::mbar_wait_or_abort(k_empty(st), (u - 1) & 1, abort_flag))) break;
+      tr.mark(2, j);
       // ---- keys: centroid values and +-rho sign tile ----
       uint8_t* Kd = smem_raw + L::kKOff + st * L::kKStage;
       {
@@ -609,7 +602,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnA
             gw[i][0] = (uint32_t)w & ((1u << (8 * KB)) - 1);
             gw[i][1] = (uint32_t)(w >> (8 * KB));
             sb[i] = ~(uint32_t)*reinterpret_cast<const uint16_t*>(pk + L::kIdxK + ikey[i] * G + igp[i] * 2);
-            const float rho = rho_s[st][ikey[i]];
+            const float rho = rho_s[ps][ikey[i]];
             rr[i] = tc::pack_bf16x2(rho, rho);
           }
         }
@@ -635,7 +628,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnA
       tc::fence_async_smem();
       tc::mbar_arrive(k_full(st));
       tr.mark(3, j);
-      // ---- values: V_hat[st] is free once tile j-kStages' P V_hat has drained ----
+      // ---- values: V_hat[st] is free once both P V_hat MMAs of tile j-kStages have drained ----
       if (u >= 1 && !(ok = tc::mbar_wait_or_abort(v_empty(st), (u - 1) & 1, abort_flag))) break;
       tr.mark(4, j);
       uint8_t* Vd = smem_raw + L::kVOff + st * L::kVStage;
@@ -652,7 +645,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnA
             for (int x = 0; x < VB; ++x) w |= (uint64_t)sv[x] << (16 * x);
             gw[i][0] = (uint32_t)w & (VB == 4 ? 0xffffffffu : ((1u << (8 * (VB & 3))) - 1));
             gw[i][1] = (uint32_t)(w >> (8 * VB));
-            const float nvf = nv_s[st][ikey[i]];
+            const float nvf = nv_s[ps][ikey[i]];
             nv2[i] = __floats2bfloat162_rn(nvf, nvf);
           }
         }
@@ -681,43 +674,69 @@ __global__ void __launch_bounds__(kWsThreads, 1) attention_ws_kernel(const AttnA
   } else if (lane == 0) {
     // =============================== MMA issuer ===============================
     constexpr uint32_t idesc_s = tc::idesc_bf16(kBM, kBN, false, false);
-    constexpr uint32_t idesc_o = tc::idesc_bf16(kBM, L::DV, false, true);
-    auto issue_scores = [&](int j) -> bool {
-      const int bb = j & 1, u = j >> 1, st = j % kStages;
-      tr.mark(0, j);
-      if (!tc::mbar_wait_or_abort(k_full(st), (j / kStages) & 1, abort_flag)) return false;
-      tr.mark(1, j);
-      if (u >= 1 && !tc::mbar_wait_or_abort(s_empty(bb), (u - 1) & 1, abort_flag)) return false;
-      tc::fence_after_sync();
-      tr.mark(2, j);
+    constexpr uint32_t idesc_o = tc::idesc_bf16(kBM, D, false, true);
+    // S_t = q_rot_t K_hat[:, :D]^T (A in tensor memory) + q_s_t K_hat[:, D:]^T (A in shared memory)
+    auto issue_scores = [&](int tl, int j) {
+      const int st = j % kStages;
+      const uint32_t d_s = tmem_base + L::kColS + tl * kBN;
       const uint64_t kdesc = tc::smem_desc(tc::smem_u32(smem_raw + L::kKOff + st * L::kKStage), 128, L::kSboK);
+      const uint64_t qsdesc = tc::smem_desc(tc::smem_u32(smem_raw + L::kQsOff + tl * L::kQsBytes), 128, L::kSboQs);
 #pragma unroll
-      for (int ks = 0; ks < 2 * D / 16; ++ks)
-        tc::mma_bf16_ts(tmem_base + L::kColS + bb * kBN, tmem_base + L::kColQ + ks * 8,
-                        kdesc + (uint64_t)(ks * 256 >> 4), idesc_s, ks > 0);
-      tc::mma_commit(s_full(bb));
-      tc::mma_commit(k_empty(st));
-      tr.mark(3, j);
-      return true;
+      for (int ks = 0; ks < D / 16; ++ks)
+        tc::mma_bf16_ts(d_s, tmem_base + L::kColQ + tl * (D / 2) + ks * 8, kdesc + (uint64_t)(ks * 256 >> 4), idesc_s,
+                        ks > 0);
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks)
+        tc::mma_bf16(d_s, qsdesc + (uint64_t)(ks * 256 >> 4), kdesc + (uint64_t)((D / 16 + ks) * 256 >> 4), idesc_s,
+                     1u);
+      tc::mma_commit(s_full(tl));
     };
-    ok = tc::mbar_wait_or_abort(q_full, 0, abort_flag);
-    if (ok && n_tiles > 0) ok = issue_scores(0);
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      const int bb = j & 1, u = j >> 1, st = j % kStages;
-      if (j + 1 < n_tiles && !(ok = issue_scores(j + 1))) break;
-      tr.mark(4, j);
-      if (!(ok = tc::mbar_wait_or_abort(v_full(st), (j / kStages) & 1, abort_flag))) break;
-      if (!(ok = tc::mbar_wait_or_abort(p_full(bb), u & 1, abort_flag))) break;
-      tc::fence_after_sync();
-      tr.mark(5, j);
+    auto issue_pv = [&](int tl, int j) {
+      const int st = j % kStages;
       const uint64_t vdesc = tc::smem_desc(tc::smem_u32(smem_raw + L::kVOff + st * L::kVStage), L::kLboV, L::kSboV);
 #pragma unroll
       for (int ks = 0; ks < kBN / 16; ++ks)
-        tc::mma_bf16_ts(tmem_o, tmem_base + L::kColP + bb * (kBN / 2) + ks * 8,
+        tc::mma_bf16_ts(tmem_base + L::kColO + tl * D, tmem_base + L::kColS + tl * kBN + ks * 8,
                         vdesc + (uint64_t)(ks * 2 * L::kLboV >> 4), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
-      tc::mma_commit(pv_done(bb));
+      tc::mma_commit(pv_done(tl));
+    };
+    ok = tc::mbar_wait_or_abort(q_full, 0, abort_flag);
+    if (ok && n_tiles > 0) {
+      tr.mark(0, 0);
+      ok = tc::mbar_wait_or_abort(k_full(0), 0, abort_flag);
+      if (ok) {
+        tc::fence_after_sync();
+        issue_scores(0, 0);
+        issue_scores(1, 0);
+        tc::mma_commit(k_empty(0));
+      }
+    }
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int st = j % kStages, u = j / kStages;
+      const bool more = j + 1 < n_tiles;
+      const int st1 = (j + 1) % kStages;
+      tr.mark(1, j);
+      if (!(ok = tc::mbar_wait_or_abort(v_full(st), u & 1, abort_flag))) break;
+      if (!(ok = tc::mbar_wait_or_abort(p_full(0), j & 1, abort_flag))) break;
+      tc::fence_after_sync();
+      tr.mark(2, j);
+      issue_pv(0, j);
+      if (more) {
+        if (!(ok = tc::mbar_wait_or_abort(k_full(st1), ((j + 1) / kStages) & 1, abort_flag))) break;
+        tc::fence_after_sync();
+        issue_scores(0, j + 1);  // overwrites S_A / P_A: ordered after issue_pv(0, j) on the tensor pipe
+      }
+      tr.mark(3, j);
+      if (!(ok = tc::mbar_wait_or_abort(p_full(1), j & 1, abort_flag))) break;
+      tc::fence_after_sync();
+      tr.mark(4, j);
+      issue_pv(1, j);
       tc::mma_commit(v_empty(st));
-      tr.mark(6, j);
+      if (more) {
+        issue_scores(1, j + 1);
+        tc::mma_commit(k_empty(st1));
+      }
+      tr.mark(5, j);
     }
   }
   if (!ok && atomicExch(&s_abort, 2) != 2) record_fault();  // one fault per CTA
@@ -764,10 +783,14 @@ static int launch_attention_tc(const AttnArgs& a, int64_t B, __nv_bfloat16* o_ro
   constexpr size_t smem = WsSmem<D, BITS>::kTotal > 120 * 1024 ? WsSmem<D, BITS>::kTotal : 120 * 1024;
   auto kern = attention_ws_kernel<D, BITS>;
   TQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  dim3 grid((unsigned)((a.Sq + kBM - 1) / kBM), (unsigned)a.Hq, (unsigned)B);
+  // two query tiles per CTA: two heads of one GQA group when the group size is even, otherwise
+  // two consecutive position blocks of one head
+  const int pair_heads = ((a.Hq / a.Hkv) % 2 == 0) ? 1 : 0;
+  const int64_t blocks = (a.Sq + kBM - 1) / kBM;
+  dim3 grid((unsigned)(pair_heads ? blocks : (blocks + 1) / 2), (unsigned)(pair_heads ? a.Hq / 2 : a.Hq), (unsigned)B);
   {
     ProfScope prof(kProfAttention, stream);
-    kern<<<grid, kWsThreads, smem, stream>>>(a, o_rot);
+    kern<<<grid, kWsThreads, smem, stream>>>(a, o_rot, pair_heads);
   }
   TQ_CUDA_OK(cudaGetLastError());
   return TQ_OK;
