@@ -9,8 +9,9 @@
 // Estimator algebra (reference compressors.py:201-224, kernels/attention.py:380-461):
 //   score(q,k) = n_k <q_rot, C[idx_k]> + coeff rn_k <q_s, sgn_k>
 //              = n_k * ( <q_rot, C[idx_k]> + <coeff q_s, (rn_k/n_k) sgn_k> )
-// so one MMA over the concatenated contraction dimension [C[idx] ; (rn/n) sgn] of length 2d
-// followed by a per-key column scale n_k * sm_scale * log2(e) gives the softmax argument.
+//              = < [q_rot | coeff q_s] , [ n_k C[idx_k] ; rn_k sgn_k ] >
+// so one MMA over the concatenated contraction dimension of length 2d, with the norms folded into the
+// decoded key operand, gives the raw score; the softmax only applies the constant sm_scale * log2(e).
 //
 // Every device-side wait is bounded; when one expires the kernel bumps a fault counter,
 // frees its tensor memory and returns, and later launches return immediately.
@@ -297,10 +298,8 @@ attention_ws_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
   constexpr int G = L::G, KB = L::KB, VB = L::VB, GP = G / 2, kStages = L::kStages;
   constexpr float kLog2e = 1.4426950408889634f;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  // n_k * sm_scale * log2(e) per key column.  Written by the producers up to kStages tiles ahead of the score
-  // MMA and read by the softmax warps one tile behind it: 8 slots (tile & 7) can never collide.
-  __shared__ __align__(16) float cscale[8][kBN];
-  __shared__ float rho_s[2][kBN];         // rn_k / n_k      (producer-internal, slot j & 1)
+  __shared__ float nk_s[2][kBN];          // key norms            (producer-internal, slot j & 1)
+  __shared__ float rho_s[2][kBN];         // key residual norms
   __shared__ float nv_s[2][kBN];          // value norms
   __shared__ uint32_t lutK[1 << (2 * KB)];  // index pair -> bf16x2 centroids
   __shared__ uint32_t lutV[1 << (2 * VB)];
@@ -407,6 +406,7 @@ attention_ws_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
       tc::mbar_arrive(q_full);
     }
     float m_run = -INFINITY, l_run = 0.f;
+    const float cexp = a.sm_scale * kLog2e, rcexp = 1.f / cexp;  // K_hat carries the key norms: S is the raw score
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int k0 = j * kBN;
       tr.mark(0, j);
@@ -429,12 +429,11 @@ attention_ws_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
       float mx = -INFINITY;
       const bool edge = (k0 + kBN > a.Sk) || (a.causal && k0 + kBN - 1 > q0[tl] + shift) || a.mask != nullptr;
       if (!edge) {
+        // raw scores: the positive constant sm_scale*log2(e) is applied to the maximum and inside the exp2
 #pragma unroll
-        for (int c4 = 0; c4 < kBN; c4 += 4) {
-          const float4 cs = *reinterpret_cast<const float4*>(&cscale[j & 7][c4]);
-          t[c4] *= cs.x; t[c4 + 1] *= cs.y; t[c4 + 2] *= cs.z; t[c4 + 3] *= cs.w;
+        for (int c4 = 0; c4 < kBN; c4 += 4)
           mx = fmaxf(mx, fmaxf(fmaxf(t[c4], t[c4 + 1]), fmaxf(t[c4 + 2], t[c4 + 3])));
-        }
+        mx *= cexp;
       } else {
         const float* mrow = (a.mask != nullptr && qi < a.Sq)
                                 ? a.mask + b * a.mask_stride_b + (int64_t)qi * a.mask_stride_q + k0
@@ -442,10 +441,10 @@ attention_ws_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
 #pragma unroll
         for (int c = 0; c < kBN; ++c) {
           const int k = k0 + c;
-          float v = t[c] * cscale[j & 7][c];
+          float v = t[c] * cexp;
           if (mrow != nullptr && k < a.Sk) v = fmaf(mrow[c], kLog2e, v);
           if (k >= a.Sk || (a.causal && k > qi + shift)) v = -INFINITY;
-          t[c] = v;
+          t[c] = v * rcexp;  // back to raw units: the exp2 below rescales (-inf stays -inf)
           mx = fmaxf(mx, v);
         }
       }
@@ -466,8 +465,8 @@ attention_ws_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
         uint32_t pw[16];
 #pragma unroll
         for (int c = 0; c < 16; ++c) {
-          const float p0 = tc::fast_exp2(t[32 * hblk + 2 * c] - m_use);
-          const float p1 = tc::fast_exp2(t[32 * hblk + 2 * c + 1] - m_use);
+          const float p0 = tc::fast_exp2(fmaf(t[32 * hblk + 2 * c], cexp, -m_use));
+          const float p1 = tc::fast_exp2(fmaf(t[32 * hblk + 2 * c + 1], cexp, -m_use));
           psum += p0 + p1;
           pw[c] = tc::pack_bf16x2(p0, p1);
         }
@@ -575,8 +574,8 @@ attention_ws_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
       if (p < US) *reinterpret_cast<uint2*>(pk + L::kIdxK + p * 8) = rs;
       if (p < kBN) {
         const float nk = fp16_value((uint16_t)rn[0]);
-        cscale[j & 7][p] = nk * a.sm_scale * kLog2e;
-        rho_s[ps][p] = nk > 0.f ? fp16_value((uint16_t)rn[1]) / nk : 0.f;
+        nk_s[ps][p] = nk;
+        rho_s[ps][p] = fp16_value((uint16_t)rn[1]);
         nv_s[ps][p] = fp16_value((uint16_t)rn[2]);
       }
       // every producer's staged bytes must be visible before anyone decodes (a bounded wait
@@ -592,6 +591,7 @@ attention_ws_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
       uint8_t* Kd = smem_raw + L::kKOff + st * L::kKStage;
       {
         uint32_t gw[NI][2], sb[NI], rr[NI];
+        __nv_bfloat162 nk2[NI];
 #pragma unroll
         for (int i = 0; i < NI; ++i) {
           if (i * kProducers + p < kBN * GP) {
@@ -602,8 +602,9 @@ attention_ws_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
             gw[i][0] = (uint32_t)w & ((1u << (8 * KB)) - 1);
             gw[i][1] = (uint32_t)(w >> (8 * KB));
             sb[i] = ~(uint32_t)*reinterpret_cast<const uint16_t*>(pk + L::kIdxK + ikey[i] * G + igp[i] * 2);
-            const float rho = rho_s[ps][ikey[i]];
+            const float rho = rho_s[ps][ikey[i]], nkf = nk_s[ps][ikey[i]];
             rr[i] = tc::pack_bf16x2(rho, rho);
+            nk2[i] = __floats2bfloat162_rn(nkf, nkf);
           }
         }
 #pragma unroll
@@ -614,6 +615,11 @@ attention_ws_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
             for (int half = 0; half < 2; ++half) {
               uint32_t kq[4];
               decode_group<KB>(lutK, gw[i][half], kq);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const __nv_bfloat162 prod = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&kq[q]), nk2[i]);
+                kq[q] = *reinterpret_cast<const uint32_t*>(&prod);
+              }
               uint32_t sq[4];
 #pragma unroll
               for (int q = 0; q < 4; ++q)  // sign bit 0 -> bit 15, bit 1 -> bit 31 of the bf16x2 word
@@ -824,6 +830,7 @@ int attention_fwd_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_t 
                        cudaStream_t stream) {
   const int64_t n_q = B * Hq * Sq;
   TQ_REQUIRE(B <= 65535 && Hq <= 65535, "batch and head counts are limited to 65535 in bf16 mode");
+  TQ_REQUIRE(a.sm_scale > 0.f && a.sm_scale < 1e30f, "sm_scale must be positive and finite in bf16 mode");
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   __nv_bfloat16* w_cat = reinterpret_cast<__nv_bfloat16*>(ws);
   ws += round256((size_t)2 * d * d * 2);
