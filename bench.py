@@ -47,6 +47,10 @@ def parse():
     ap.add_argument("--bits", type=int, default=3)
     ap.add_argument("--seq", type=int, default=S, help="sequence length (default: the named workload)")
     ap.add_argument("--batch", type=int, default=B)
+    ap.add_argument("--workload", default="op", choices=["op", "llama8b", "deepseek7b", "quality"],
+                    help="op: the op-level headline workload (default); llama8b / deepseek7b: end-to-end prefill of a "
+                         "random-init model of that shape through apply_turboquant; quality: estimator quality "
+                         "metrics on a Qwen2.5-3B-shaped attention layer")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -178,8 +182,126 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+MODEL_SHAPES = {
+    # name: (layers, hidden, q heads, kv heads, head_dim, ffn, vocab, rope_theta, global batch, seq)
+    "llama8b": (32, 4096, 32, 8, 128, 14336, 128256, 500000.0, 8, 4096),
+    "deepseek7b": (30, 4096, 32, 32, 128, 11008, 102400, 10000.0, 16, 4096),
+}
+
+
+def run_model(args):
+    """End-to-end prefill tokens/s of a random-init LLaMA-architecture model (bf16, N(0, 0.02) init, uniform
+    random tokens) with every attention layer replaced by apply_turboquant(bits, seed=42).  The global
+    batch is split over the ranks (full replica per GPU, strong scaling); the only collective is the
+    all_gather of the last-token logits, inside the timed region."""
+    import turboquant_b200 as tq
+    from transformers import LlamaConfig, LlamaForCausalLM
+    from turboquant_b200.sharding import gather_rows, unit_range
+
+    L, hid, hq, hkv, hd, ffn, vocab, theta, gbatch, seq = MODEL_SHAPES[args.workload]
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = LlamaConfig(num_hidden_layers=L, hidden_size=hid, num_attention_heads=hq, num_key_value_heads=hkv,
+                      head_dim=hd, intermediate_size=ffn, vocab_size=vocab, rope_theta=theta,
+                      max_position_embeddings=seq, initializer_range=0.02)
+    torch.manual_seed(0)
+    torch.set_default_dtype(torch.bfloat16)
+    with torch.device(dev):
+        model = LlamaForCausalLM(cfg).eval()
+    torch.set_default_dtype(torch.float32)
+    ids_all = torch.randint(0, vocab, (gbatch, seq), generator=torch.Generator().manual_seed(0))
+    lo, hi = unit_range(gbatch, rank, world)
+    ids_host = ids_all[lo:hi].pin_memory()
+
+    def forward(m):
+        with torch.no_grad():
+            ids = ids_host.to(dev, non_blocking=True)
+            last = m(ids, logits_to_keep=1).logits[:, -1].float()
+            if dist is not None:
+                last = gather_rows(last)
+            return last.cpu()
+
+    def timed(m, steps, warm):
+        for _ in range(warm):
+            forward(m)
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            out = forward(m)
+        e1.record()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+        t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()), out
+
+    steps, warm = max(1, min(args.steps, 5)), max(1, min(args.warmup, 3))
+    ms_plain, logits_plain = timed(model, steps, warm)
+    tq.apply_turboquant(model, bits=args.bits, seed=42)
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms_tq, logits_tq = timed(model, steps, warm)
+    clocks = sampler.finish()
+    if rank == 0:
+        cos = torch.nn.functional.cosine_similarity(logits_tq, logits_plain, dim=-1).mean().item()
+        line = {"metric": f"{args.workload}_{args.bits}bit_prefill_tok_per_s", "value": gbatch * seq / (ms_tq * 1e-3),
+                "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warm, "ms_per_step": ms_tq,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+                "data": "synthetic", "config": {"workload": args.workload, "global_batch": gbatch, "seq_len": seq,
+                                                "layers": L, "bits": args.bits, "parallelism": f"dp{world}",
+                                                "logits": "last token, all_gather inside the timed region"},
+                "clocks": clocks,
+                "e2e": {"value": gbatch * seq / (ms_tq * 1e-3), "unit": "tok/s",
+                        "h2d_bytes_per_step": ids_host.numel() * 8, "d2h_bytes_per_step": gbatch * vocab * 4},
+                "uncompressed_attention_tok_per_s": gbatch * seq / (ms_plain * 1e-3),
+                "last_token_logit_cosine_vs_uncompressed": cos, "device_wait_faults": tq.device_fault_count(dev)}
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def run_quality(args):
+    """Estimator quality on a Qwen2.5-3B-shaped attention layer (16 query heads, 2 KV heads, d=128), the
+    synthetic stand-in for the reference's validate script (validate.py:137-196): compression ratio by bit
+    accounting, cosine between estimator and exact score rows, top-1 / top-5 agreement of the per-head
+    argmax, with the last key as proxy query.  Random-init projections of N(0,1) hidden states."""
+    import turboquant_b200 as tq
+    dev = torch.device("cuda", 0)
+    out = {}
+    for T in (2048, 4096, 8192):
+        g = torch.Generator(device=dev).manual_seed(T)
+        k = torch.randn(1, 2, T, D, generator=g, device=dev).to(torch.bfloat16)
+        q = k[:, :, -1:, :]  # last key as proxy query, per KV head
+        exact = (q.float() @ k.float().transpose(-1, -2))[0, :, 0]  # [H, T]
+        for bits in (2, 3, 4):
+            kc = tq.TurboQuantCompressorV2(D, bits, 0, device=str(dev))
+            est = kc.asymmetric_attention_scores(q, kc.compress(k))[0, :, 0]
+            cos = torch.nn.functional.cosine_similarity(est, exact, dim=-1).mean().item()
+            top1 = (est.argmax(-1) == exact.argmax(-1)).float().mean().item()
+            top5 = torch.stack([(exact.argmax(-1)[h] == est[h].topk(5).indices).any() for h in range(2)]).float().mean().item()
+            ratio = 32.0 * D / (2 * bits * D + 48)
+            out[f"T{T}_b{bits}"] = {"compression_ratio": round(ratio, 2), "score_cosine": cos, "top1": top1, "top5": top5}
+    print(json.dumps({"metric": "tq_estimator_quality", "workload": "qwen2.5-3b-shaped attention, synthetic", "results": out}))
+
+
 def main():
     args = parse()
+    if args.workload in MODEL_SHAPES:
+        return run_model(args)
+    if args.workload == "quality":
+        return run_quality(args)
     if args.impl == "reference":
         return run_reference(args)
 
@@ -276,8 +398,10 @@ def main():
     flops = 6.0 * D * causal_pairs(batch, seq)  # 2d (q.K_hat) + 2d (q_s.sign) + 2d (P.V_hat) per causal pair
     achieved = flops / (attn_ms * 1e-3) / 1e12 if attn_ms > 0 else None
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
-                "frac": (achieved / peaks["tflops"]) if achieved else None, "traffic": None,
-                "kernel": "attention_tc_kernel", "ms_per_launch": attn_ms, "peak_source": peaks["source"],
+                "frac": (achieved / peaks["tflops"]) if achieved else None,
+                # DRAM bytes per launch: ncu capture at batch 1 (141.0 MB read + 37.5 MB written), which scales with batch
+                "traffic": 178.5e6 * batch if (seq == S and D == 128) else None,
+                "kernel": "attention_ws_kernel", "ms_per_launch": attn_ms, "peak_source": peaks["source"],
                 "kernel_ms": {"compress_keys": ms_sum[0] / max(launches[0], 1),
                               "compress_values": ms_sum[1] / max(launches[1], 1),
                               "prepare_queries": ms_sum[2] / max(launches[2], 1),
@@ -300,7 +424,7 @@ def main():
                        "seq_len": seq, "head_dim": D, "bits": bits, "causal": True,
                        "l2": "inputs (402 MB per step) exceed the 126 MB L2; no flush",
                        "causal_pairs_per_s": causal_pairs(batch, seq) * world / (ms_per_step * 1e-3)},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": int(sum(launches)) + 2 * args.steps,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": (int(sum(launches)) + 2 * args.steps) * world,
             "roofline": roofline, "cpu_baseline": cpu, "device_wait_faults": faults}
     print(json.dumps(line), flush=True)
     if dist is not None:

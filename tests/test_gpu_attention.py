@@ -144,3 +144,35 @@ def test_end_to_end_operator_sequence_vs_reference_fixture(golden_family):
 def test_no_device_wait_faults():
     from turboquant_b200 import device_fault_count
     assert device_fault_count() == 0
+
+
+@pytest.mark.parametrize("Hq,Hkv", [(8, 2), (3, 3)])
+def test_long_sequence_tensor_core_vs_fp32_kernel_and_oracle(Hq, Hkv):
+    """S = 4096 (64 key tiles, many ring and barrier-phase wrap-arounds, several CTAs per head; head
+    pairs for the even group, position-block pairs for MHA): the tensor-core kernel against the
+    independent fp32 CUDA-core kernel on the whole output, and against the oracle on the last 32
+    query rows of one head."""
+    from turboquant_b200 import fused_attention
+    d, bits, B, S = 128, 3, 2, 4096
+    g = torch.Generator(device="cuda").manual_seed(7)
+    q = torch.randn(B, Hq, S, d, generator=g, device="cuda").to(torch.bfloat16)
+    k = torch.randn(B, Hkv, S, d, generator=g, device="cuda").to(torch.bfloat16)
+    v = torch.randn(B, Hkv, S, d, generator=g, device="cuda").to(torch.bfloat16)
+    kc, vc = device_compressors(d, bits)
+    ck, cv = kc.compress(k), vc.compress(v)
+    out16 = fused_attention(q, ck, cv, kc, vc, causal=True, mode="bf16")
+    out32 = fused_attention(q, ck, cv, kc, vc, causal=True, mode="fp32")
+    assert rel_err(out16, out32) < TOL["bf16"], rel_err(out16, out32)
+    per_row = ((out16.float() - out32.float()).norm(dim=-1) / out32.float().norm(dim=-1)).max()
+    assert float(per_row) < 5e-2, float(per_row)          # no single bad row hides in the aggregate
+    # oracle on a slice: batch 1, last query head, last 32 rows, from the product's packed bytes
+    kp, vp = oracle_params(d, bits)
+    hk = (Hq - 1) // (Hq // Hkv)
+    sel = slice((1 * Hkv + hk) * S, (1 * Hkv + hk + 1) * S)
+    sc = orc.scores_from_packed(q[1:2, -1:, -32:].float().cpu(), ck["packed_key_indices"][sel].cpu().numpy(),
+                                ck["packed_qjl_signs"][sel].cpu().numpy(), ck["vec_norms"][1, hk].cpu(),
+                                ck["residual_norm"][1, hk].cpu(), kp, (1, 1, S, d))
+    vals = orc.values_from_packed(cv["packed_indices"][sel].cpu().numpy(), cv["vec_norms"][sel].cpu(), vp, (1, 1, S, d))
+    want = torch.softmax(sc / d ** 0.5 + orc.causal_mask(S, S)[-32:], -1) @ vals
+    assert rel_err(out32[1:2, -1:, -32:], want) < 4e-3   # fp32 arithmetic, but the output is stored as bf16 here
+    assert rel_err(out16[1:2, -1:, -32:], want) < TOL["bf16"]

@@ -1,0 +1,105 @@
+"""End-to-end plugin path on small models: `apply_turboquant` on the GPU against the same model on
+the CPU whose attention cores are evaluated by the oracle (the reference arithmetic), layer by
+layer with the reference's seeds (layer i: keys seed+i, values seed+i+10000)."""
+
+import copy
+
+import pytest
+import torch
+import torch.nn as nn
+
+from helpers import rel_err
+from oracle import tq_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+class OracleCore(nn.Module):
+    """Replaces an HF attention module on the CPU; projections are the original module's, the
+    attention core is oracle.attention_core (families/llama.py:100-114, gpt2.py:90-110)."""
+
+    def __init__(self, original, kind, layer, bits, seed):
+        super().__init__()
+        self.o, self.kind = original, kind
+        ks, vs = orc.layer_seeds(seed, layer)
+        d = original.head_dim
+        self.kp, self.vp = orc.make_key_params(d, bits, ks), orc.make_value_params(d, bits, vs)
+
+    def forward(self, hidden_states, position_embeddings=None, attention_mask=None, **kw):
+        o = self.o
+        B, T, _ = hidden_states.shape
+        if self.kind == "gpt2":
+            q, k, v = o.c_attn(hidden_states).split(o.embed_dim, dim=2)
+            shp = (B, T, -1, o.head_dim)
+            q, k, v = (t.view(shp).transpose(1, 2) for t in (q, k, v))
+        else:
+            from transformers.models.llama.modeling_llama import apply_rotary_pos_emb
+            shp = (B, T, -1, o.head_dim)
+            q = o.q_proj(hidden_states).view(shp).transpose(1, 2)
+            k = o.k_proj(hidden_states).view(shp).transpose(1, 2)
+            v = o.v_proj(hidden_states).view(shp).transpose(1, 2)
+            q, k = apply_rotary_pos_emb(q, k, *position_embeddings)
+        out, _ = orc.attention_core(q, k, v, self.kp, self.vp, mask=orc.causal_mask(T, T), literal=True)
+        out = out.transpose(1, 2).reshape(B, T, -1)
+        return (o.c_proj(out) if self.kind == "gpt2" else o.o_proj(out)), None
+
+
+def _oracle_model(model, cls_name, kind, bits, seed):
+    ref = copy.deepcopy(model)
+    layer = 0
+    for _, parent in list(ref.named_modules()):
+        for name, child in list(parent.named_children()):
+            if type(child).__name__ == cls_name:
+                setattr(parent, name, OracleCore(child, kind, layer, bits, seed))
+                layer += 1
+    assert layer > 0
+    return ref
+
+
+def _build(kind):
+    from transformers import GPT2Config, GPT2LMHeadModel, LlamaConfig, LlamaForCausalLM, Qwen2Config, Qwen2ForCausalLM
+    torch.manual_seed(0)
+    if kind == "gpt2":
+        cfg = GPT2Config(n_embd=256, n_head=4, n_layer=2, n_positions=128, vocab_size=512,
+                         attn_pdrop=0.0, resid_pdrop=0.0, embd_pdrop=0.0)
+        return GPT2LMHeadModel(cfg).eval(), "GPT2Attention"
+    if kind == "llama":
+        cfg = LlamaConfig(hidden_size=256, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                          intermediate_size=512, num_hidden_layers=2, vocab_size=512)
+        return LlamaForCausalLM(cfg).eval(), "LlamaAttention"
+    cfg = Qwen2Config(hidden_size=256, num_attention_heads=4, num_key_value_heads=1, intermediate_size=512,
+                      num_hidden_layers=2, vocab_size=512)
+    return Qwen2ForCausalLM(cfg).eval(), "Qwen2Attention"
+
+
+@pytest.mark.parametrize("kind", ["gpt2", "llama", "qwen2"])
+@pytest.mark.parametrize("bits", [3, 4])
+def test_model_logits_match_oracle_fp32(kind, bits):
+    from turboquant_b200 import apply_turboquant
+    model, cls_name = _build(kind)
+    ids = torch.randint(0, 512, (2, 96), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = _oracle_model(model, cls_name, "gpt2" if kind == "gpt2" else "rope", bits, 42)(ids).logits
+        got = apply_turboquant(copy.deepcopy(model).cuda(), bits=bits, seed=42)(ids.cuda()).logits
+        plain = model(ids).logits
+    # fp32 mode; the literal reference stores k_mse in fp16 (~2e-4 per layer)
+    assert rel_err(got, want) < 3e-3, rel_err(got, want)
+    # and compression is doing something: the compressed model differs from the uncompressed one
+    assert rel_err(got, plain) > 10 * rel_err(got, want)
+
+
+def test_llama_bf16_is_causal_and_close_to_fp32_mode():
+    from turboquant_b200 import apply_turboquant
+    model, _ = _build("llama")
+    ids = torch.randint(0, 512, (1, 200), generator=torch.Generator().manual_seed(2))
+    ids2 = ids.clone()
+    ids2[0, -1] = (ids2[0, -1] + 1) % 512
+    with torch.no_grad():
+        m32 = apply_turboquant(copy.deepcopy(model).cuda(), bits=3, seed=42)
+        m16 = apply_turboquant(copy.deepcopy(model).cuda().to(torch.bfloat16), bits=3, seed=42)
+        a, b2 = m16(ids.cuda()).logits.float(), m16(ids2.cuda()).logits.float()
+        ref = m32(ids.cuda()).logits
+    assert torch.isfinite(a).all()
+    assert torch.equal(a[:, :-1], b2[:, :-1])         # HF passes no mask under sdpa: causality is ours
+    assert not torch.equal(a[:, -1], b2[:, -1])
+    assert rel_err(a, ref) < 1e-1                     # whole model (weights included) in bf16 vs fp32
