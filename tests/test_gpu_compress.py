@@ -106,3 +106,46 @@ def test_compress_empty_and_zero_vectors():
     assert np.array_equal(z["packed_key_indices"].cpu().numpy(), oz["packed_key_indices"])
     assert np.array_equal(z["packed_qjl_signs"].cpu().numpy(), oz["packed_qjl_signs"])
     assert float(z["vec_norms"].float().abs().max()) == 0.0 and float(z["residual_norm"].float().abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("d,bits", [(128, 2), (128, 3), (128, 4), (64, 2), (64, 3), (64, 4)])
+def test_tensor_core_compress_vs_oracle(d, bits):
+    """bf16 inputs in bf16 mode run the tcgen05 kernel (rotation and sketch as split-bf16 MMAs).  Its
+    operands carry ~16 mantissa bits, so a coordinate within ~1e-6 of a boundary may move by one
+    level and a projection within rounding of zero may flip its sign bit: bounded here."""
+    g = torch.Generator().manual_seed(100 + d + bits)
+    B, H, S = 2, 3, 1500                       # 9000 vectors: ragged last tile, several tiles per CTA
+    k = torch.randn(B, S, H, d, generator=g)
+    k[..., 7] *= 8
+    k[0, 5] = 0.0                              # zero vectors
+    v = torch.randn(B, S, H, d, generator=g)
+    k, v = k.to(torch.bfloat16), v.to(torch.bfloat16)
+    kp, vp = oracle_params(d, bits)
+    ok = orc.key_compress(k.transpose(1, 2), kp)
+    ov = orc.value_compress(v.transpose(1, 2), vp)
+    kc, vc = device_compressors(d, bits, mode="bf16")
+    ck = kc.compress(k.cuda().transpose(1, 2))   # strided view, read in place
+    cv = vc.compress(v.cuda().transpose(1, 2))
+    mk = _index_mismatch(ck["packed_key_indices"].cpu().numpy(), ok["packed_key_indices"], bits - 1, d)
+    mv = _index_mismatch(cv["packed_indices"].cpu().numpy(), ov["packed_indices"], bits, d)
+    assert mk <= 3e-5 and mv <= 3e-5, (mk, mv)
+    assert _bit_mismatch(ck["packed_qjl_signs"].cpu().numpy(), ok["packed_qjl_signs"]) <= 2e-4
+    assert _fp16_close(ck["vec_norms"], ok["vec_norms"]) and _fp16_close(ck["residual_norm"], ok["residual_norm"])
+    assert _fp16_close(cv["vec_norms"], ov["vec_norms"])
+    # and against the fp32 kernel on the same device data
+    kc32, vc32 = device_compressors(d, bits, mode="fp32")
+    c32 = kc32.compress(k.cuda().transpose(1, 2))
+    assert _index_mismatch(ck["packed_key_indices"].cpu().numpy(), c32["packed_key_indices"].cpu().numpy(), bits - 1, d) <= 3e-5
+
+
+@pytest.mark.parametrize("S", [1, 127, 128, 129])
+def test_tensor_core_compress_ragged(S):
+    d, bits = 128, 3
+    k = torch.randn(1, 2, S, d, generator=torch.Generator().manual_seed(S)).to(torch.bfloat16)
+    kp, vp = oracle_params(d, bits)
+    kc, vc = device_compressors(d, bits, mode="bf16")
+    ck, cv = kc.compress(k.cuda()), vc.compress(k.cuda())
+    ok, ov = orc.key_compress(k, kp), orc.value_compress(k, vp)
+    assert _index_mismatch(ck["packed_key_indices"].cpu().numpy(), ok["packed_key_indices"], bits - 1, d) <= 1e-3
+    assert _index_mismatch(cv["packed_indices"].cpu().numpy(), ov["packed_indices"], bits, d) <= 1e-3
+    assert _bit_mismatch(ck["packed_qjl_signs"].cpu().numpy(), ok["packed_qjl_signs"]) <= 2e-3

@@ -36,6 +36,7 @@ inline int elem_size(int dtype) { return dtype == TQ_F32 ? 4 : 2; }
 // Copies the device counter of expired bounded waits (kept by the tensor-core
 // translation unit) to the host.
 int read_wait_faults(unsigned long long* out);
+int read_compress_faults(unsigned long long* out);
 int trace_enable(int on);
 int trace_read(long long* host_buf, int max_records, int* n_out);
 

@@ -16,25 +16,9 @@
 // reference (src/turboquant_pytorch/compressors.py:98-161, :270-294).
 #include "tq_common.cuh"
 #include "tq_simt.cuh"
+#include "tq_compress.cuh"
 
 namespace tq {
-
-constexpr int kTileRows = 64;
-
-struct CompressArgs {
-  const void* src;
-  int64_t n_vec, H, S;
-  int64_t stride_b, stride_h, stride_s;
-  const float* Pi;
-  const float* S_eff;
-  const float* centroids;
-  const float* boundaries;
-  uint8_t* packed_idx;
-  uint8_t* packed_signs;
-  uint16_t* vec_norms;
-  uint16_t* residual_norms;
-  int num_tiles;
-};
 
 template <typename T, int D, int IB, bool IS_KEY>
 __global__ void __launch_bounds__(16 * (D / 8)) compress_simt_kernel(const CompressArgs a) {
@@ -181,7 +165,9 @@ static int dispatch_ib(int ib, const CompressArgs& a, cudaStream_t stream) {
 }
 
 template <bool IS_KEY>
-static int dispatch_compress(int dtype, int d, int ib, const CompressArgs& a, cudaStream_t stream) {
+static int dispatch_compress(int dtype, int d, int ib, const CompressArgs& a, int mode, cudaStream_t stream) {
+  // tensor-core kernel: bf16 inputs are exact MMA operands; other input types keep the fp32 kernel
+  if (mode == TQ_MODE_BF16 && dtype == TQ_BF16) return compress_tc(IS_KEY, d, ib, a, stream);
 #define TQ_CASE(TYPE)                                               \
   if (d == 128) return dispatch_ib<TYPE, 128, IS_KEY>(ib, a, stream); \
   return dispatch_ib<TYPE, 64, IS_KEY>(ib, a, stream);
@@ -228,7 +214,7 @@ int tq_compress_keys(const void* keys, int dtype, int64_t B, int64_t H, int64_t 
   CompressArgs a{keys, n, H, S, stride_b, stride_h, stride_s, Pi, S_eff, centroids, boundaries,
                  packed_idx, packed_signs, vec_norms, residual_norms,
                  (int)((n + kTileRows - 1) / kTileRows)};
-  return dispatch_compress<true>(dtype, d, bits - 1, a, static_cast<cudaStream_t>(stream));
+  return dispatch_compress<true>(dtype, d, bits - 1, a, mode, static_cast<cudaStream_t>(stream));
 }
 
 int tq_compress_values(const void* values, int dtype, int64_t B, int64_t H, int64_t S, int d,
@@ -243,7 +229,7 @@ int tq_compress_values(const void* values, int dtype, int64_t B, int64_t H, int6
   TQ_REQUIRE(packed_idx && vec_norms, "NULL output pointer");
   CompressArgs a{values, n, H, S, stride_b, stride_h, stride_s, Pi, nullptr, nullptr, boundaries,
                  packed_idx, nullptr, vec_norms, nullptr, (int)((n + kTileRows - 1) / kTileRows)};
-  return dispatch_compress<false>(dtype, d, bits, a, static_cast<cudaStream_t>(stream));
+  return dispatch_compress<false>(dtype, d, bits, a, mode, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -1,0 +1,27 @@
+// Argument block shared by the fp32 (CUDA-core) and tensor-core compression kernels.
+#pragma once
+#include "tq_common.cuh"
+
+namespace tq {
+
+constexpr int kTileRows = 64;
+
+struct CompressArgs {
+  const void* src;
+  int64_t n_vec, H, S;
+  int64_t stride_b, stride_h, stride_s;
+  const float* Pi;
+  const float* S_eff;
+  const float* centroids;
+  const float* boundaries;
+  uint8_t* packed_idx;
+  uint8_t* packed_signs;
+  uint16_t* vec_norms;
+  uint16_t* residual_norms;
+  int num_tiles;
+};
+
+// bf16 inputs, rotation and sketch projection on tcgen05 (tq_compress_tc.cu).
+int compress_tc(bool is_key, int d, int index_bits, const CompressArgs& a, cudaStream_t stream);
+
+}  // namespace tq

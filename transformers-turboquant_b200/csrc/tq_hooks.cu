@@ -175,8 +175,10 @@ int tq_device_fault_count(void* stream, int64_t* count_host) {
   TQ_REQUIRE(count_host != nullptr, "count_host is NULL");
   unsigned long long v = 0;
   TQ_CUDA_OK(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  unsigned long long w = 0;
   if (int st = read_wait_faults(&v)) return st;
-  *count_host = static_cast<int64_t>(v);
+  if (int st = read_compress_faults(&w)) return st;
+  *count_host = static_cast<int64_t>(v + w);
   return TQ_OK;
 }
 
