@@ -41,6 +41,12 @@ int attention_fwd_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_t 
 
 size_t workspace_bytes_bf16(int64_t n_q, int d);
 
+// SM-pair (2-CTA cluster) tensor-core kernel, head_dim 128; `o_rot` is bf16 [n_q, d] scratch.
+int attention_c2(const AttnArgs& a, int64_t B, int d, int bits, void* o_rot, cudaStream_t stream);
+int read_c2_faults(unsigned long long* out);
+int trace_enable_c2(int on);
+int trace_read_c2(long long* host_buf, int max_records, int* n_out);
+
 int prepare_queries_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq, int d, int64_t sb, int64_t sh,
                          int64_t ss, const float* Pi_k, const float* S_eff, void* w_cat_scratch, void* q_cat,
                          cudaStream_t stream);

@@ -1,0 +1,627 @@
+// Fused compressed attention on SM PAIRS (thread-block cluster of 2, tcgen05 cta_group::2).
+//
+// Each CTA of the pair owns one query tile of 128 rows that reads the same KV head -- two query heads
+// of one GQA group at the same positions, or two consecutive position blocks of one head -- and keeps
+// it WHOLE in its own tensor memory (both contraction halves), together with a double-buffered score
+// tile and its output accumulator: 128 + 2*128 + 128 = 512 columns.  Keys advance in tiles of 128.
+// One MMA over the pair (M = 256) reads its B operand half from each CTA's shared memory, so each CTA
+// decodes only HALF of every tile: the keys [64r, 64r+64) of K_hat and the value coordinates
+// [d/2*r, d/2*(r+1)) of V_hat (r = rank in the pair).  Per SM this halves the decode work and the
+// operand traffic, and N = 128 runs the tensor pipe at its full rate.
+//
+// Roles per CTA (17 warps): warps 0-7 softmax (two threads per row, 64 score columns each), warps
+// 8-15 producers (prefetch packed bytes, stage, decode), warp 16 tensor-memory allocation; in the
+// leader CTA (rank 0) one thread of warp 16 issues every MMA of the pair.
+//
+// Barriers.  "leader" ones live in rank 0's shared memory and collect one arrival per WARP of both
+// CTAs (lane 0 after __syncwarp; the peer arrives through its cluster address); "both" ones exist in
+// each CTA and are completed by tcgen05.commit multicast to the pair.
+//   leader k_full[s], v_full[s] (16): both halves of K_hat / V_hat of tile j decoded
+//   leader p_full[b] (16)            : P[b] written over S[b] (so S[b] has been read) by all softmax warps
+//   both   k_empty[s], v_empty[s]    : the score / PV MMA of tile j has drained
+//   both   s_full[b], pv_done[b]     : S[b] holds tile j's scores / O += P V_hat of tile j finished
+//   local  pk_full[2] (256), xch[4] (64), q_full -> leader (16)
+// Every wait is bounded; an expired wait raises the CTA's abort flag, the CTA unwinds to the final
+// cluster barrier, a device counter is bumped and later launches return at once.
+#include <math.h>
+
+#include "tq_attention.cuh"
+#include "tq_common.cuh"
+#include "tq_simt.cuh"
+#include "tq_tcgen05.cuh"
+
+namespace tq {
+
+__device__ unsigned long long g_c2_faults = 0ull;
+
+int read_c2_faults(unsigned long long* out) {
+  TQ_CUDA_OK(cudaMemcpyFromSymbol(out, g_c2_faults, sizeof(*out)));
+  return TQ_OK;
+}
+
+// Diagnostics: stage timestamps of the first cluster's leader CTA, see tq_trace_read.
+constexpr int kTraceCap2 = 4096;
+__device__ int g_trace2_on = 0;
+__device__ long long g_trace2[2 * kTraceCap2];
+
+int trace_enable_c2(int on) {
+  const int v = on ? 1 : 0;
+  static long long fill[2 * kTraceCap2];
+  for (int i = 0; i < 2 * kTraceCap2; ++i) fill[i] = -1;
+  TQ_CUDA_OK(cudaMemcpyToSymbol(g_trace2, fill, sizeof(fill)));
+  TQ_CUDA_OK(cudaMemcpyToSymbol(g_trace2_on, &v, sizeof(v)));
+  return TQ_OK;
+}
+int trace_read_c2(long long* host_buf, int max_records, int* n_out) {
+  int n = kTraceCap2 < max_records ? kTraceCap2 : max_records;
+  TQ_CUDA_OK(cudaDeviceSynchronize());
+  TQ_CUDA_OK(cudaMemcpyFromSymbol(host_buf, g_trace2, sizeof(long long) * 2 * n));
+  *n_out = n;
+  return TQ_OK;
+}
+
+namespace {
+
+struct Tracer2 {
+  bool on;
+  int role, n;
+  __device__ Tracer2(bool on_, int role_) : on(on_), role(role_), n(0) {}
+  __device__ __forceinline__ void mark(int ev, int tile) {
+    if (!on || n >= kTraceCap2 / 3) return;
+    const int i = role * (kTraceCap2 / 3) + n++;
+    g_trace2[2 * i] = ((long long)role << 32) | ((long long)ev << 16) | (long long)tile;
+    g_trace2[2 * i + 1] = clock64();
+  }
+};
+
+constexpr int kBM = 128;       // query rows per CTA
+constexpr int kBN = 128;       // keys per tile (64 decoded by each CTA)
+constexpr int kHalfN = 64;
+constexpr int kSoftmax = 256;      // 8 softmax warps: two threads per query row, 64 score columns each
+                                   // (16 warps were measured slower: the exp2 throughput, not the thread count, bounds the phase)
+constexpr int kProducers = 256;    // 8 producer warps
+constexpr int kThreads = kSoftmax + kProducers + 32;
+constexpr int kCtlWarp = kThreads / 32 - 1;
+constexpr int kSoftmaxArrivals = 2 * kSoftmax / 32;     // softmax warps of both CTAs
+constexpr int kProducerArrivals = 2 * kProducers / 32;  // producer warps of both CTAs
+
+template <int B>
+__device__ __forceinline__ void fill_pair_lut(uint32_t* lut, const float* __restrict__ cen, int tid, int nthreads) {
+  for (int e = tid; e < (1 << (2 * B)); e += nthreads)
+    lut[e] = tc::pack_bf16x2(cen[e & ((1 << B) - 1)], cen[e >> B]);
+}
+template <int B>
+__device__ __forceinline__ void decode_group(const uint32_t* lut, uint32_t bits, uint32_t (&out)[4]) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q) out[q] = lut[(bits >> (2 * q * B)) & ((1u << (2 * B)) - 1)];
+}
+
+template <int D, int BITS>
+struct C2Smem {
+  static constexpr int G = D / 8, KB = BITS - 1, VB = BITS;
+  static constexpr int kStages = 3;
+  static constexpr uint32_t kKStage = kHalfN * 2 * D * 2;       // 64 keys x 2D
+  static constexpr uint32_t kVStage = (D / 2) * kBN * 2;        // d/2 coordinates x 128 keys
+  static constexpr uint32_t kIdxK = kHalfN * G * KB;            // packed bytes this CTA stages per tile
+  static constexpr uint32_t kSgn = kHalfN * G;
+  static constexpr uint32_t kIdxV = kBN * (G / 2) * VB;
+  static constexpr uint32_t kPkStage = kIdxK + kSgn + kIdxV;
+  static constexpr uint32_t kKOff = 0;
+  static constexpr uint32_t kVOff = kKOff + kStages * kKStage;
+  static constexpr uint32_t kPkOff = kVOff + kStages * kVStage;
+  static constexpr uint32_t kTotal = kPkOff + 2 * kPkStage;
+  static constexpr uint32_t kSboK = 2 * G * 128;                // K-major [keys, 2D]
+  static constexpr uint32_t kSboV = 128;                        // MN-major [d/2, 128 keys]: coordinate chunks adjacent
+  static constexpr uint32_t kLboV = (G / 2) * 128;              // ... 8-key groups G/2 core matrices apart
+  static constexpr uint32_t kColQ = 0;                          // Q_cat: 2D bf16 = D columns
+  static constexpr uint32_t kColS = D;                          // S[2]: 2 x 128 (P[b] = first 64 columns of S[b])
+  static constexpr uint32_t kColO = D + 2 * kBN;                // O: D
+  static constexpr uint32_t kCols = 512;
+  static_assert(kColO + D <= kCols, "tensor memory over-subscribed");
+};
+
+template <int D, int BITS>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+attention_c2_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const int pair_heads) {
+  using L = C2Smem<D, BITS>;
+  constexpr int G = L::G, KB = L::KB, VB = L::VB, kStages = L::kStages;
+  constexpr int NQ = kSoftmax / kBM;  // threads per query row
+  constexpr int HC = kBN / NQ;       // score columns per softmax thread
+  constexpr float kLog2e = 1.4426950408889634f;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ float nk_s[2][kHalfN];       // key norms, residual norms of this CTA's keys (slot j & 1)
+  __shared__ float rho_s[2][kHalfN];
+  __shared__ float nv_s[2][kBN];          // value norms of all keys of the tile
+  __shared__ float xmax[2][kSoftmax / kBM][kBM];  // [tile parity][column part][row]
+  __shared__ uint32_t lutK[1 << (2 * KB)];
+  __shared__ uint32_t lutV[1 << (2 * VB)];
+  __shared__ __align__(8) uint64_t bars[4 * kStages + 8 + 2 + 4 + 1];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_abort;
+  volatile int* abort_flag = &s_abort;
+
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  const uint32_t rank = tc::cluster_ctarank();
+  if (tid == 0) s_abort = (*reinterpret_cast<volatile unsigned long long*>(&g_c2_faults) != 0ull) ? 1 : 0;
+  __syncthreads();
+  const bool dead = s_abort != 0;  // an earlier bounded wait expired: do nothing but keep the cluster barriers paired
+
+  // ---- which query tile ------------------------------------------------------------------
+  const int64_t b = blockIdx.z;
+  const int xpair = (int)((gridDim.x >> 1) - 1 - (blockIdx.x >> 1));  // heaviest (latest) position blocks first
+  int64_t head;
+  int q0, q0_last;
+  if (pair_heads) {
+    head = 2 * (int64_t)blockIdx.y + rank;
+    q0 = q0_last = xpair * kBM;
+  } else {
+    head = blockIdx.y;
+    q0 = (2 * xpair + (int)rank) * kBM;
+    q0_last = (2 * xpair + 1) * kBM;
+  }
+  const int64_t kv_base = (b * a.Hkv + head / (a.Hq / a.Hkv)) * a.Sk;
+  const int shift = (int)(a.Sk - a.Sq);
+  int k_end = (int)a.Sk;
+  if (a.causal) k_end = min(k_end, min(q0_last + kBM - 1, (int)a.Sq - 1) + shift + 1);
+  const int n_tiles = dead ? 0 : (k_end + kBN - 1) / kBN;  // identical in both CTAs of the pair
+
+  const uint32_t bar0 = tc::smem_u32(&bars[0]);
+  auto k_full = [&](int i) { return bar0 + 8u * i; };                       // leader
+  auto v_full = [&](int i) { return bar0 + 8u * (kStages + i); };           // leader
+  auto k_empty = [&](int i) { return bar0 + 8u * (2 * kStages + i); };      // both
+  auto v_empty = [&](int i) { return bar0 + 8u * (3 * kStages + i); };      // both
+  auto s_full = [&](int i) { return bar0 + 8u * (4 * kStages + i); };       // both
+  auto pv_done = [&](int i) { return bar0 + 8u * (4 * kStages + 2 + i); };  // both
+  auto p_full = [&](int i) { return bar0 + 8u * (4 * kStages + 6 + i); };   // leader
+  auto pk_full = [&](int i) { return bar0 + 8u * (4 * kStages + 8 + i); };  // local
+  auto xch = [&](int i) { return bar0 + 8u * (4 * kStages + 10 + i); };     // local
+  const uint32_t q_full = bar0 + 8u * (4 * kStages + 14);                   // leader
+  // one arrival on a barrier that lives in rank 0: local form there, cluster address from the peer
+  auto arrive_leader = [&](uint32_t bar) {
+    if (rank == 0) tc::mbar_arrive(bar);
+    else tc::mbar_arrive_cluster(tc::map_to_cta(bar, 0));
+  };
+
+  if (tid == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      tc::mbar_init(k_full(i), kProducerArrivals);
+      tc::mbar_init(v_full(i), kProducerArrivals);
+      tc::mbar_init(k_empty(i), 1);
+      tc::mbar_init(v_empty(i), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      tc::mbar_init(s_full(i), 1);
+      tc::mbar_init(pv_done(i), 1);
+      tc::mbar_init(p_full(i), kSoftmaxArrivals);
+      tc::mbar_init(pk_full(i), kProducers);
+    }
+    for (int i = 0; i < 4; ++i) tc::mbar_init(xch(i), 32 * (kSoftmax / kBM));
+    tc::mbar_init(q_full, kSoftmaxArrivals);
+    tc::fence_mbar_init();
+  }
+  if (warp == kCtlWarp) tc::tmem_alloc2(tc::smem_u32(&tmem_slot), L::kCols);
+  fill_pair_lut<KB>(lutK, a.cen_k, tid, kThreads);
+  fill_pair_lut<VB>(lutV, a.cen_v, tid, kThreads);
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::cluster_sync();  // the peer's barriers and tensor memory exist before anyone signals or issues
+  tc::fence_after_sync();
+  const uint32_t tmem_base = tmem_slot;
+  const uint32_t tmem_o = tmem_base + L::kColO;
+  bool ok = true;
+  Tracer2 tr(g_trace2_on != 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 &&
+                 (warp == 0 || warp == kSoftmax / 32 || warp == kCtlWarp),
+             warp == 0 ? 0 : warp == kSoftmax / 32 ? 1 : 2);
+
+  if (warp < kSoftmax / 32) {
+    // =============================== softmax warps ===============================
+    const int quad = warp % 4, chalf = warp / 4;
+    const int row = quad * 32 + lane;
+    const int qi = q0 + row;
+    const int64_t qrow = (b * a.Hq + head) * a.Sq + qi;
+    const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+    if (n_tiles > 0) {  // query row -> tensor memory: 2D bf16 = D columns, each of the row's threads stores D/NQ
+      const bool live = qi < a.Sq;
+      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.q_cat) + qrow * 2 * D) +
+                         chalf * (D / (4 * NQ));
+#pragma unroll 1
+      for (int c0 = 0; c0 < D / NQ; c0 += 32) {
+        uint32_t w[32];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          uint4 v = make_uint4(0, 0, 0, 0);
+          if (live) v = src[c0 / 4 + i];
+          w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+        }
+        tc::tmem_st32(tmem_base + L::kColQ + lane_base + chalf * (D / NQ) + c0, w);
+      }
+      tc::wait_st();
+      tc::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) arrive_leader(q_full);
+    }
+    float m_run = -INFINITY, l_run = 0.f;
+    const float cexp = a.sm_scale * kLog2e, rcexp = 1.f / cexp;  // K_hat carries the key norms: S is the raw score
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int bb = j & 1, u = j >> 1, k0 = j * kBN;
+      const int kc0 = k0 + chalf * HC;
+      const uint32_t tmem_s = tmem_base + L::kColS + bb * kBN;
+      tr.mark(0, j);
+      if (!(ok = tc::mbar_wait_or_abort(s_full(bb), u & 1, abort_flag))) break;
+      tc::fence_after_sync();
+      tr.mark(1, j);
+      float t[HC];
+#pragma unroll
+      for (int c0 = 0; c0 < HC; c0 += 32) {
+        uint32_t raw[32];
+        tc::tmem_ld32(tmem_s + lane_base + chalf * HC + c0, raw);
+        tc::wait_ld();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) t[c0 + c] = __uint_as_float(raw[c]);
+      }
+      float mx = -INFINITY;
+      const bool edge = (k0 + kBN > a.Sk) || (a.causal && k0 + kBN - 1 > q0 + shift) || a.mask != nullptr;
+      if (!edge) {
+#pragma unroll
+        for (int c4 = 0; c4 < HC; c4 += 4)
+          mx = fmaxf(mx, fmaxf(fmaxf(t[c4], t[c4 + 1]), fmaxf(t[c4 + 2], t[c4 + 3])));
+        mx *= cexp;
+      } else {
+        const float* mrow = (a.mask != nullptr && qi < a.Sq)
+                                ? a.mask + b * a.mask_stride_b + (int64_t)qi * a.mask_stride_q + kc0
+                                : nullptr;
+#pragma unroll
+        for (int c = 0; c < HC; ++c) {
+          const int k = kc0 + c;
+          float v = t[c] * cexp;
+          if (mrow != nullptr && k < a.Sk) v = fmaf(mrow[c], kLog2e, v);
+          if (k >= a.Sk || (a.causal && k > qi + shift)) v = -INFINITY;
+          t[c] = v * rcexp;
+          mx = fmaxf(mx, v);
+        }
+      }
+      // exchange half-row maxima with the partner warp (slots alternate with the tile parity)
+      tr.mark(2, j);
+      xmax[bb][chalf][row] = mx;
+      tc::mbar_arrive(xch(quad));
+      if (!(ok = tc::mbar_wait_or_abort(xch(quad), j & 1, abort_flag))) break;
+#pragma unroll
+      for (int o = 1; o < NQ; ++o) mx = fmaxf(mx, xmax[bb][(chalf + o) % NQ][row]);
+      tr.mark(3, j);
+      // P[bb] overwrites the first 64 columns of S[bb]: both halves of the row must have been loaded
+      // (the exchange above orders the partner's loads before this thread's store below)
+      const float m_cand = fmaxf(m_run, mx);
+      const bool grow = __any_sync(0xffffffffu, m_cand > m_run + 8.f);  // identical in both warps of the quadrant
+      float alpha = 1.f;
+      if (grow) {
+        alpha = (m_run == -INFINITY) ? 0.f : tc::fast_exp2(m_run - m_cand);
+        m_run = m_cand;
+      }
+      const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
+      float psum = 0.f;
+#pragma unroll
+      for (int hblk = 0; hblk < HC / 32; ++hblk) {
+        uint32_t pw[16];
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          const float p0 = tc::fast_exp2(fmaf(t[32 * hblk + 2 * c], cexp, -m_use));
+          const float p1 = tc::fast_exp2(fmaf(t[32 * hblk + 2 * c + 1], cexp, -m_use));
+          psum += p0 + p1;
+          pw[c] = tc::pack_bf16x2(p0, p1);
+        }
+        tc::tmem_st16(tmem_s + lane_base + chalf * (HC / 2) + 16 * hblk, pw);
+      }
+      l_run = l_run * alpha + psum;
+      tr.mark(4, j);
+      if (grow && j >= 1) {
+        // O must be at rest: wait for the previous tile's P V_hat; each thread rescales D/NQ columns of its row
+        if (!(ok = tc::mbar_wait_or_abort(pv_done((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag))) break;
+        tc::fence_after_sync();
+#pragma unroll 1
+        for (int c0 = 0; c0 < D / NQ; c0 += 32) {
+          uint32_t raw[32];
+          const uint32_t addr = tmem_o + lane_base + chalf * (D / NQ) + c0;
+          tc::tmem_ld32(addr, raw);
+          tc::wait_ld();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) raw[c] = __float_as_uint(__uint_as_float(raw[c]) * alpha);
+          tc::tmem_st32(addr, raw);
+        }
+      }
+      tc::wait_st();
+      tc::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) arrive_leader(p_full(bb));
+      tr.mark(5, j);
+    }
+    // ---- epilogue: normalise and store the rotated output row ----
+    if (ok && n_tiles > 0)
+      ok = tc::mbar_wait_or_abort(pv_done((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, abort_flag);
+    if (ok && n_tiles > 0) {
+      xmax[n_tiles & 1][chalf][row] = l_run;
+      tc::mbar_arrive(xch(quad));
+      ok = tc::mbar_wait_or_abort(xch(quad), n_tiles & 1, abort_flag);
+    }
+    if (ok && n_tiles > 0) {
+      tc::fence_after_sync();
+      float l_tot = l_run;
+#pragma unroll
+      for (int o = 1; o < NQ; ++o) l_tot += xmax[n_tiles & 1][(chalf + o) % NQ][row];
+      const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+      __nv_bfloat16* dst = o_rot + qrow * D + chalf * (D / NQ);
+#pragma unroll 1
+      for (int c0 = 0; c0 < D / NQ; c0 += 32) {
+        uint32_t raw[32];
+        tc::tmem_ld32(tmem_o + lane_base + chalf * (D / NQ) + c0, raw);
+        tc::wait_ld();
+        if (qi < a.Sq) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 w;
+            w.x = tc::pack_bf16x2(__uint_as_float(raw[8 * i]) * inv, __uint_as_float(raw[8 * i + 1]) * inv);
+            w.y = tc::pack_bf16x2(__uint_as_float(raw[8 * i + 2]) * inv, __uint_as_float(raw[8 * i + 3]) * inv);
+            w.z = tc::pack_bf16x2(__uint_as_float(raw[8 * i + 4]) * inv, __uint_as_float(raw[8 * i + 5]) * inv);
+            w.w = tc::pack_bf16x2(__uint_as_float(raw[8 * i + 6]) * inv, __uint_as_float(raw[8 * i + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c0 + 8 * i) = w;
+          }
+        }
+      }
+    }
+  } else if (warp < kCtlWarp) {
+    // =============================== producer warps ===============================
+    // This CTA decodes keys [k0 + 64 rank, +64) of K_hat (all 2D contraction columns) and value
+    // coordinates [D/2 rank, +D/2) of all 128 keys of V_hat.
+    const int p = tid - kSoftmax;
+    constexpr int GPK = G / 2;                       // 16-coordinate items per key row
+    constexpr int GPV = G / 4;                       // ... per half value row
+    constexpr int UK = L::kIdxK / 8, US = L::kSgn / 8, UV = L::kIdxV / 8;  // 8-byte units staged per tile
+    constexpr int VROW = (G / 2) * VB;               // packed bytes of half a value row
+    constexpr int NK = (UK + kProducers - 1) / kProducers, NV = (UV + kProducers - 1) / kProducers;
+    constexpr int NIK = (kHalfN * GPK + kProducers - 1) / kProducers;
+    constexpr int NIV = (kBN * GPV + kProducers - 1) / kProducers;
+    uint2 rk[NK], rv[NV], rs;
+    uint32_t rn[3];
+    const uint8_t* gk = a.key_idx + kv_base * (G * KB);
+    const uint8_t* gs = a.key_sgn + kv_base * G;
+    const uint8_t* gv = a.val_idx + kv_base * (G * VB) + rank * VROW;
+    const int koff = (int)rank * kHalfN;
+    // per-thread constants of the staging copy: byte offset of each 8-byte unit inside the tile's packed
+    // arrays and the key (row) it belongs to
+    int k_off[NK], k_row[NK], v_off[NV], v_row[NV];
+#pragma unroll
+    for (int i = 0; i < NK; ++i) {
+      const int un = i * kProducers + p;
+      k_off[i] = un * 8;
+      k_row[i] = un < UK ? koff + (un * 8) / (G * KB) : (1 << 30);
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int un = i * kProducers + p;
+      const int key = (un * 8) / VROW;
+      v_off[i] = key * (G * VB) + (un * 8) % VROW;
+      v_row[i] = un < UV ? key : (1 << 30);
+    }
+    const int s_row = p < US ? koff + (p * 8) / G : (1 << 30);
+    auto prefetch = [&](int k0) {
+      const uint2 zero = make_uint2(0, 0);
+      const int left = (int)a.Sk - k0;  // keys of this tile that exist
+      const uint8_t* tk = gk + (int64_t)(k0 + koff) * (G * KB);
+      const uint8_t* tv = gv + (int64_t)k0 * (G * VB);
+#pragma unroll
+      for (int i = 0; i < NK; ++i) rk[i] = k_row[i] < left ? *reinterpret_cast<const uint2*>(tk + k_off[i]) : zero;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) rv[i] = v_row[i] < left ? *reinterpret_cast<const uint2*>(tv + v_off[i]) : zero;
+      rs = s_row < left ? *reinterpret_cast<const uint2*>(gs + (int64_t)(k0 + koff) * G + p * 8) : zero;
+      if (p < kHalfN) {
+        const bool live = koff + p < left;
+        rn[0] = live ? a.key_vn[kv_base + k0 + koff + p] : 0;
+        rn[1] = live ? a.key_rn[kv_base + k0 + koff + p] : 0;
+      }
+      if (p < kBN) rn[2] = (p < left) ? a.val_vn[kv_base + k0 + p] : 0;
+    };
+    int kkey[NIK], kgp[NIK], vkey[NIV], vgp[NIV];
+#pragma unroll
+    for (int i = 0; i < NIK; ++i) {
+      const int e = i * kProducers + p;
+      kkey[i] = (e % 8) + 8 * (e / (8 * GPK));
+      kgp[i] = (e / 8) % GPK;
+    }
+#pragma unroll
+    for (int i = 0; i < NIV; ++i) {
+      const int e = i * kProducers + p;
+      vkey[i] = (e % 8) + 8 * (e / (8 * GPV));
+      vgp[i] = (e / 8) % GPV;
+    }
+    if (n_tiles > 0) prefetch(0);
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int st = j % kStages, u = j / kStages, ps = j & 1;
+      uint8_t* pk = smem_raw + L::kPkOff + ps * L::kPkStage;
+      tr.mark(0, j);
+#pragma unroll
+      for (int i = 0; i < NK; ++i)
+        if (i * kProducers + p < UK) *reinterpret_cast<uint2*>(pk + (i * kProducers + p) * 8) = rk[i];
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+        if (i * kProducers + p < UV)
+          *reinterpret_cast<uint2*>(pk + L::kIdxK + L::kSgn + (i * kProducers + p) * 8) = rv[i];
+      if (p < US) *reinterpret_cast<uint2*>(pk + L::kIdxK + p * 8) = rs;
+      if (p < kHalfN) {
+        nk_s[ps][p] = fp16_value((uint16_t)rn[0]);
+        rho_s[ps][p] = fp16_value((uint16_t)rn[1]);
+      }
+      if (p < kBN) nv_s[ps][p] = fp16_value((uint16_t)rn[2]);
+      tc::mbar_arrive(pk_full(ps));
+      if (!(ok = tc::mbar_wait_or_abort(pk_full(ps), (j >> 1) & 1, abort_flag))) break;
+      tr.mark(1, j);
+      if (j + 1 < n_tiles) prefetch((j + 1) * kBN);
+      tr.mark(6, j);
+      if (u >= 1 && !(ok = tc::mbar_wait_or_abort(k_empty(st), (u - 1) & 1, abort_flag))) break;
+      tr.mark(2, j);
+      // ---- keys ----
+      uint8_t* Kd = smem_raw + L::kKOff + st * L::kKStage;
+      {
+        uint32_t gw[NIK][2], sb[NIK], rr[NIK];
+        __nv_bfloat162 nk2[NIK];
+#pragma unroll
+        for (int i = 0; i < NIK; ++i) {
+          if (i * kProducers + p < kHalfN * GPK) {
+            const uint16_t* sk = reinterpret_cast<const uint16_t*>(pk + kkey[i] * (G * KB) + kgp[i] * 2 * KB);
+            uint64_t w = 0;
+#pragma unroll
+            for (int x = 0; x < KB; ++x) w |= (uint64_t)sk[x] << (16 * x);
+            gw[i][0] = (uint32_t)w & ((1u << (8 * KB)) - 1);
+            gw[i][1] = (uint32_t)(w >> (8 * KB));
+            sb[i] = ~(uint32_t)*reinterpret_cast<const uint16_t*>(pk + L::kIdxK + kkey[i] * G + kgp[i] * 2);
+            const float rho = rho_s[ps][kkey[i]], nkf = nk_s[ps][kkey[i]];
+            rr[i] = tc::pack_bf16x2(rho, rho);
+            nk2[i] = __floats2bfloat162_rn(nkf, nkf);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < NIK; ++i) {
+          if (i * kProducers + p < kHalfN * GPK) {
+            uint8_t* kd = Kd + (kkey[i] / 8) * L::kSboK + (kkey[i] % 8) * 16;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              uint32_t kq[4], sq[4];
+              decode_group<KB>(lutK, gw[i][half], kq);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const __nv_bfloat162 prod = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&kq[q]), nk2[i]);
+                kq[q] = *reinterpret_cast<const uint32_t*>(&prod);
+                sq[q] = rr[i] ^ ((((sb[i] >> (8 * half + 2 * q)) & 3u) * 0x40008000u) & 0x80008000u);
+              }
+              const int g = 2 * kgp[i] + half;
+              *reinterpret_cast<uint4*>(kd + g * 128) = make_uint4(kq[0], kq[1], kq[2], kq[3]);
+              *reinterpret_cast<uint4*>(kd + (G + g) * 128) = make_uint4(sq[0], sq[1], sq[2], sq[3]);
+            }
+          }
+        }
+      }
+      tc::fence_async_smem();
+      __syncwarp();
+      if (lane == 0) arrive_leader(k_full(st));
+      tr.mark(3, j);
+      // ---- values ----
+      if (u >= 1 && !(ok = tc::mbar_wait_or_abort(v_empty(st), (u - 1) & 1, abort_flag))) break;
+      tr.mark(4, j);
+      uint8_t* Vd = smem_raw + L::kVOff + st * L::kVStage;
+      {
+        uint32_t gw[NIV][2];
+        __nv_bfloat162 nv2[NIV];
+#pragma unroll
+        for (int i = 0; i < NIV; ++i) {
+          if (i * kProducers + p < kBN * GPV) {
+            const uint16_t* sv =
+                reinterpret_cast<const uint16_t*>(pk + L::kIdxK + L::kSgn + vkey[i] * VROW + vgp[i] * 2 * VB);
+            uint64_t w = 0;
+#pragma unroll
+            for (int x = 0; x < VB; ++x) w |= (uint64_t)sv[x] << (16 * x);
+            gw[i][0] = (uint32_t)w & (VB == 4 ? 0xffffffffu : ((1u << (8 * (VB & 3))) - 1));
+            gw[i][1] = (uint32_t)(w >> (8 * VB));
+            const float nvf = nv_s[ps][vkey[i]];
+            nv2[i] = __floats2bfloat162_rn(nvf, nvf);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < NIV; ++i) {
+          if (i * kProducers + p < kBN * GPV) {
+            uint8_t* vd = Vd + (vkey[i] / 8) * L::kLboV + (vkey[i] % 8) * 16;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              uint32_t vq[4];
+              decode_group<VB>(lutV, gw[i][half], vq);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const __nv_bfloat162 prod = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&vq[q]), nv2[i]);
+                vq[q] = *reinterpret_cast<const uint32_t*>(&prod);
+              }
+              *reinterpret_cast<uint4*>(vd + (2 * vgp[i] + half) * L::kSboV) = make_uint4(vq[0], vq[1], vq[2], vq[3]);
+            }
+          }
+        }
+      }
+      tc::fence_async_smem();
+      __syncwarp();
+      if (lane == 0) arrive_leader(v_full(st));
+      tr.mark(5, j);
+    }
+  } else if (rank == 0 && lane == 0) {
+    // =============================== MMA issuer (leader CTA) ===============================
+    constexpr uint32_t idesc_s = tc::idesc_bf16(2 * kBM, kBN, false, false);
+    constexpr uint32_t idesc_o = tc::idesc_bf16(2 * kBM, D, false, true);
+    auto issue_scores = [&](int j) -> bool {
+      const int bb = j & 1, st = j % kStages;
+      tr.mark(0, j);
+      if (!tc::mbar_wait_cluster_or_abort(k_full(st), (j / kStages) & 1, abort_flag)) return false;
+      tr.mark(1, j);
+      // S[bb] is free: P[bb] of tile j-2 lives in the same columns, its p_full was awaited before the
+      // P V_hat MMA of tile j-2 was issued, and that MMA precedes this one on the tensor pipe
+      tc::fence_after_sync();
+      const uint64_t kdesc = tc::smem_desc(tc::smem_u32(smem_raw + L::kKOff + st * L::kKStage), 128, L::kSboK);
+#pragma unroll
+      for (int ks = 0; ks < 2 * D / 16; ++ks)
+        tc::mma_bf16_ts2(tmem_base + L::kColS + bb * kBN, tmem_base + L::kColQ + ks * 8,
+                         kdesc + (uint64_t)(ks * 256 >> 4), idesc_s, ks > 0);
+      tc::mma_commit2(s_full(bb), 3);
+      tc::mma_commit2(k_empty(st), 3);
+      tr.mark(2, j);
+      return true;
+    };
+    if (n_tiles > 0) ok = tc::mbar_wait_cluster_or_abort(q_full, 0, abort_flag);
+    if (ok && n_tiles > 0) ok = issue_scores(0);
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int bb = j & 1, u = j >> 1, st = j % kStages;
+      if (j + 1 < n_tiles && !(ok = issue_scores(j + 1))) break;
+      tr.mark(3, j);
+      if (!(ok = tc::mbar_wait_cluster_or_abort(v_full(st), (j / kStages) & 1, abort_flag))) break;
+      tr.mark(4, j);
+      if (!(ok = tc::mbar_wait_cluster_or_abort(p_full(bb), u & 1, abort_flag))) break;
+      tc::fence_after_sync();
+      tr.mark(5, j);
+      const uint64_t vdesc = tc::smem_desc(tc::smem_u32(smem_raw + L::kVOff + st * L::kVStage), L::kLboV, L::kSboV);
+#pragma unroll
+      for (int ks = 0; ks < kBN / 16; ++ks)
+        tc::mma_bf16_ts2(tmem_o, tmem_base + L::kColS + bb * kBN + ks * 8, vdesc + (uint64_t)(ks * 2 * L::kLboV >> 4),
+                         idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+      tc::mma_commit2(pv_done(bb), 3);
+      tc::mma_commit2(v_empty(st), 3);
+      tr.mark(6, j);
+    }
+  }
+  if (!ok && atomicExch(&s_abort, 2) != 2) atomicAdd(&g_c2_faults, 1ull);  // one fault per CTA
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::cluster_sync();  // neither CTA leaves (or frees tensor memory) while the pair's MMAs or signals may touch it
+  if (warp == kCtlWarp) tc::tmem_dealloc2(tmem_base, L::kCols);
+}
+
+template <int D, int BITS>
+int launch_c2(const AttnArgs& a, int64_t B, __nv_bfloat16* o_rot, cudaStream_t stream) {
+  constexpr size_t smem = C2Smem<D, BITS>::kTotal > 120 * 1024 ? C2Smem<D, BITS>::kTotal : 120 * 1024;
+  auto kern = attention_c2_kernel<D, BITS>;
+  TQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const int pair_heads = ((a.Hq / a.Hkv) % 2 == 0) ? 1 : 0;
+  const int64_t blocks = (a.Sq + kBM - 1) / kBM;
+  // x: 2 CTAs (one cluster) per pair of query tiles
+  dim3 grid((unsigned)(2 * (pair_heads ? blocks : (blocks + 1) / 2)), (unsigned)(pair_heads ? a.Hq / 2 : a.Hq),
+            (unsigned)B);
+  {
+    ProfScope prof(kProfAttention, stream);
+    kern<<<grid, kThreads, smem, stream>>>(a, o_rot, pair_heads);
+  }
+  TQ_CUDA_OK(cudaGetLastError());
+  return TQ_OK;
+}
+
+}  // namespace
+
+int attention_c2(const AttnArgs& a, int64_t B, int d, int bits, void* o_rot, cudaStream_t stream) {
+  __nv_bfloat16* o = static_cast<__nv_bfloat16*>(o_rot);
+  if (d == 128)
+    return bits == 2 ? launch_c2<128, 2>(a, B, o, stream) : bits == 3 ? launch_c2<128, 3>(a, B, o, stream)
+                                                                      : launch_c2<128, 4>(a, B, o, stream);
+  return fail(TQ_ERR_UNSUPPORTED, "the SM-pair attention kernel is built for head_dim 128 only");
+}
+
+}  // namespace tq

@@ -16,6 +16,7 @@
 // Every device-side wait is bounded; when one expires the kernel bumps a fault counter,
 // frees its tensor memory and returns, and later launches return immediately.
 #include <math.h>
+#include <stdlib.h>
 
 #include "tq_attention.cuh"
 #include "tq_common.cuh"
@@ -825,6 +826,17 @@ int prepare_queries_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_
   return d == 128 ? launch_rows_gemm<128, 256>(prep, stream) : launch_rows_gemm<64, 128>(prep, stream);
 }
 
+// The SM-pair kernel (tq_attention_c2.cu) serves head_dim 128; TQ_B200_ATTN=ws selects the single-SM
+// kernel instead (diagnostics).
+static bool use_sm_pairs() {
+  static int cached = -1;
+  if (cached < 0) {
+    const char* e = getenv("TQ_B200_ATTN");
+    cached = (e != nullptr && e[0] == 'w') ? 0 : 1;
+  }
+  return cached == 1;
+}
+
 int attention_fwd_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq, int d, int64_t sb, int64_t sh,
                        int64_t ss, const float* Pi_k, const float* S_eff, AttnArgs a, int bits, void* workspace,
                        cudaStream_t stream) {
@@ -847,7 +859,9 @@ int attention_fwd_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_t 
 
   a.q_cat = q_cat;
   int st;
-  if (d == 128)
+  if (d == 128 && use_sm_pairs())
+    st = attention_c2(a, B, d, bits, o_rot, stream);
+  else if (d == 128)
     st = bits == 2   ? launch_attention_tc<128, 2>(a, B, o_rot, stream)
          : bits == 3 ? launch_attention_tc<128, 3>(a, B, o_rot, stream)
                      : launch_attention_tc<128, 4>(a, B, o_rot, stream);

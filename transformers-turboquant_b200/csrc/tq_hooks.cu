@@ -3,9 +3,11 @@
 // kernels; each thread owns 8 consecutive fields, i.e. exactly b whole bytes of the
 // row's bit stream, so no atomics or pre-zeroed outputs are needed.
 #include <stdarg.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "tq_common.cuh"
+#include "tq_attention.cuh"
 
 namespace tq {
 
@@ -178,14 +180,25 @@ int tq_device_fault_count(void* stream, int64_t* count_host) {
   unsigned long long w = 0;
   if (int st = read_wait_faults(&v)) return st;
   if (int st = read_compress_faults(&w)) return st;
-  *count_host = static_cast<int64_t>(v + w);
+  unsigned long long x = 0;
+  if (int st = read_c2_faults(&x)) return st;
+  *count_host = static_cast<int64_t>(v + w + x);
   return TQ_OK;
 }
 
-int tq_trace_enable(int on) { return trace_enable(on); }
+static bool trace_sm_pairs() {
+  const char* e = getenv("TQ_B200_ATTN");
+  return !(e != nullptr && e[0] == 'w');
+}
+
+int tq_trace_enable(int on) {
+  if (int st = trace_enable(on)) return st;
+  return trace_enable_c2(on);
+}
 
 int tq_trace_read(int64_t* records_host, int max_records, int* n_host) {
   TQ_REQUIRE(records_host && n_host && max_records > 0, "bad trace buffer");
+  if (trace_sm_pairs()) return trace_read_c2(reinterpret_cast<long long*>(records_host), max_records, n_host);
   return trace_read(reinterpret_cast<long long*>(records_host), max_records, n_host);
 }
 
