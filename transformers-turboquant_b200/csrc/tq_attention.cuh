@@ -1,6 +1,8 @@
 // Argument block and entry points shared by the fp32 (CUDA-core) and bf16 (tcgen05)
 // implementations of the fused compressed attention.
 #pragma once
+#include <cuda_bf16.h>
+
 #include "tq_common.cuh"
 
 namespace tq {
@@ -41,8 +43,18 @@ int attention_fwd_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_t 
 
 size_t workspace_bytes_bf16(int64_t n_q, int d);
 
-// SM-pair (2-CTA cluster) tensor-core kernel, head_dim 128; `o_rot` is bf16 [n_q, d] scratch.
-int attention_c2(const AttnArgs& a, int64_t B, int d, int bits, void* o_rot, cudaStream_t stream);
+// Raw queries and the constant bf16 operands of the SM-pair kernel, which prepares its own query tile
+// (q [Pi ; coeff S]^T) and rotates its output back (o Pi_v) on the tensor pipe.
+struct PairArgs {
+  const void* q;
+  int q_dtype;
+  int64_t q_stride_b, q_stride_h, q_stride_s;
+  const __nv_bfloat16* w_cat;    // [2d, d] = [Pi ; coeff S]
+  const __nv_bfloat16* w_unrot;  // [d, d]  = Pi_v^T
+};
+
+// SM-pair (2-CTA cluster) tensor-core kernel, head_dim 128; needs no per-query scratch.
+int attention_c2(const AttnArgs& a, const PairArgs& x, int64_t B, int d, int bits, cudaStream_t stream);
 int read_c2_faults(unsigned long long* out);
 int trace_enable_c2(int on);
 int trace_read_c2(long long* host_buf, int max_records, int* n_out);

@@ -9,9 +9,16 @@
 // [d/2*r, d/2*(r+1)) of V_hat (r = rank in the pair).  Per SM this halves the decode work and the
 // operand traffic, and N = 128 runs the tensor pipe at its full rate.
 //
-// Roles per CTA (17 warps): warps 0-7 softmax (two threads per row, 64 score columns each), warps
+// The kernel is self-contained: its prologue turns the raw query tile into Q_cat = q [Pi ; coeff S]^T
+// with one MMA group (A = raw tile, B = this CTA's half of the constant operand, both staged in the
+// still idle K_hat ring) and its epilogue multiplies the normalised output tile by Pi_v the same way
+// (A = bf16 output tile in tensor memory over the retired score columns), so neither the prepared
+// queries nor the rotated outputs ever reach HBM.
+//
+// Roles per CTA (18 warps): warps 0-7 softmax (two threads per row, 64 score columns each), warps
 // 8-15 producers (prefetch packed bytes, stage, decode), warp 16 tensor-memory allocation; in the
-// leader CTA (rank 0) one thread of warp 16 issues every MMA of the pair.
+// leader CTA (rank 0) one thread of warp 16 issues the score MMAs of the pair and one thread of warp
+// 17 the P V_hat MMAs.
 //
 // Barriers.  "leader" ones live in rank 0's shared memory and collect one arrival per WARP of both
 // CTAs (lane 0 after __syncwarp; the peer arrives through its cluster address); "both" ones exist in
@@ -20,13 +27,17 @@
 //   leader p_full[b] (16)            : P[b] written over S[b] (so S[b] has been read) by all softmax warps
 //   both   k_empty[s], v_empty[s]    : the score / PV MMA of tile j has drained
 //   both   s_full[b], pv_done[b]     : S[b] holds tile j's scores / O += P V_hat of tile j finished
-//   local  pk_full[2] (256), xch[4] (64), q_full -> leader (16)
+//   local  pk_full[2] (256), xch[4] (64)
+//   leader qp_full (32): raw query tile and constant operand staged;  both qp_done: Q_cat accumulated
+//   leader q_full (16) : 1st phase Q_cat packed into tensor memory, 2nd phase output tile + Pi_v staged
+//   both   e_done      : back-rotated output tile accumulated
 // Every wait is bounded; an expired wait raises the CTA's abort flag, the CTA unwinds to the final
 // cluster barrier, a device counter is bumped and later launches return at once.
 #include <math.h>
 
 #include "tq_attention.cuh"
 #include "tq_common.cuh"
+#include "tq_rows.cuh"
 #include "tq_simt.cuh"
 #include "tq_tcgen05.cuh"
 
@@ -67,10 +78,19 @@ struct Tracer2 {
   int role, n;
   __device__ Tracer2(bool on_, int role_) : on(on_), role(role_), n(0) {}
   __device__ __forceinline__ void mark(int ev, int tile) {
-    if (!on || n >= kTraceCap2 / 3) return;
-    const int i = role * (kTraceCap2 / 3) + n++;
+    if (!on || n >= kTraceCap2 / 4) return;
+    const int i = role * (kTraceCap2 / 4) + n++;
     g_trace2[2 * i] = ((long long)role << 32) | ((long long)ev << 16) | (long long)tile;
     g_trace2[2 * i + 1] = clock64();
+  }
+  // wall-clock nanoseconds next to the SM clock: their ratio over a CTA's life is the SM frequency under load
+  __device__ __forceinline__ void mark_ns(int ev, int tile) {
+    if (!on || n >= kTraceCap2 / 4) return;
+    const int i = role * (kTraceCap2 / 4) + n++;
+    long long ns;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
+    g_trace2[2 * i] = ((long long)role << 32) | ((long long)ev << 16) | (long long)tile;
+    g_trace2[2 * i + 1] = ns;
   }
 };
 
@@ -80,8 +100,9 @@ constexpr int kHalfN = 64;
 constexpr int kSoftmax = 256;      // 8 softmax warps: two threads per query row, 64 score columns each
                                    // (16 warps were measured slower: the exp2 throughput, not the thread count, bounds the phase)
 constexpr int kProducers = 256;    // 8 producer warps
-constexpr int kThreads = kSoftmax + kProducers + 32;
-constexpr int kCtlWarp = kThreads / 32 - 1;
+constexpr int kThreads = kSoftmax + kProducers + 64;
+constexpr int kCtlWarp = kThreads / 32 - 2;   // tensor-memory allocation; issues the score MMAs in the leader CTA
+constexpr int kPvWarp = kThreads / 32 - 1;    // issues the P V_hat MMAs in the leader CTA
 constexpr int kSoftmaxArrivals = 2 * kSoftmax / 32;     // softmax warps of both CTAs
 constexpr int kProducerArrivals = 2 * kProducers / 32;  // producer warps of both CTAs
 
@@ -118,11 +139,23 @@ struct C2Smem {
   static constexpr uint32_t kColO = D + 2 * kBN;                // O: D
   static constexpr uint32_t kCols = 512;
   static_assert(kColO + D <= kCols, "tensor memory over-subscribed");
+  // Prologue operands borrow the far end of the rings, so that the first two K_hat tiles can be decoded
+  // meanwhile: raw query tile [128, D] in V_hat stages 0-1, half of [Pi ; coeff S] ([D, D]) in K_hat
+  // stage 2.  Epilogue: Pi_v^T half [D/2, D] in K_hat stage 0, the output tile (for coalesced stores)
+  // from K_hat stage 1 on.  All operands K-major with 8-row groups kSboW apart.
+  static constexpr uint32_t kSboW = G * 128;
+  static constexpr uint32_t kQOff = kVOff;
+  static constexpr uint32_t kWOff = kKOff + 2 * kKStage;
+  static constexpr uint32_t kUOff = kKOff;
+  static constexpr uint32_t kOutOff = kKOff + kKStage;
+  static_assert(kStages == 3 && kBM * D * 2 <= 2 * kVStage && D * D * 2 <= kKStage, "prologue operands must fit");
+  static_assert((D / 2) * D * 2 <= kKStage && kBM * (D * 4 + 16) <= kPkOff - kOutOff, "epilogue operands must fit");
+  static_assert(2 * D <= 2 * kBN, "the Q_cat accumulator borrows both score tiles");
 };
 
 template <int D, int BITS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-attention_c2_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const int pair_heads) {
+attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
   using L = C2Smem<D, BITS>;
   constexpr int G = L::G, KB = L::KB, VB = L::VB, kStages = L::kStages;
   constexpr int NQ = kSoftmax / kBM;  // threads per query row
@@ -135,7 +168,7 @@ attention_c2_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
   __shared__ float xmax[2][kSoftmax / kBM][kBM];  // [tile parity][column part][row]
   __shared__ uint32_t lutK[1 << (2 * KB)];
   __shared__ uint32_t lutV[1 << (2 * VB)];
-  __shared__ __align__(8) uint64_t bars[4 * kStages + 8 + 2 + 4 + 1];
+  __shared__ __align__(8) uint64_t bars[4 * kStages + 8 + 2 + 4 + 4];
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
   volatile int* abort_flag = &s_abort;
@@ -176,6 +209,9 @@ attention_c2_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
   auto pk_full = [&](int i) { return bar0 + 8u * (4 * kStages + 8 + i); };  // local
   auto xch = [&](int i) { return bar0 + 8u * (4 * kStages + 10 + i); };     // local
   const uint32_t q_full = bar0 + 8u * (4 * kStages + 14);                   // leader
+  const uint32_t qp_full = bar0 + 8u * (4 * kStages + 15);                  // leader
+  const uint32_t qp_done = bar0 + 8u * (4 * kStages + 16);                  // both
+  const uint32_t e_done = bar0 + 8u * (4 * kStages + 17);                   // both
   // one arrival on a barrier that lives in rank 0: local form there, cluster address from the peer
   auto arrive_leader = [&](uint32_t bar) {
     if (rank == 0) tc::mbar_arrive(bar);
@@ -197,6 +233,9 @@ attention_c2_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
     }
     for (int i = 0; i < 4; ++i) tc::mbar_init(xch(i), 32 * (kSoftmax / kBM));
     tc::mbar_init(q_full, kSoftmaxArrivals);
+    tc::mbar_init(qp_full, kSoftmaxArrivals + kProducerArrivals);
+    tc::mbar_init(qp_done, 1);
+    tc::mbar_init(e_done, 1);
     tc::fence_mbar_init();
   }
   if (warp == kCtlWarp) tc::tmem_alloc2(tc::smem_u32(&tmem_slot), L::kCols);
@@ -209,9 +248,10 @@ attention_c2_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
   const uint32_t tmem_base = tmem_slot;
   const uint32_t tmem_o = tmem_base + L::kColO;
   bool ok = true;
-  Tracer2 tr(g_trace2_on != 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 &&
-                 (warp == 0 || warp == kSoftmax / 32 || warp == kCtlWarp),
-             warp == 0 ? 0 : warp == kSoftmax / 32 ? 1 : 2);
+  // traced: the heaviest cluster of the last (head pair, batch), which runs late in the launch
+  Tracer2 tr(g_trace2_on != 0 && blockIdx.x == 0 && blockIdx.y == gridDim.y - 1 && blockIdx.z == gridDim.z - 1 && lane == 0 &&
+                 (warp == 0 || warp == kSoftmax / 32 || warp >= kCtlWarp),
+             warp == 0 ? 0 : warp == kSoftmax / 32 ? 1 : warp == kCtlWarp ? 2 : 3);
 
   if (warp < kSoftmax / 32) {
     // =============================== softmax warps ===============================
@@ -220,25 +260,53 @@ attention_c2_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
     const int qi = q0 + row;
     const int64_t qrow = (b * a.Hq + head) * a.Sq + qi;
     const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
-    if (n_tiles > 0) {  // query row -> tensor memory: 2D bf16 = D columns, each of the row's threads stores D/NQ
-      const bool live = qi < a.Sq;
-      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.q_cat) + qrow * 2 * D) +
-                         chalf * (D / (4 * NQ));
-#pragma unroll 1
-      for (int c0 = 0; c0 < D / NQ; c0 += 32) {
-        uint32_t w[32];
+    tr.mark(10, 999);
+    tr.mark_ns(18, 999);
+    if (n_tiles > 0) {
+      // raw query tile [128, D] -> A operand of the prologue MMA (8 threads fill one 128-byte core matrix)
+      constexpr int NA = kBM * G / kSoftmax;
+      uint8_t* Aq = smem_raw + L::kQOff;
+      const int64_t qbase = b * x.q_stride_b + head * x.q_stride_h;
+      uint4 v[NA];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          uint4 v = make_uint4(0, 0, 0, 0);
-          if (live) v = src[c0 / 4 + i];
-          w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
-        }
-        tc::tmem_st32(tmem_base + L::kColQ + lane_base + chalf * (D / NQ) + c0, w);
+      for (int i = 0; i < NA; ++i) {
+        const int e = i * kSoftmax + tid, r = e % 8 + 8 * (e / (8 * G)), c = (e / 8) % G;
+        v[i] = make_uint4(0, 0, 0, 0);
+        if (q0 + r < a.Sq) v[i] = load_row_chunk_bf16(x.q, x.q_dtype, qbase + (int64_t)(q0 + r) * x.q_stride_s + c * 8);
       }
-      tc::wait_st();
-      tc::fence_before_sync();
+      tr.mark(20, 999);
+#pragma unroll
+      for (int i = 0; i < NA; ++i) {
+        const int e = i * kSoftmax + tid, r = e % 8 + 8 * (e / (8 * G)), c = (e / 8) % G;
+        *reinterpret_cast<uint4*>(Aq + (r / 8) * L::kSboW + c * 128 + (r % 8) * 16) = v[i];
+      }
+      tr.mark(21, 999);
+      tc::fence_async_smem();
+      tr.mark(22, 999);
       __syncwarp();
-      if (lane == 0) arrive_leader(q_full);
+      if (lane == 0) arrive_leader(qp_full);
+      tr.mark(11, 999);
+      // Q_cat row (fp32, 2D columns over both score tiles) -> packed bf16 in the query columns; each of
+      // the row's threads converts 2D/NQ accumulator columns
+      if ((ok = tc::mbar_wait_or_abort(qp_done, 0, abort_flag))) {
+        tc::fence_after_sync();
+        tr.mark(12, 999);
+#pragma unroll 1
+        for (int c0 = 0; c0 < 2 * D / NQ; c0 += 32) {
+          uint32_t raw[32], pw[16];
+          tc::tmem_ld32(tmem_base + L::kColS + lane_base + chalf * (2 * D / NQ) + c0, raw);
+          tc::wait_ld();
+#pragma unroll
+          for (int c = 0; c < 16; ++c)
+            pw[c] = tc::pack_bf16x2(__uint_as_float(raw[2 * c]), __uint_as_float(raw[2 * c + 1]));
+          tc::tmem_st16(tmem_base + L::kColQ + lane_base + chalf * (D / NQ) + c0 / 2, pw);
+        }
+        tc::wait_st();
+        tc::fence_before_sync();
+        __syncwarp();
+        if (lane == 0) arrive_leader(q_full);
+        tr.mark(13, 999);
+      }
     }
     float m_run = -INFINITY, l_run = 0.f;
     const float cexp = a.sm_scale * kLog2e, rcexp = 1.f / cexp;  // K_hat carries the key norms: S is the raw score
@@ -334,9 +402,20 @@ attention_c2_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
       if (lane == 0) arrive_leader(p_full(bb));
       tr.mark(5, j);
     }
-    // ---- epilogue: normalise and store the rotated output row ----
-    if (ok && n_tiles > 0)
+    // ---- epilogue: out = (O / l) Pi_v on the tensor pipe ----
+    // This CTA's half of Pi_v^T (output coordinates [D/2 rank, +D/2), all D contraction columns) goes to
+    // K_hat stage 0, free once the last MMA has drained; fetch it before waiting for that.
+    constexpr int NW = (D / 2) * G / kSoftmax;
+    uint4 wu[NW];
+    if (ok && n_tiles > 0) {
+#pragma unroll
+      for (int i = 0; i < NW; ++i) {
+        const int e = i * kSoftmax + tid, r = e % 8 + 8 * (e / (8 * G)), c = (e / 8) % G;
+        wu[i] = *reinterpret_cast<const uint4*>(x.w_unrot + ((int64_t)rank * (D / 2) + r) * D + c * 8);
+      }
       ok = tc::mbar_wait_or_abort(pv_done((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, abort_flag);
+      tr.mark(14, 999);
+    }
     if (ok && n_tiles > 0) {
       xmax[n_tiles & 1][chalf][row] = l_run;
       tc::mbar_arrive(xch(quad));
@@ -344,28 +423,66 @@ attention_c2_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
     }
     if (ok && n_tiles > 0) {
       tc::fence_after_sync();
+      uint8_t* Bu = smem_raw + L::kUOff;
+#pragma unroll
+      for (int i = 0; i < NW; ++i) {
+        const int e = i * kSoftmax + tid, r = e % 8 + 8 * (e / (8 * G)), c = (e / 8) % G;
+        *reinterpret_cast<uint4*>(Bu + (r / 8) * L::kSboW + c * 128 + (r % 8) * 16) = wu[i];
+      }
       float l_tot = l_run;
 #pragma unroll
       for (int o = 1; o < NQ; ++o) l_tot += xmax[n_tiles & 1][(chalf + o) % NQ][row];
       const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-      __nv_bfloat16* dst = o_rot + qrow * D + chalf * (D / NQ);
+      // normalised output row as packed bf16 over the (retired) first score tile: A operand
 #pragma unroll 1
       for (int c0 = 0; c0 < D / NQ; c0 += 32) {
-        uint32_t raw[32];
+        uint32_t raw[32], pw[16];
         tc::tmem_ld32(tmem_o + lane_base + chalf * (D / NQ) + c0, raw);
         tc::wait_ld();
-        if (qi < a.Sq) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint4 w;
-            w.x = tc::pack_bf16x2(__uint_as_float(raw[8 * i]) * inv, __uint_as_float(raw[8 * i + 1]) * inv);
-            w.y = tc::pack_bf16x2(__uint_as_float(raw[8 * i + 2]) * inv, __uint_as_float(raw[8 * i + 3]) * inv);
-            w.z = tc::pack_bf16x2(__uint_as_float(raw[8 * i + 4]) * inv, __uint_as_float(raw[8 * i + 5]) * inv);
-            w.w = tc::pack_bf16x2(__uint_as_float(raw[8 * i + 6]) * inv, __uint_as_float(raw[8 * i + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + c0 + 8 * i) = w;
-          }
-        }
+        for (int c = 0; c < 16; ++c)
+          pw[c] = tc::pack_bf16x2(__uint_as_float(raw[2 * c]) * inv, __uint_as_float(raw[2 * c + 1]) * inv);
+        tc::tmem_st16(tmem_base + L::kColS + lane_base + chalf * (D / (2 * NQ)) + c0 / 2, pw);
       }
+      tc::wait_st();
+      tc::fence_async_smem();
+      tc::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) arrive_leader(q_full);  // second phase of this barrier
+      tr.mark(15, 999);
+      ok = tc::mbar_wait_or_abort(e_done, 0, abort_flag);
+      tr.mark(16, 999);
+    }
+    if (ok && n_tiles > 0) {
+      // accumulator row -> output dtype -> shared memory (padded rows), so that whole rows leave coalesced
+      tc::fence_after_sync();
+      const int esz = a.out_dtype == TQ_F32 ? 4 : 2;
+      const int pitch = D * esz + 16;
+      uint8_t* Ot = smem_raw + L::kOutOff;
+#pragma unroll 1
+      for (int c0 = 0; c0 < D / NQ; c0 += 32) {
+        uint32_t acc[32];
+        tc::tmem_ld32(tmem_base + L::kColS + kBN + lane_base + chalf * (D / NQ) + c0, acc);
+        tc::wait_ld();
+        store_row_chunk(Ot + row * pitch, a.out_dtype, chalf * (D / NQ) + c0, acc);
+      }
+      tc::mbar_arrive(xch(quad));
+      ok = tc::mbar_wait_or_abort(xch(quad), (n_tiles + 1) & 1, abort_flag);
+    }
+    if (ok && n_tiles > 0) {
+      // the two warps of the quadrant store 16 of its 32 rows each
+      const int esz = a.out_dtype == TQ_F32 ? 4 : 2;
+      const int pitch = D * esz + 16, cpr = D * esz / 16;  // 16-byte chunks per row
+      const uint8_t* Ot = smem_raw + L::kOutOff;
+      uint8_t* obase = static_cast<uint8_t*>(a.out) + (b * a.o_stride_b + head * a.o_stride_h) * esz;
+      for (int idx = lane; idx < 16 * cpr; idx += 32) {
+        const int r = quad * 32 + chalf * 16 + idx / cpr, c = idx % cpr;
+        if (q0 + r < a.Sq)
+          *reinterpret_cast<uint4*>(obase + (int64_t)(q0 + r) * a.o_stride_s * esz + c * 16) =
+              *reinterpret_cast<const uint4*>(Ot + r * pitch + c * 16);
+      }
+      tr.mark(17, 999);
+      tr.mark_ns(19, 999);
     }
   } else if (warp < kCtlWarp) {
     // =============================== producer warps ===============================
@@ -432,7 +549,27 @@ attention_c2_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
       vkey[i] = (e % 8) + 8 * (e / (8 * GPV));
       vgp[i] = (e / 8) % GPV;
     }
-    if (n_tiles > 0) prefetch(0);
+    if (n_tiles > 0) {
+      prefetch(0);
+      // this CTA's half of [Pi ; coeff S] -> B operand of the prologue MMA
+      constexpr int NB = D * G / kProducers;
+      uint8_t* Bw = smem_raw + L::kWOff;
+      const __nv_bfloat16* wsrc = x.w_cat + (int64_t)rank * D * D;
+      uint4 v[NB];
+#pragma unroll
+      for (int i = 0; i < NB; ++i) {
+        const int e = i * kProducers + p, r = e % 8 + 8 * (e / (8 * G)), c = (e / 8) % G;
+        v[i] = *reinterpret_cast<const uint4*>(wsrc + r * D + c * 8);
+      }
+#pragma unroll
+      for (int i = 0; i < NB; ++i) {
+        const int e = i * kProducers + p, r = e % 8 + 8 * (e / (8 * G)), c = (e / 8) % G;
+        *reinterpret_cast<uint4*>(Bw + (r / 8) * L::kSboW + c * 128 + (r % 8) * 16) = v[i];
+      }
+      tc::fence_async_smem();
+      __syncwarp();
+      if (lane == 0) arrive_leader(qp_full);
+    }
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int st = j % kStages, u = j / kStages, ps = j & 1;
       uint8_t* pk = smem_raw + L::kPkOff + ps * L::kPkStage;
@@ -456,6 +593,7 @@ attention_c2_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
       if (j + 1 < n_tiles) prefetch((j + 1) * kBN);
       tr.mark(6, j);
       if (u >= 1 && !(ok = tc::mbar_wait_or_abort(k_empty(st), (u - 1) & 1, abort_flag))) break;
+      if (j == 2 && !(ok = tc::mbar_wait_or_abort(qp_done, 0, abort_flag))) break;  // stage 2 held a prologue operand
       tr.mark(2, j);
       // ---- keys ----
       uint8_t* Kd = smem_raw + L::kKOff + st * L::kKStage;
@@ -504,6 +642,7 @@ attention_c2_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
       tr.mark(3, j);
       // ---- values ----
       if (u >= 1 && !(ok = tc::mbar_wait_or_abort(v_empty(st), (u - 1) & 1, abort_flag))) break;
+      if (j < 2 && !(ok = tc::mbar_wait_or_abort(qp_done, 0, abort_flag))) break;  // stages 0, 1 held the raw query tile
       tr.mark(4, j);
       uint8_t* Vd = smem_raw + L::kVOff + st * L::kVStage;
       {
@@ -546,17 +685,31 @@ attention_c2_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
       if (lane == 0) arrive_leader(v_full(st));
       tr.mark(5, j);
     }
-  } else if (rank == 0 && lane == 0) {
-    // =============================== MMA issuer (leader CTA) ===============================
+  } else if (warp == kCtlWarp && rank == 0 && lane == 0) {
+    // =============================== score MMA issuer (leader CTA) ===============================
+    // Two issuing threads, because issuing one tile's 24 MMAs and their commits from a single thread took
+    // longer than the softmax of a tile; every dependency between the two streams goes through an mbarrier.
     constexpr uint32_t idesc_s = tc::idesc_bf16(2 * kBM, kBN, false, false);
-    constexpr uint32_t idesc_o = tc::idesc_bf16(2 * kBM, D, false, true);
-    auto issue_scores = [&](int j) -> bool {
+    constexpr uint32_t idesc_q = tc::idesc_bf16(2 * kBM, 2 * D, false, false);
+    if (n_tiles > 0 && (ok = tc::mbar_wait_or_abort(qp_full, 0, abort_flag))) {
+      // Q_cat (fp32, over both score tiles) = raw tile [128, D] x half of [Pi ; coeff S] from each CTA
+      tc::fence_after_sync();
+      const uint64_t adesc = tc::smem_desc(tc::smem_u32(smem_raw + L::kQOff), 128, L::kSboW);
+      const uint64_t bdesc = tc::smem_desc(tc::smem_u32(smem_raw + L::kWOff), 128, L::kSboW);
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks)
+        tc::mma_bf16_ss2(tmem_base + L::kColS, adesc + (uint64_t)(ks * 256 >> 4), bdesc + (uint64_t)(ks * 256 >> 4),
+                         idesc_q, ks > 0);
+      tc::mma_commit2(qp_done, 3);
+    }
+    if (ok && n_tiles > 0) ok = tc::mbar_wait_or_abort(q_full, 0, abort_flag);
+    for (int j = 0; j < n_tiles && ok; ++j) {
       const int bb = j & 1, st = j % kStages;
       tr.mark(0, j);
-      if (!tc::mbar_wait_cluster_or_abort(k_full(st), (j / kStages) & 1, abort_flag)) return false;
+      if (!(ok = tc::mbar_wait_or_abort(k_full(st), (j / kStages) & 1, abort_flag))) break;
+      // S[bb] is free once P[bb] of tile j-2, which lives in the same columns, has been consumed
+      if (j >= 2 && !(ok = tc::mbar_wait_or_abort(pv_done(bb), ((j - 2) >> 1) & 1, abort_flag))) break;
       tr.mark(1, j);
-      // S[bb] is free: P[bb] of tile j-2 lives in the same columns, its p_full was awaited before the
-      // P V_hat MMA of tile j-2 was issued, and that MMA precedes this one on the tensor pipe
       tc::fence_after_sync();
       const uint64_t kdesc = tc::smem_desc(tc::smem_u32(smem_raw + L::kKOff + st * L::kKStage), 128, L::kSboK);
 #pragma unroll
@@ -566,17 +719,17 @@ attention_c2_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
       tc::mma_commit2(s_full(bb), 3);
       tc::mma_commit2(k_empty(st), 3);
       tr.mark(2, j);
-      return true;
-    };
-    if (n_tiles > 0) ok = tc::mbar_wait_cluster_or_abort(q_full, 0, abort_flag);
-    if (ok && n_tiles > 0) ok = issue_scores(0);
+    }
+  } else if (warp == kPvWarp && rank == 0 && lane == 0) {
+    // =============================== P V_hat MMA issuer (leader CTA) ===============================
+    constexpr uint32_t idesc_o = tc::idesc_bf16(2 * kBM, D, false, true);
+    constexpr uint32_t idesc_e = tc::idesc_bf16(2 * kBM, D, false, false);
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int bb = j & 1, u = j >> 1, st = j % kStages;
-      if (j + 1 < n_tiles && !(ok = issue_scores(j + 1))) break;
       tr.mark(3, j);
-      if (!(ok = tc::mbar_wait_cluster_or_abort(v_full(st), (j / kStages) & 1, abort_flag))) break;
+      if (!(ok = tc::mbar_wait_or_abort(v_full(st), (j / kStages) & 1, abort_flag))) break;
       tr.mark(4, j);
-      if (!(ok = tc::mbar_wait_cluster_or_abort(p_full(bb), u & 1, abort_flag))) break;
+      if (!(ok = tc::mbar_wait_or_abort(p_full(bb), u & 1, abort_flag))) break;
       tc::fence_after_sync();
       tr.mark(5, j);
       const uint64_t vdesc = tc::smem_desc(tc::smem_u32(smem_raw + L::kVOff + st * L::kVStage), L::kLboV, L::kSboV);
@@ -588,6 +741,16 @@ attention_c2_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
       tc::mma_commit2(v_empty(st), 3);
       tr.mark(6, j);
     }
+    if (ok && n_tiles > 0 && (ok = tc::mbar_wait_or_abort(q_full, 1, abort_flag))) {
+      // out tile (fp32, second score tile) = normalised bf16 output tile x Pi_v
+      tc::fence_after_sync();
+      const uint64_t bdesc = tc::smem_desc(tc::smem_u32(smem_raw + L::kUOff), 128, L::kSboW);
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks)
+        tc::mma_bf16_ts2(tmem_base + L::kColS + kBN, tmem_base + L::kColS + ks * 8, bdesc + (uint64_t)(ks * 256 >> 4),
+                         idesc_e, ks > 0);
+      tc::mma_commit2(e_done, 3);
+    }
   }
   if (!ok && atomicExch(&s_abort, 2) != 2) atomicAdd(&g_c2_faults, 1ull);  // one fault per CTA
   tc::fence_before_sync();
@@ -597,7 +760,7 @@ attention_c2_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
 }
 
 template <int D, int BITS>
-int launch_c2(const AttnArgs& a, int64_t B, __nv_bfloat16* o_rot, cudaStream_t stream) {
+int launch_c2(const AttnArgs& a, const PairArgs& x, int64_t B, cudaStream_t stream) {
   constexpr size_t smem = C2Smem<D, BITS>::kTotal > 120 * 1024 ? C2Smem<D, BITS>::kTotal : 120 * 1024;
   auto kern = attention_c2_kernel<D, BITS>;
   TQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -608,7 +771,7 @@ int launch_c2(const AttnArgs& a, int64_t B, __nv_bfloat16* o_rot, cudaStream_t s
             (unsigned)B);
   {
     ProfScope prof(kProfAttention, stream);
-    kern<<<grid, kThreads, smem, stream>>>(a, o_rot, pair_heads);
+    kern<<<grid, kThreads, smem, stream>>>(a, x, pair_heads);
   }
   TQ_CUDA_OK(cudaGetLastError());
   return TQ_OK;
@@ -616,11 +779,10 @@ int launch_c2(const AttnArgs& a, int64_t B, __nv_bfloat16* o_rot, cudaStream_t s
 
 }  // namespace
 
-int attention_c2(const AttnArgs& a, int64_t B, int d, int bits, void* o_rot, cudaStream_t stream) {
-  __nv_bfloat16* o = static_cast<__nv_bfloat16*>(o_rot);
+int attention_c2(const AttnArgs& a, const PairArgs& x, int64_t B, int d, int bits, cudaStream_t stream) {
   if (d == 128)
-    return bits == 2 ? launch_c2<128, 2>(a, B, o, stream) : bits == 3 ? launch_c2<128, 3>(a, B, o, stream)
-                                                                      : launch_c2<128, 4>(a, B, o, stream);
+    return bits == 2 ? launch_c2<128, 2>(a, x, B, stream) : bits == 3 ? launch_c2<128, 3>(a, x, B, stream)
+                                                                      : launch_c2<128, 4>(a, x, B, stream);
   return fail(TQ_ERR_UNSUPPORTED, "the SM-pair attention kernel is built for head_dim 128 only");
 }
 

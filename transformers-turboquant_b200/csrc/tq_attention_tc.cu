@@ -20,6 +20,7 @@
 
 #include "tq_attention.cuh"
 #include "tq_common.cuh"
+#include "tq_rows.cuh"
 #include "tq_simt.cuh"
 #include "tq_tcgen05.cuh"
 
@@ -83,51 +84,6 @@ struct RowsGemmArgs {
   int64_t os_b, os_h, os_s;        // element strides of out (rows of NOUT contiguous elements)
   int num_tiles;
 };
-
-__device__ __forceinline__ uint4 load_row_chunk_bf16(const void* base, int dtype, int64_t off) {
-  if (dtype == TQ_BF16) return *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(base) + off);
-  float v[8];
-  if (dtype == TQ_F32) load8<float>(static_cast<const float*>(base) + off, v);
-  else load8<__half>(static_cast<const __half*>(base) + off, v);
-  uint4 r;
-  r.x = tc::pack_bf16x2(v[0], v[1]);
-  r.y = tc::pack_bf16x2(v[2], v[3]);
-  r.z = tc::pack_bf16x2(v[4], v[5]);
-  r.w = tc::pack_bf16x2(v[6], v[7]);
-  return r;
-}
-
-__device__ __forceinline__ void store_row_chunk(void* base, int dtype, int64_t off, const uint32_t (&acc)[32]) {
-  // 32 fp32 accumulator values -> 32 consecutive output elements
-  if (dtype == TQ_F32) {
-    float4* p = reinterpret_cast<float4*>(static_cast<float*>(base) + off);
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-      p[i] = make_float4(__uint_as_float(acc[4 * i]), __uint_as_float(acc[4 * i + 1]),
-                         __uint_as_float(acc[4 * i + 2]), __uint_as_float(acc[4 * i + 3]));
-  } else if (dtype == TQ_BF16) {
-    uint4* p = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(base) + off);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      uint4 w;
-      w.x = tc::pack_bf16x2(__uint_as_float(acc[8 * i]), __uint_as_float(acc[8 * i + 1]));
-      w.y = tc::pack_bf16x2(__uint_as_float(acc[8 * i + 2]), __uint_as_float(acc[8 * i + 3]));
-      w.z = tc::pack_bf16x2(__uint_as_float(acc[8 * i + 4]), __uint_as_float(acc[8 * i + 5]));
-      w.w = tc::pack_bf16x2(__uint_as_float(acc[8 * i + 6]), __uint_as_float(acc[8 * i + 7]));
-      p[i] = w;
-    }
-  } else {
-    uint4* p = reinterpret_cast<uint4*>(static_cast<__half*>(base) + off);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      __half2 h[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e)
-        h[e] = __floats2half2_rn(__uint_as_float(acc[8 * i + 2 * e]), __uint_as_float(acc[8 * i + 2 * e + 1]));
-      p[i] = *reinterpret_cast<uint4*>(h);
-    }
-  }
-}
 
 // 128 threads; thread t owns row t of the 128-row tile (tensor-memory lane t).
 template <int D, int NOUT>
@@ -854,14 +810,19 @@ int attention_fwd_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_t 
 
   build_wunrot_kernel<<<d, d, 0, stream>>>(a.Pi_v, d, w_unrot);
   TQ_CUDA_OK(cudaGetLastError());
+  if (d == 128 && use_sm_pairs()) {
+    // the SM-pair kernel prepares its query tiles and back-rotates its outputs itself
+    build_wcat_kernel<<<d, d, 0, stream>>>(Pi_k, S_eff, d, sqrtf(1.5707963267948966f) / (float)d, w_cat);
+    TQ_CUDA_OK(cudaGetLastError());
+    const PairArgs x{q, dtype, sb, sh, ss, w_cat, w_unrot};
+    return attention_c2(a, x, B, d, bits, stream);
+  }
   if (int st = prepare_queries_bf16(q, dtype, B, Hq, Sq, d, sb, sh, ss, Pi_k, S_eff, w_cat, q_cat, stream)) return st;
   const int tiles = (int)((n_q + 127) / 128);
 
   a.q_cat = q_cat;
   int st;
-  if (d == 128 && use_sm_pairs())
-    st = attention_c2(a, B, d, bits, o_rot, stream);
-  else if (d == 128)
+  if (d == 128)
     st = bits == 2   ? launch_attention_tc<128, 2>(a, B, o_rot, stream)
          : bits == 3 ? launch_attention_tc<128, 3>(a, B, o_rot, stream)
                      : launch_attention_tc<128, 4>(a, B, o_rot, stream);

@@ -248,27 +248,10 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
-// Bounded wait on a local mbarrier whose arrivals may come from the peer CTA (cluster-scope acquire).
-__device__ __forceinline__ bool mbar_wait_cluster_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                                           long long limit = 400000000ll) {
-  const long long t0 = clock64();
-  for (;;) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity), "r"(500u)
-        : "memory");
-    if (ok) return true;
-    if (*abort_flag) return false;
-    if (clock64() - t0 > limit) {
-      *abort_flag = 1;
-      return false;
-    }
-  }
-}
+// Waiting on a local mbarrier whose arrivals come from the peer CTA uses the plain (CTA-scope) forms
+// above: the peer publishes its shared-memory writes to the async proxy before it arrives, and only the
+// tensor pipe reads them.  A cluster-scope acquire on every wait was measured at ~400 cycles each, which
+// made the MMA-issuing thread the bottleneck of the SM-pair kernel.
 // Whole-warp calls, executed by the same warp index in BOTH CTAs of the pair.
 __device__ __forceinline__ void tmem_alloc2(uint32_t slot_saddr, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_saddr), "r"(ncols)
@@ -288,6 +271,17 @@ __device__ __forceinline__ void mma_bf16_ts2(uint32_t tmem_d, uint32_t tmem_a, u
       "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
       :
       : "r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Same with A in shared memory: each CTA's 128 rows of A at the same shared-memory offset in both.
+__device__ __forceinline__ void mma_bf16_ss2(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      :
+      : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 // Arrive on the mbarrier at this shared-memory offset in every CTA of `cta_mask` once all MMAs issued
