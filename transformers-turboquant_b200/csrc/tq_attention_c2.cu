@@ -130,7 +130,10 @@ struct C2Smem {
   static constexpr uint32_t kKOff = 0;
   static constexpr uint32_t kVOff = kKOff + kStages * kKStage;
   static constexpr uint32_t kPkOff = kVOff + kStages * kVStage;
-  static constexpr uint32_t kTotal = kPkOff + 2 * kPkStage;
+  static constexpr uint32_t kUOff = kPkOff + 2 * kPkStage;      // this CTA's half of Pi_v^T, [D/2, D] K-major
+  static constexpr uint32_t kUBytes = (D / 2) * D * 2;
+  static constexpr uint32_t kWBytes = D * D * 2;                // this CTA's half of [Pi ; coeff S]
+  static constexpr uint32_t kTotal = kUOff + kUBytes;
   static constexpr uint32_t kSboK = 2 * G * 128;                // K-major [keys, 2D]
   static constexpr uint32_t kSboV = 128;                        // MN-major [d/2, 128 keys]: coordinate chunks adjacent
   static constexpr uint32_t kLboV = (G / 2) * 128;              // ... 8-key groups G/2 core matrices apart
@@ -141,15 +144,15 @@ struct C2Smem {
   static_assert(kColO + D <= kCols, "tensor memory over-subscribed");
   // Prologue operands borrow the far end of the rings, so that the first two K_hat tiles can be decoded
   // meanwhile: raw query tile [128, D] in V_hat stages 0-1, half of [Pi ; coeff S] ([D, D]) in K_hat
-  // stage 2.  Epilogue: Pi_v^T half [D/2, D] in K_hat stage 0, the output tile (for coalesced stores)
-  // from K_hat stage 1 on.  All operands K-major with 8-row groups kSboW apart.
+  // stage 2.  Epilogue: the output tile is staged over the K_hat ring for coalesced stores.  All operands
+  // K-major with 8-row groups kSboW apart; the two constant ones arrive by bulk copy (their global image
+  // has this layout already).
   static constexpr uint32_t kSboW = G * 128;
   static constexpr uint32_t kQOff = kVOff;
   static constexpr uint32_t kWOff = kKOff + 2 * kKStage;
-  static constexpr uint32_t kUOff = kKOff;
-  static constexpr uint32_t kOutOff = kKOff + kKStage;
+  static constexpr uint32_t kOutOff = kKOff;
   static_assert(kStages == 3 && kBM * D * 2 <= 2 * kVStage && D * D * 2 <= kKStage, "prologue operands must fit");
-  static_assert((D / 2) * D * 2 <= kKStage && kBM * (D * 4 + 16) <= kPkOff - kOutOff, "epilogue operands must fit");
+  static_assert(kBM * (D * 4 + 16) <= kPkOff - kOutOff, "the output tile must fit");
   static_assert(2 * D <= 2 * kBN, "the Q_cat accumulator borrows both score tiles");
 };
 
@@ -168,7 +171,7 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
   __shared__ float xmax[2][kSoftmax / kBM][kBM];  // [tile parity][column part][row]
   __shared__ uint32_t lutK[1 << (2 * KB)];
   __shared__ uint32_t lutV[1 << (2 * VB)];
-  __shared__ __align__(8) uint64_t bars[4 * kStages + 8 + 2 + 4 + 4];
+  __shared__ __align__(8) uint64_t bars[4 * kStages + 8 + 2 + 4 + 7];
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
   volatile int* abort_flag = &s_abort;
@@ -212,6 +215,9 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
   const uint32_t qp_full = bar0 + 8u * (4 * kStages + 15);                  // leader
   const uint32_t qp_done = bar0 + 8u * (4 * kStages + 16);                  // both
   const uint32_t e_done = bar0 + 8u * (4 * kStages + 17);                   // both
+  const uint32_t w_full = bar0 + 8u * (4 * kStages + 18);                   // local, bulk-copy bytes
+  const uint32_t u_full = bar0 + 8u * (4 * kStages + 19);                   // local, bulk-copy bytes
+  const uint32_t u_peer = bar0 + 8u * (4 * kStages + 20);                   // leader: the peer's Pi_v^T half is in
   // one arrival on a barrier that lives in rank 0: local form there, cluster address from the peer
   auto arrive_leader = [&](uint32_t bar) {
     if (rank == 0) tc::mbar_arrive(bar);
@@ -233,10 +239,20 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
     }
     for (int i = 0; i < 4; ++i) tc::mbar_init(xch(i), 32 * (kSoftmax / kBM));
     tc::mbar_init(q_full, kSoftmaxArrivals);
-    tc::mbar_init(qp_full, kSoftmaxArrivals + kProducerArrivals);
+    tc::mbar_init(qp_full, kSoftmaxArrivals + 1);  // + the peer's constant operand
+    tc::mbar_init(w_full, 1);
+    tc::mbar_init(u_full, 1);
+    tc::mbar_init(u_peer, 1);
     tc::mbar_init(qp_done, 1);
     tc::mbar_init(e_done, 1);
     tc::fence_mbar_init();
+    if (!dead) {
+      // constant operands of the prologue and epilogue MMAs: one bulk copy each, no register staging
+      tc::mbar_arrive_expect_tx(w_full, L::kWBytes);
+      tc::bulk_load(tc::smem_u32(smem_raw + L::kWOff), x.w_cat + (int64_t)rank * D * D, L::kWBytes, w_full);
+      tc::mbar_arrive_expect_tx(u_full, L::kUBytes);
+      tc::bulk_load(tc::smem_u32(smem_raw + L::kUOff), x.w_unrot + (int64_t)rank * (D / 2) * D, L::kUBytes, u_full);
+    }
   }
   if (warp == kCtlWarp) tc::tmem_alloc2(tc::smem_u32(&tmem_slot), L::kCols);
   fill_pair_lut<KB>(lutK, a.cen_k, tid, kThreads);
@@ -319,13 +335,17 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
       tc::fence_after_sync();
       tr.mark(1, j);
       float t[HC];
-#pragma unroll
-      for (int c0 = 0; c0 < HC; c0 += 32) {
-        uint32_t raw[32];
-        tc::tmem_ld32(tmem_s + lane_base + chalf * HC + c0, raw);
+      {
+        static_assert(HC == 64, "two 32-column loads per thread");
+        uint32_t raw0[32], raw1[32];
+        tc::tmem_ld32(tmem_s + lane_base + chalf * HC, raw0);
+        tc::tmem_ld32(tmem_s + lane_base + chalf * HC + 32, raw1);
         tc::wait_ld();
 #pragma unroll
-        for (int c = 0; c < 32; ++c) t[c0 + c] = __uint_as_float(raw[c]);
+        for (int c = 0; c < 32; ++c) {
+          t[c] = __uint_as_float(raw0[c]);
+          t[32 + c] = __uint_as_float(raw1[c]);
+        }
       }
       float mx = -INFINITY;
       const bool edge = (k0 + kBN > a.Sk) || (a.causal && k0 + kBN - 1 > q0 + shift) || a.mask != nullptr;
@@ -403,16 +423,7 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
       tr.mark(5, j);
     }
     // ---- epilogue: out = (O / l) Pi_v on the tensor pipe ----
-    // This CTA's half of Pi_v^T (output coordinates [D/2 rank, +D/2), all D contraction columns) goes to
-    // K_hat stage 0, free once the last MMA has drained; fetch it before waiting for that.
-    constexpr int NW = (D / 2) * G / kSoftmax;
-    uint4 wu[NW];
     if (ok && n_tiles > 0) {
-#pragma unroll
-      for (int i = 0; i < NW; ++i) {
-        const int e = i * kSoftmax + tid, r = e % 8 + 8 * (e / (8 * G)), c = (e / 8) % G;
-        wu[i] = *reinterpret_cast<const uint4*>(x.w_unrot + ((int64_t)rank * (D / 2) + r) * D + c * 8);
-      }
       ok = tc::mbar_wait_or_abort(pv_done((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, abort_flag);
       tr.mark(14, 999);
     }
@@ -423,12 +434,6 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
     }
     if (ok && n_tiles > 0) {
       tc::fence_after_sync();
-      uint8_t* Bu = smem_raw + L::kUOff;
-#pragma unroll
-      for (int i = 0; i < NW; ++i) {
-        const int e = i * kSoftmax + tid, r = e % 8 + 8 * (e / (8 * G)), c = (e / 8) % G;
-        *reinterpret_cast<uint4*>(Bu + (r / 8) * L::kSboW + c * 128 + (r % 8) * 16) = wu[i];
-      }
       float l_tot = l_run;
 #pragma unroll
       for (int o = 1; o < NQ; ++o) l_tot += xmax[n_tiles & 1][(chalf + o) % NQ][row];
@@ -445,7 +450,6 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
         tc::tmem_st16(tmem_base + L::kColS + lane_base + chalf * (D / (2 * NQ)) + c0 / 2, pw);
       }
       tc::wait_st();
-      tc::fence_async_smem();
       tc::fence_before_sync();
       __syncwarp();
       if (lane == 0) arrive_leader(q_full);  // second phase of this barrier
@@ -549,27 +553,7 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
       vkey[i] = (e % 8) + 8 * (e / (8 * GPV));
       vgp[i] = (e / 8) % GPV;
     }
-    if (n_tiles > 0) {
-      prefetch(0);
-      // this CTA's half of [Pi ; coeff S] -> B operand of the prologue MMA
-      constexpr int NB = D * G / kProducers;
-      uint8_t* Bw = smem_raw + L::kWOff;
-      const __nv_bfloat16* wsrc = x.w_cat + (int64_t)rank * D * D;
-      uint4 v[NB];
-#pragma unroll
-      for (int i = 0; i < NB; ++i) {
-        const int e = i * kProducers + p, r = e % 8 + 8 * (e / (8 * G)), c = (e / 8) % G;
-        v[i] = *reinterpret_cast<const uint4*>(wsrc + r * D + c * 8);
-      }
-#pragma unroll
-      for (int i = 0; i < NB; ++i) {
-        const int e = i * kProducers + p, r = e % 8 + 8 * (e / (8 * G)), c = (e / 8) % G;
-        *reinterpret_cast<uint4*>(Bw + (r / 8) * L::kSboW + c * 128 + (r % 8) * 16) = v[i];
-      }
-      tc::fence_async_smem();
-      __syncwarp();
-      if (lane == 0) arrive_leader(qp_full);
-    }
+    if (n_tiles > 0) prefetch(0);
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int st = j % kStages, u = j / kStages, ps = j & 1;
       uint8_t* pk = smem_raw + L::kPkOff + ps * L::kPkStage;
@@ -691,7 +675,8 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
     // longer than the softmax of a tile; every dependency between the two streams goes through an mbarrier.
     constexpr uint32_t idesc_s = tc::idesc_bf16(2 * kBM, kBN, false, false);
     constexpr uint32_t idesc_q = tc::idesc_bf16(2 * kBM, 2 * D, false, false);
-    if (n_tiles > 0 && (ok = tc::mbar_wait_or_abort(qp_full, 0, abort_flag))) {
+    if (n_tiles > 0) ok = tc::mbar_wait_or_abort(w_full, 0, abort_flag);
+    if (ok && n_tiles > 0 && (ok = tc::mbar_wait_or_abort(qp_full, 0, abort_flag))) {
       // Q_cat (fp32, over both score tiles) = raw tile [128, D] x half of [Pi ; coeff S] from each CTA
       tc::fence_after_sync();
       const uint64_t adesc = tc::smem_desc(tc::smem_u32(smem_raw + L::kQOff), 128, L::kSboW);
@@ -720,6 +705,12 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
       tc::mma_commit2(k_empty(st), 3);
       tr.mark(2, j);
     }
+  } else if (warp == kCtlWarp && lane == 0) {
+    // peer CTA: tell the leader when this half of [Pi ; coeff S] has landed
+    if (n_tiles > 0 && (ok = tc::mbar_wait_or_abort(w_full, 0, abort_flag))) arrive_leader(qp_full);
+  } else if (warp == kPvWarp && rank != 0 && lane == 0) {
+    // peer CTA: ... and this half of Pi_v^T
+    if (n_tiles > 0 && (ok = tc::mbar_wait_or_abort(u_full, 0, abort_flag))) arrive_leader(u_peer);
   } else if (warp == kPvWarp && rank == 0 && lane == 0) {
     // =============================== P V_hat MMA issuer (leader CTA) ===============================
     constexpr uint32_t idesc_o = tc::idesc_bf16(2 * kBM, D, false, true);
@@ -741,6 +732,7 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
       tc::mma_commit2(v_empty(st), 3);
       tr.mark(6, j);
     }
+    if (ok && n_tiles > 0) ok = tc::mbar_wait_or_abort(u_full, 0, abort_flag) && tc::mbar_wait_or_abort(u_peer, 0, abort_flag);
     if (ok && n_tiles > 0 && (ok = tc::mbar_wait_or_abort(q_full, 1, abort_flag))) {
       // out tile (fp32, second score tile) = normalised bf16 output tile x Pi_v
       tc::fence_after_sync();

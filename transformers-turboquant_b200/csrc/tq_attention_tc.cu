@@ -58,17 +58,26 @@ __device__ __forceinline__ void record_fault() { atomicAdd(&g_wait_faults, 1ull)
 // ---- constant operand builder ------------------------------------------------------------
 // w_cat [2d, d] bf16 = [ Pi ; coeff * S ] with S = S_eff * Pi, so that q * w_cat^T = [q_rot | coeff q_s];
 // w_unrot [d, d] bf16 = Pi_v^T, so that o_rot * w_unrot^T = o_rot * Pi_v.
+// `tile_rows` = 0 stores them row-major.  Otherwise every block of `tile_rows` rows is stored as the
+// K-major operand image a CTA wants in shared memory (8-row groups d*16 bytes apart, 16-byte chunks of a
+// group 128 bytes apart), so that one contiguous bulk copy brings a block in.
+__device__ __forceinline__ int operand_index(int row, int col, int d, int tile_rows) {
+  if (tile_rows == 0) return row * d + col;
+  const int r = row % tile_rows;
+  return (row / tile_rows) * tile_rows * d + (r / 8) * (d * 8) + (col / 8) * 64 + (r % 8) * 8 + col % 8;
+}
 __global__ void build_wcat_kernel(const float* __restrict__ Pi, const float* __restrict__ S_eff, int d, float coeff,
-                                  __nv_bfloat16* __restrict__ w_cat) {
+                                  __nv_bfloat16* __restrict__ w_cat, int tile_rows) {
   const int j = blockIdx.x, i = threadIdx.x;  // one block per row, d threads
-  w_cat[j * d + i] = __float2bfloat16_rn(Pi[j * d + i]);
+  w_cat[operand_index(j, i, d, tile_rows)] = __float2bfloat16_rn(Pi[j * d + i]);
   float acc = 0.f;
   for (int c = 0; c < d; ++c) acc = fmaf(S_eff[j * d + c], Pi[c * d + i], acc);
-  w_cat[(d + j) * d + i] = __float2bfloat16_rn(coeff * acc);
+  w_cat[operand_index(d + j, i, d, tile_rows)] = __float2bfloat16_rn(coeff * acc);
 }
-__global__ void build_wunrot_kernel(const float* __restrict__ Pi_v, int d, __nv_bfloat16* __restrict__ w_unrot) {
+__global__ void build_wunrot_kernel(const float* __restrict__ Pi_v, int d, __nv_bfloat16* __restrict__ w_unrot,
+                                    int tile_rows) {
   const int j = blockIdx.x, i = threadIdx.x;
-  w_unrot[j * d + i] = __float2bfloat16_rn(Pi_v[i * d + j]);
+  w_unrot[operand_index(j, i, d, tile_rows)] = __float2bfloat16_rn(Pi_v[i * d + j]);
 }
 
 // ---- row GEMM ----------------------------------------------------------------------------
@@ -774,7 +783,7 @@ int prepare_queries_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_
   const int64_t n_q = B * Hq * Sq;
   ProfScope prof(kProfPrepareQueries, stream);
   __nv_bfloat16* w_cat = static_cast<__nv_bfloat16*>(w_cat_scratch);
-  build_wcat_kernel<<<d, d, 0, stream>>>(Pi_k, S_eff, d, sqrtf(1.5707963267948966f) / (float)d, w_cat);
+  build_wcat_kernel<<<d, d, 0, stream>>>(Pi_k, S_eff, d, sqrtf(1.5707963267948966f) / (float)d, w_cat, 0);
   TQ_CUDA_OK(cudaGetLastError());
   const int tiles = (int)((n_q + 127) / 128);
   RowsGemmArgs prep{q, dtype, n_q, Hq, Sq, sb, sh, ss, w_cat, q_cat, TQ_BF16,
@@ -808,11 +817,13 @@ int attention_fwd_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_t 
   ws += round256((size_t)n_q * 2 * d * 2);
   __nv_bfloat16* o_rot = reinterpret_cast<__nv_bfloat16*>(ws);
 
-  build_wunrot_kernel<<<d, d, 0, stream>>>(a.Pi_v, d, w_unrot);
+  const bool pairs = d == 128 && use_sm_pairs();
+  build_wunrot_kernel<<<d, d, 0, stream>>>(a.Pi_v, d, w_unrot, pairs ? d / 2 : 0);
   TQ_CUDA_OK(cudaGetLastError());
-  if (d == 128 && use_sm_pairs()) {
-    // the SM-pair kernel prepares its query tiles and back-rotates its outputs itself
-    build_wcat_kernel<<<d, d, 0, stream>>>(Pi_k, S_eff, d, sqrtf(1.5707963267948966f) / (float)d, w_cat);
+  if (pairs) {
+    // the SM-pair kernel prepares its query tiles and back-rotates its outputs itself; each CTA of a pair
+    // bulk-copies its half of either constant operand (d rows of w_cat, d/2 rows of w_unrot)
+    build_wcat_kernel<<<d, d, 0, stream>>>(Pi_k, S_eff, d, sqrtf(1.5707963267948966f) / (float)d, w_cat, d);
     TQ_CUDA_OK(cudaGetLastError());
     const PairArgs x{q, dtype, sb, sh, ss, w_cat, w_unrot};
     return attention_c2(a, x, B, d, bits, stream);

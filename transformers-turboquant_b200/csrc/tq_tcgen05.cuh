@@ -76,6 +76,17 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// One arrival that also announces `bytes` of asynchronous copies which will complete on this barrier.
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Contiguous global -> shared copy by the copy engine (no registers, no load/store unit traffic); both
+// addresses 16-byte aligned, `bytes` a multiple of 16.  Completion is counted on `bar` of this CTA.
+__device__ __forceinline__ void bulk_load(uint32_t dst_saddr, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_saddr),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
 // Hardware-suspended wait: the thread sleeps until the phase completes or ~`hint_ns` pass,
 // so a waiting warp does not burn issue slots the working warps need.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
