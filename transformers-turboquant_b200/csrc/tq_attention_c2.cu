@@ -350,10 +350,15 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
       float mx = -INFINITY;
       const bool edge = (k0 + kBN > a.Sk) || (a.causal && k0 + kBN - 1 > q0 + shift) || a.mask != nullptr;
       if (!edge) {
+        float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;  // three-input maxima, four chains
 #pragma unroll
-        for (int c4 = 0; c4 < HC; c4 += 4)
-          mx = fmaxf(mx, fmaxf(fmaxf(t[c4], t[c4 + 1]), fmaxf(t[c4 + 2], t[c4 + 3])));
-        mx *= cexp;
+        for (int c8 = 0; c8 < HC; c8 += 8) {
+          m0 = tc::fmax3(m0, t[c8], t[c8 + 1]);
+          m1 = tc::fmax3(m1, t[c8 + 2], t[c8 + 3]);
+          m2 = tc::fmax3(m2, t[c8 + 4], t[c8 + 5]);
+          m3 = tc::fmax3(m3, t[c8 + 6], t[c8 + 7]);
+        }
+        mx = fmaxf(tc::fmax3(m0, m1, m2), m3) * cexp;
       } else {
         const float* mrow = (a.mask != nullptr && qi < a.Sq)
                                 ? a.mask + b * a.mask_stride_b + (int64_t)qi * a.mask_stride_q + kc0

@@ -141,6 +141,44 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// 2^x on the FMA pipe instead of the special-function unit: round-to-nearest split x = n + f by the
+// magic-number add, degree-3 minimax polynomial of 2^f on [-0.5, 0.5] (relative error 7.5e-5, far below
+// bf16 rounding), n added into the exponent field by one integer multiply-add.  x is clamped at -126, so
+// the result is never below the smallest normal number (and never exactly 0): callers that need exact
+// zeros for masked scores use fast_exp2.
+__device__ __forceinline__ float exp2_poly(float x) {
+  x = fmaxf(x, -126.f);
+  const float xr = x + 12582912.f;  // 1.5 * 2^23: the integer part lands in the low mantissa bits
+  const float f = x - (xr - 12582912.f);
+  float p = fmaf(f, 0.05517164f, 0.24261113f);
+  p = fmaf(p, f, 0.69326097f);
+  p = fmaf(p, f, 0.99992806f);
+  int r;
+  asm("mad.lo.s32 %0, %1, 8388608, %2;" : "=r"(r) : "r"(__float_as_int(xr)), "r"(__float_as_int(p)));
+  return __int_as_float(r);
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+// Packed fp32 pairs (one instruction per two lanes of work): {d0, d1} = {a0, a1} * b + c and
+// {acc0, acc1} += {x0, x1}.
+__device__ __forceinline__ void ffma2(float& d0, float& d1, float a0, float a1, float b, float c) {
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmov.b64 rc, {%5, %5};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+__device__ __forceinline__ void fadd2(float& acc0, float& acc1, float x0, float x1) {
+  asm("{\n\t.reg .b64 ra, rx;\n\t"
+      "mov.b64 ra, {%0, %1};\n\tmov.b64 rx, {%2, %3};\n\t"
+      "add.rn.f32x2 ra, ra, rx;\n\tmov.b64 {%0, %1}, ra;\n\t}"
+      : "+f"(acc0), "+f"(acc1)
+      : "f"(x0), "f"(x1));
+}
+
 // ---- proxies and ordering ----------------------------------------------------------------
 
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
