@@ -427,13 +427,16 @@ def main():
     # ---- roofline of the dominant kernel (fused attention: tensor-core bound) ---------------
     peaks = measured_peaks()
     attn_ms = ms_sum[3] / max(launches[3], 1)
-    flops = 6.0 * D * causal_pairs(batch, seq)  # 2d (q.K_hat) + 2d (q_s.sign) + 2d (P.V_hat) per causal pair
+    # 2d (q.K_hat) + 2d (q_s.sign) + 2d (P.V_hat) per causal pair; the query preparation and output
+    # back-rotation the kernel also performs (6 d^2 per query row, 3 % more) are not counted
+    flops = 6.0 * D * causal_pairs(batch, seq)
     achieved = flops / (attn_ms * 1e-3) / 1e12 if attn_ms > 0 else None
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
                 "frac": (achieved / peaks["tflops"]) if achieved else None,
-                # DRAM bytes per launch: ncu capture at batch 1 (141.0 MB read + 37.5 MB written), which scales with batch
-                "traffic": 178.5e6 * batch if (seq == S and D == 128) else None,
-                "kernel": "attention_ws_kernel", "ms_per_launch": attn_ms, "peak_source": peaks["source"],
+                # DRAM bytes per launch: ncu capture at batch 1 (74.0 MB read + 29.3 MB written; queries in,
+                # outputs out, packed keys and values), which scales with batch
+                "traffic": 103.3e6 * batch if (seq == S and D == 128) else None,
+                "kernel": "attention_c2_kernel", "ms_per_launch": attn_ms, "peak_source": peaks["source"],
                 "kernel_ms": {"compress_keys": ms_sum[0] / max(launches[0], 1),
                               "compress_values": ms_sum[1] / max(launches[1], 1),
                               "prepare_queries": ms_sum[2] / max(launches[2], 1),

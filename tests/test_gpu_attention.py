@@ -77,6 +77,28 @@ def test_fused_attention_shapes(mode, Sq, Sk):
     assert rel_err(out, want) < TOL[mode], rel_err(out, want)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("Hq,Hkv", [(4, 2), (3, 3)])
+def test_tensor_core_mode_converts_other_dtypes_and_follows_strides(dtype, Hq, Hkv):
+    """bf16 (tensor-core) mode fed fp16 / fp32 queries laid out [B, S, H, D] (the layout the family
+    adapters see before their transpose): the kernel converts the rows itself, follows the strides and
+    writes the output in the query dtype.  An odd GQA group pairs position blocks instead of heads."""
+    d, bits, B, S = 128, 3, 2, 300
+    q, k, v = _case(B, Hq, Hkv, S, S, d, seed=11, dtype=torch.float32)
+    kp, vp = oracle_params(d, bits)
+    ok, ov = orc.key_compress(k, kp), orc.value_compress(v, vp)
+    q = q.to(dtype)
+    want = oracle_attention_from_packed(q, ok, ov, kp, vp, causal=True)
+    from turboquant_b200 import fused_attention
+    kc, vc = device_compressors(d, bits, mode="bf16")
+    q_dev = q.permute(0, 2, 1, 3).contiguous().cuda().permute(0, 2, 1, 3)   # [B, H, S, D] view of [B, S, H, D]
+    assert not q_dev.is_contiguous()
+    out = fused_attention(q_dev, oracle_key_dict_to_device(ok), oracle_value_dict_to_device(ov), kc, vc,
+                          causal=True, mode="bf16")
+    assert out.dtype == dtype and out.shape == q.shape
+    assert rel_err(out, want) < TOL["bf16"], rel_err(out, want)
+
+
 @pytest.mark.parametrize("mode", ["fp32", "bf16"])
 def test_fused_attention_additive_mask_and_noncausal(mode):
     """Padding-style additive mask (finite large negative, as HF builds it) and the
