@@ -178,10 +178,8 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const uint32_t rank = tc::cluster_ctarank();
-  if (tid == 0) s_abort = (*reinterpret_cast<volatile unsigned long long*>(&g_c2_faults) != 0ull) ? 1 : 0;
-  __syncthreads();
-  const bool dead = s_abort != 0;  // an earlier bounded wait expired: do nothing but keep the cluster barriers paired
-
+  // Whether an earlier launch ran into an expired wait is read by one thread of the (otherwise idle)
+  // P V_hat issuer warp and published with the set-up barrier below; nothing before that depends on it.
   // ---- which query tile ------------------------------------------------------------------
   const int64_t b = blockIdx.z;
   const int xpair = (int)((gridDim.x >> 1) - 1 - (blockIdx.x >> 1));  // heaviest (latest) position blocks first
@@ -199,7 +197,7 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
   const int shift = (int)(a.Sk - a.Sq);
   int k_end = (int)a.Sk;
   if (a.causal) k_end = min(k_end, min(q0_last + kBM - 1, (int)a.Sq - 1) + shift + 1);
-  const int n_tiles = dead ? 0 : (k_end + kBN - 1) / kBN;  // identical in both CTAs of the pair
+  const int n_tiles_live = (k_end + kBN - 1) / kBN;  // identical in both CTAs of the pair
 
   const uint32_t bar0 = tc::smem_u32(&bars[0]);
   auto k_full = [&](int i) { return bar0 + 8u * i; };                       // leader
@@ -224,43 +222,64 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
     else tc::mbar_arrive_cluster(tc::map_to_cta(bar, 0));
   };
 
-  if (tid == 0) {
-    for (int i = 0; i < kStages; ++i) {
-      tc::mbar_init(k_full(i), kProducerArrivals);
-      tc::mbar_init(v_full(i), kProducerArrivals);
-      tc::mbar_init(k_empty(i), 1);
-      tc::mbar_init(v_empty(i), 1);
+  // The softmax warps fetch the raw query tile first of all (8 threads per 128-byte core matrix of the A
+  // operand), so that the DRAM latency overlaps the barrier / tensor-memory set-up below.
+  const long long t_entry = clock64();
+  constexpr int NA = kBM * (D / 8) / kSoftmax;
+  uint4 qv[NA];
+  if (tid < kSoftmax) {
+    const int64_t qbase = b * x.q_stride_b + head * x.q_stride_h;
+#pragma unroll
+    for (int i = 0; i < NA; ++i) {
+      const int e = i * kSoftmax + tid, r = e % 8 + 8 * (e / (8 * (D / 8))), c = (e / 8) % (D / 8);
+      const int64_t off = qbase + (int64_t)(q0 + r) * x.q_stride_s + c * 8;
+      qv[i] = make_uint4(0, 0, 0, 0);
+      if (q0 + r < a.Sq) {
+        if (x.q_dtype == TQ_BF16) qv[i] = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(x.q) + off);
+        else qv[i] = load_row_chunk_bf16(x.q, x.q_dtype, off);
+      }
     }
-    for (int i = 0; i < 2; ++i) {
-      tc::mbar_init(s_full(i), 1);
-      tc::mbar_init(pv_done(i), 1);
-      tc::mbar_init(p_full(i), kSoftmaxArrivals);
-      tc::mbar_init(pk_full(i), kProducers);
+  }
+  const long long t_q = clock64();
+  if (warp == kPvWarp) {
+    // barrier initialisation, one barrier per lane and round; then lane 0 starts the bulk copies of the
+    // constant operands of the prologue and epilogue MMAs (no register staging)
+    constexpr int kBars = 4 * kStages + 21;
+    for (int i = lane; i < kBars; i += 32) {
+      const int r = i - 4 * kStages;
+      uint32_t count = 1;                                     // commit / bulk-copy / single-thread barriers
+      if (i < 2 * kStages) count = kProducerArrivals;         // k_full, v_full
+      else if (r == 6 || r == 7 || r == 14) count = kSoftmaxArrivals;  // p_full, q_full
+      else if (r == 8 || r == 9) count = kProducers;          // pk_full
+      else if (r >= 10 && r <= 13) count = 32 * (kSoftmax / kBM);      // xch
+      else if (r == 15) count = kSoftmaxArrivals + 1;         // qp_full: + the peer's constant operand
+      tc::mbar_init(bar0 + 8u * i, count);
     }
-    for (int i = 0; i < 4; ++i) tc::mbar_init(xch(i), 32 * (kSoftmax / kBM));
-    tc::mbar_init(q_full, kSoftmaxArrivals);
-    tc::mbar_init(qp_full, kSoftmaxArrivals + 1);  // + the peer's constant operand
-    tc::mbar_init(w_full, 1);
-    tc::mbar_init(u_full, 1);
-    tc::mbar_init(u_peer, 1);
-    tc::mbar_init(qp_done, 1);
-    tc::mbar_init(e_done, 1);
     tc::fence_mbar_init();
-    if (!dead) {
-      // constant operands of the prologue and epilogue MMAs: one bulk copy each, no register staging
-      tc::mbar_arrive_expect_tx(w_full, L::kWBytes);
-      tc::bulk_load(tc::smem_u32(smem_raw + L::kWOff), x.w_cat + (int64_t)rank * D * D, L::kWBytes, w_full);
-      tc::mbar_arrive_expect_tx(u_full, L::kUBytes);
-      tc::bulk_load(tc::smem_u32(smem_raw + L::kUOff), x.w_unrot + (int64_t)rank * (D / 2) * D, L::kUBytes, u_full);
+    tc::fence_async_smem();  // the copy engine completes on barriers initialised just above
+    __syncwarp();
+    if (lane == 0) {
+      const bool poisoned = *reinterpret_cast<volatile unsigned long long*>(&g_c2_faults) != 0ull;
+      s_abort = poisoned ? 1 : 0;
+      if (!poisoned) {
+        tc::mbar_arrive_expect_tx(w_full, L::kWBytes);
+        tc::bulk_load(tc::smem_u32(smem_raw + L::kWOff), x.w_cat + (int64_t)rank * D * D, L::kWBytes, w_full);
+        tc::mbar_arrive_expect_tx(u_full, L::kUBytes);
+        tc::bulk_load(tc::smem_u32(smem_raw + L::kUOff), x.w_unrot + (int64_t)rank * (D / 2) * D, L::kUBytes, u_full);
+      }
     }
   }
   if (warp == kCtlWarp) tc::tmem_alloc2(tc::smem_u32(&tmem_slot), L::kCols);
   fill_pair_lut<KB>(lutK, a.cen_k, tid, kThreads);
   fill_pair_lut<VB>(lutV, a.cen_v, tid, kThreads);
+  const long long t_i = clock64();
   tc::fence_before_sync();
   __syncthreads();
+  const long long t_s = clock64();
   tc::cluster_sync();  // the peer's barriers and tensor memory exist before anyone signals or issues
   tc::fence_after_sync();
+  const bool dead = s_abort != 0;  // an earlier bounded wait expired: do nothing but keep the cluster barriers paired
+  const int n_tiles = dead ? 0 : n_tiles_live;
   const uint32_t tmem_base = tmem_slot;
   const uint32_t tmem_o = tmem_base + L::kColO;
   bool ok = true;
@@ -276,25 +295,26 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
     const int qi = q0 + row;
     const int64_t qrow = (b * a.Hq + head) * a.Sq + qi;
     const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+    if (tr.on) {  // kernel entry, measured before the set-up
+      const int i = tr.role * (kTraceCap2 / 4) + tr.n++;
+      g_trace2[2 * i] = ((long long)tr.role << 32) | (25ll << 16) | 999ll;
+      g_trace2[2 * i + 1] = t_entry;
+      const long long ts[3] = {t_q, t_i, t_s};
+      for (int e = 0; e < 3; ++e) {
+        const int i2 = tr.role * (kTraceCap2 / 4) + tr.n++;
+        g_trace2[2 * i2] = ((long long)tr.role << 32) | ((long long)(26 + e) << 16) | 999ll;
+        g_trace2[2 * i2 + 1] = ts[e];
+      }
+    }
     tr.mark(10, 999);
     tr.mark_ns(18, 999);
     if (n_tiles > 0) {
-      // raw query tile [128, D] -> A operand of the prologue MMA (8 threads fill one 128-byte core matrix)
-      constexpr int NA = kBM * G / kSoftmax;
+      // raw query tile [128, D] -> A operand of the prologue MMA
       uint8_t* Aq = smem_raw + L::kQOff;
-      const int64_t qbase = b * x.q_stride_b + head * x.q_stride_h;
-      uint4 v[NA];
 #pragma unroll
       for (int i = 0; i < NA; ++i) {
         const int e = i * kSoftmax + tid, r = e % 8 + 8 * (e / (8 * G)), c = (e / 8) % G;
-        v[i] = make_uint4(0, 0, 0, 0);
-        if (q0 + r < a.Sq) v[i] = load_row_chunk_bf16(x.q, x.q_dtype, qbase + (int64_t)(q0 + r) * x.q_stride_s + c * 8);
-      }
-      tr.mark(20, 999);
-#pragma unroll
-      for (int i = 0; i < NA; ++i) {
-        const int e = i * kSoftmax + tid, r = e % 8 + 8 * (e / (8 * G)), c = (e / 8) % G;
-        *reinterpret_cast<uint4*>(Aq + (r / 8) * L::kSboW + c * 128 + (r % 8) * 16) = v[i];
+        *reinterpret_cast<uint4*>(Aq + (r / 8) * L::kSboW + c * 128 + (r % 8) * 16) = qv[i];
       }
       tr.mark(21, 999);
       tc::fence_async_smem();
@@ -475,17 +495,22 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
         tc::wait_ld();
         store_row_chunk(Ot + row * pitch, a.out_dtype, chalf * (D / NQ) + c0, acc);
       }
+      tr.mark(23, 999);
       tc::mbar_arrive(xch(quad));
       ok = tc::mbar_wait_or_abort(xch(quad), (n_tiles + 1) & 1, abort_flag);
+      tr.mark(24, 999);
     }
     if (ok && n_tiles > 0) {
       // the two warps of the quadrant store 16 of its 32 rows each
       const int esz = a.out_dtype == TQ_F32 ? 4 : 2;
-      const int pitch = D * esz + 16, cpr = D * esz / 16;  // 16-byte chunks per row
+      const int lcpr = a.out_dtype == TQ_F32 ? 5 : 4;  // log2 of the 16-byte chunks per row (D = 128)
+      static_assert(D == 128, "chunks per row are derived for head_dim 128");
+      const int pitch = D * esz + 16, cpr = 1 << lcpr;
       const uint8_t* Ot = smem_raw + L::kOutOff;
       uint8_t* obase = static_cast<uint8_t*>(a.out) + (b * a.o_stride_b + head * a.o_stride_h) * esz;
+#pragma unroll 4
       for (int idx = lane; idx < 16 * cpr; idx += 32) {
-        const int r = quad * 32 + chalf * 16 + idx / cpr, c = idx % cpr;
+        const int r = quad * 32 + chalf * 16 + (idx >> lcpr), c = idx & (cpr - 1);
         if (q0 + r < a.Sq)
           *reinterpret_cast<uint4*>(obase + (int64_t)(q0 + r) * a.o_stride_s * esz + c * 16) =
               *reinterpret_cast<const uint4*>(Ot + r * pitch + c * 16);
