@@ -34,12 +34,6 @@ __host__ __device__ constexpr uint32_t idesc_bf16(int M, int N, bool a_mn_major,
          (static_cast<uint32_t>(M >> 4) << 24);
 }
 
-// Same with explicit operand formats: 0 = f16, 1 = bf16 (kind::f16 accepts them independently).
-__host__ __device__ constexpr uint32_t idesc_f16(int M, int N, int a_fmt, int b_fmt, bool a_mn_major, bool b_mn_major) {
-  return (1u << 4) | (static_cast<uint32_t>(a_fmt) << 7) | (static_cast<uint32_t>(b_fmt) << 10) |
-         ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) | (static_cast<uint32_t>(N >> 3) << 17) |
-         (static_cast<uint32_t>(M >> 4) << 24);
-}
 
 // ---- mbarrier ------------------------------------------------------------------------
 
@@ -115,21 +109,6 @@ __device__ __forceinline__ bool mbar_wait_or_abort(uint32_t bar, uint32_t parity
   }
   return true;
 }
-// Named barrier among `nthreads` threads (ids 1..15; 0 is __syncthreads).
-__device__ __forceinline__ void named_barrier(int id, int nthreads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
-}
-// Two exp2 per instruction in half precision: {2^lo, 2^hi} of the packed f16x2 argument.
-__device__ __forceinline__ uint32_t exp2_f16x2(uint32_t x) {
-  uint32_t y;
-  asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
-  return y;
-}
-__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
-  uint32_t r;
-  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-  return r;
-}
 __device__ __forceinline__ uint32_t add_f16x2(uint32_t a, uint32_t b) {
   uint32_t r;
   asm("add.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
@@ -141,22 +120,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-// 2^x on the FMA pipe instead of the special-function unit: round-to-nearest split x = n + f by the
-// magic-number add, degree-3 minimax polynomial of 2^f on [-0.5, 0.5] (relative error 7.5e-5, far below
-// bf16 rounding), n added into the exponent field by one integer multiply-add.  x is clamped at -126, so
-// the result is never below the smallest normal number (and never exactly 0): callers that need exact
-// zeros for masked scores use fast_exp2.
-__device__ __forceinline__ float exp2_poly(float x) {
-  x = fmaxf(x, -126.f);
-  const float xr = x + 12582912.f;  // 1.5 * 2^23: the integer part lands in the low mantissa bits
-  const float f = x - (xr - 12582912.f);
-  float p = fmaf(f, 0.05517164f, 0.24261113f);
-  p = fmaf(p, f, 0.69326097f);
-  p = fmaf(p, f, 0.99992806f);
-  int r;
-  asm("mad.lo.s32 %0, %1, 8388608, %2;" : "=r"(r) : "r"(__float_as_int(xr)), "r"(__float_as_int(p)));
-  return __int_as_float(r);
-}
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float r;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
