@@ -1,11 +1,12 @@
 // Key / value compression with the rotation and the QJL projection on the tensor cores
 // (TQ_MODE_BF16, bf16 inputs).
 //
-// A persistent CTA (128 threads, thread t = row t = tensor-memory lane t) walks tiles of 128
-// vectors.  Per tile:
-//   1. each thread loads its row (the next tile's row is prefetched into registers while the
-//      current one is processed), accumulates the squared norm in fp32 and writes the raw bf16 row
-//      into the A operand tile.  bf16 inputs are EXACT operands; the fp32 rotation matrix is split
+// A persistent CTA walks tiles of 128 vectors with D/32 threads per vector (row r = tensor-memory lane
+// r; a thread owns 32 consecutive coordinates of its row, so the per-coordinate work of the epilogues
+// runs on 16 warps at head_dim 128).  Per tile:
+//   1. each thread loads its 64 bytes of the row (the next tile's are prefetched into registers while the
+//      current one is processed), accumulates its part of the squared norm in fp32 (parts are summed
+//      through shared memory in a fixed order) and writes the raw bf16 values into the A operand tile.  bf16 inputs are EXACT operands; the fp32 rotation matrix is split
 //      into bf16 hi + lo parts, so y_raw = x (Pi_hi + Pi_lo)^T carries ~16 mantissa bits;
 //   2. tcgen05.mma: Y_raw = X Pi_hi^T + X Pi_lo^T (fp32 accumulation in tensor memory);
 //   3. epilogue: y = y_raw / (n + 1e-8), Lloyd-Max index by boundary counting, the row's packed
@@ -59,13 +60,15 @@ __device__ void load_split_matrix(const float* __restrict__ M, uint8_t* hi, uint
 }
 
 template <int D, int IB, bool IS_KEY>
-__global__ void __launch_bounds__(128, 1) compress_tc_kernel(const CompressArgs a) {
+__global__ void __launch_bounds__(4 * D, 1) compress_tc_kernel(const CompressArgs a) {
   constexpr int G = D / 8;
+  constexpr int NP = D / 32;               // threads per row: each owns 32 consecutive coordinates
+  constexpr int kThreads = 128 * NP;
   constexpr uint32_t SBO = G * 128;
   constexpr uint32_t MAT = D * D * 2;      // one bf16 matrix
   constexpr uint32_t TILE = 128 * D * 2;   // one bf16 A tile
   constexpr int NB = (1 << IB) - 1;
-  constexpr int ROWB = D * IB / 8;         // packed index bytes per row
+  constexpr int ROWB = D * IB / 8;         // packed index bytes per row (4 * IB of them per thread)
   constexpr int kCols = IS_KEY ? 2 * D : D;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* PiH = smem;
@@ -78,7 +81,11 @@ __global__ void __launch_bounds__(128, 1) compress_tc_kernel(const CompressArgs 
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
   __shared__ float cen_s[IS_KEY ? (1 << IB) : 1];
-  const int tid = threadIdx.x, warp = tid / 32;
+  __shared__ float ss_part[NP][128];        // partial squared norms of the row's parts
+  __shared__ float rr_part[IS_KEY ? NP : 1][128];
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  const int row = (warp % 4) * 32 + lane;   // = tensor-memory lane
+  const int part = warp / 4;                // coordinates [32 part, 32 part + 32)
 
   if (tid == 0) {
     s_abort = 0;
@@ -86,9 +93,9 @@ __global__ void __launch_bounds__(128, 1) compress_tc_kernel(const CompressArgs 
     tc::fence_mbar_init();
   }
   if (warp == 0) tc::tmem_alloc(tc::smem_u32(&tmem_slot), kCols < 32 ? 32 : kCols);
-  load_split_matrix<D>(a.Pi, PiH, PiL, tid, 128);
+  load_split_matrix<D>(a.Pi, PiH, PiL, tid, kThreads);
   if (IS_KEY) {
-    load_split_matrix<D>(a.S_eff, SeH, SeL, tid, 128);
+    load_split_matrix<D>(a.S_eff, SeH, SeL, tid, kThreads);
     if (tid < (1 << IB)) cen_s[tid] = a.centroids[tid];
   }
   float bnd[NB];
@@ -99,7 +106,7 @@ __global__ void __launch_bounds__(128, 1) compress_tc_kernel(const CompressArgs 
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t tmem = tmem_slot;
-  const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+  const uint32_t lane_base = (uint32_t)((warp % 4) * 32) << 16;
   const uint32_t bar_addr = tc::smem_u32(&bar);
   constexpr uint32_t idesc = tc::idesc_bf16(128, D, false, false);
   const uint64_t a0d = tc::smem_desc(tc::smem_u32(A0), 128, SBO), a1d = tc::smem_desc(tc::smem_u32(A1), 128, SBO);
@@ -110,31 +117,31 @@ __global__ void __launch_bounds__(128, 1) compress_tc_kernel(const CompressArgs 
   uint32_t phase = 0;
   volatile int* abort_flag = &s_abort;
 
-  uint4 rowbuf[G];  // this thread's row of the tile about to be processed
+  uint4 rowbuf[4];  // this thread's 32 coordinates of its row of the tile about to be processed
   auto fetch = [&](int tile) {
-    const int64_t n = static_cast<int64_t>(tile) * 128 + tid;
+    const int64_t n = static_cast<int64_t>(tile) * 128 + row;
     if (tile < a.num_tiles && n < a.n_vec) {
       const int64_t b = n / HS, rem = n % HS;
       const uint4* p = reinterpret_cast<const uint4*>(src + b * a.stride_b + (rem / a.S) * a.stride_h +
-                                                      (rem % a.S) * a.stride_s);
+                                                      (rem % a.S) * a.stride_s) + 4 * part;
 #pragma unroll
-      for (int c = 0; c < G; ++c) rowbuf[c] = p[c];
+      for (int c = 0; c < 4; ++c) rowbuf[c] = p[c];
     } else {
 #pragma unroll
-      for (int c = 0; c < G; ++c) rowbuf[c] = make_uint4(0, 0, 0, 0);
+      for (int c = 0; c < 4; ++c) rowbuf[c] = make_uint4(0, 0, 0, 0);
     }
   };
   fetch(blockIdx.x);
 
   for (int tile = blockIdx.x; tile < a.num_tiles; tile += gridDim.x) {
-    const int64_t n = static_cast<int64_t>(tile) * 128 + tid;
+    const int64_t n = static_cast<int64_t>(tile) * 128 + row;
     const bool live = n < a.n_vec;
     // ---- 1. norm + A tile ------------------------------------------------------------------
-    float ss = 0.f;
     {
-      uint8_t* dst = A0 + (tid / 8) * SBO + (tid % 8) * 16;
+      float ss = 0.f;
+      uint8_t* dst = A0 + (row / 8) * SBO + (row % 8) * 16 + 4 * part * 128;
 #pragma unroll
-      for (int c = 0; c < G; ++c) {
+      for (int c = 0; c < 4; ++c) {
         const uint32_t w[4] = {rowbuf[c].x, rowbuf[c].y, rowbuf[c].z, rowbuf[c].w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -144,13 +151,8 @@ __global__ void __launch_bounds__(128, 1) compress_tc_kernel(const CompressArgs 
         }
         *reinterpret_cast<uint4*>(dst + c * 128) = rowbuf[c];
       }
+      ss_part[part][row] = ss;
     }
-    const float nv = sqrtf(ss), den = nv + 1e-8f;
-    // y = y_raw / den is compared with the boundaries as y_raw > b * den (den > 0): one multiply per
-    // boundary and row instead of one division per coordinate
-    float bden[NB];
-#pragma unroll
-    for (int j = 0; j < NB; ++j) bden[j] = bnd[j] * den;
     tc::fence_async_smem();
     tc::fence_before_sync();
     __syncthreads();
@@ -166,18 +168,26 @@ __global__ void __launch_bounds__(128, 1) compress_tc_kernel(const CompressArgs 
       tc::mma_commit(bar_addr);
     }
     fetch(tile + gridDim.x);  // next tile's rows travel while this one is processed
+    float ss = 0.f;  // summed in a fixed order, so that every part of the row sees the same norm
+#pragma unroll
+    for (int q = 0; q < NP; ++q) ss += ss_part[q][row];
+    const float nv = sqrtf(ss), den = nv + 1e-8f;
+    // y = y_raw / den is compared with the boundaries as y_raw > b * den (den > 0): one multiply per
+    // boundary and row instead of one division per coordinate
+    float bden[NB];
+#pragma unroll
+    for (int j = 0; j < NB; ++j) bden[j] = bnd[j] * den;
     if (!tc::mbar_wait_or_abort(bar_addr, phase, abort_flag)) break;
     phase ^= 1;
     tc::fence_after_sync();
     // ---- 3. index + pack (4. residual) ----------------------------------------------------------
     float rr = 0.f;
-    uint32_t packed[ROWB / 4];
+    uint32_t packed[IB];
 #pragma unroll
-    for (int i = 0; i < ROWB / 4; ++i) packed[i] = 0;
-#pragma unroll
-    for (int c0 = 0; c0 < D; c0 += 32) {
+    for (int i = 0; i < IB; ++i) packed[i] = 0;
+    {
       uint32_t raw[32];
-      tc::tmem_ld32(tmem + lane_base + c0, raw);
+      tc::tmem_ld32(tmem + lane_base + 32 * part, raw);
       tc::wait_ld();
 #pragma unroll
       for (int g8 = 0; g8 < 4; ++g8) {
@@ -196,36 +206,32 @@ __global__ void __launch_bounds__(128, 1) compress_tc_kernel(const CompressArgs 
             else { rh[e / 2] = hb; rl[e / 2] = lb; }
           }
         }
-        // the 8 fields of this group are IB whole bytes at byte offset gidx*IB of the row's bit stream
-        const int gidx = c0 / 8 + g8;
+        // the 8 fields of this group are IB whole bytes at byte offset g8*IB of the thread's 4*IB bytes
 #pragma unroll
         for (int bt = 0; bt < IB; ++bt) {
-          const int byte = gidx * IB + bt;
+          const int byte = g8 * IB + bt;
           packed[byte / 4] |= static_cast<uint32_t>((word >> (8 * bt)) & 0xffu) << (8 * (byte % 4));
         }
         if (IS_KEY) {
-          const uint32_t off = (tid / 8) * SBO + gidx * 128 + (tid % 8) * 16;
+          const uint32_t off = (row / 8) * SBO + (4 * part + g8) * 128 + (row % 8) * 16;
           *reinterpret_cast<uint4*>(A0 + off) = make_uint4(rh[0], rh[1], rh[2], rh[3]);
           *reinterpret_cast<uint4*>(A1 + off) = make_uint4(rl[0], rl[1], rl[2], rl[3]);
         }
       }
     }
     if (live) {
-      if constexpr (ROWB % 16 == 0) {
-        uint4* dst = reinterpret_cast<uint4*>(a.packed_idx + n * ROWB);
+      uint32_t* dst = reinterpret_cast<uint32_t*>(a.packed_idx + n * ROWB + 4 * IB * part);
+      if constexpr (IB == 4) *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      else if constexpr (IB == 2) *reinterpret_cast<uint2*>(dst) = make_uint2(packed[0], packed[1]);
+      else {
 #pragma unroll
-        for (int i = 0; i < ROWB / 16; ++i)
-          dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
-      } else {
-        uint2* dst = reinterpret_cast<uint2*>(a.packed_idx + n * ROWB);
-#pragma unroll
-        for (int i = 0; i < ROWB / 8; ++i) dst[i] = make_uint2(packed[2 * i], packed[2 * i + 1]);
+        for (int i = 0; i < IB; ++i) dst[i] = packed[i];
       }
-      a.vec_norms[n] = fp16_bits(nv);
-      if (IS_KEY) a.residual_norms[n] = fp16_bits(sqrtf(rr));
+      if (part == 0) a.vec_norms[n] = fp16_bits(nv);
     }
     if (IS_KEY) {
       // ---- QJL sketch of the residual --------------------------------------------------------
+      rr_part[part][row] = rr;
       tc::fence_async_smem();
       tc::fence_before_sync();
       __syncthreads();
@@ -242,27 +248,25 @@ __global__ void __launch_bounds__(128, 1) compress_tc_kernel(const CompressArgs 
           tc::mma_bf16(tmem + D, a1d + (uint64_t)(ks * 256 >> 4), sehd + (uint64_t)(ks * 256 >> 4), idesc, 1u);
         tc::mma_commit(bar_addr);
       }
+      if (live && part == 0) {
+        float rs = 0.f;
+#pragma unroll
+        for (int q = 0; q < NP; ++q) rs += rr_part[q][row];
+        a.residual_norms[n] = fp16_bits(sqrtf(rs));
+      }
       if (!tc::mbar_wait_or_abort(bar_addr, phase, abort_flag)) break;
       phase ^= 1;
       tc::fence_after_sync();
-      uint32_t sg[D / 32];
+      uint32_t raw[32];
+      tc::tmem_ld32(tmem + D + lane_base + 32 * part, raw);
+      tc::wait_ld();
+      uint32_t bits = 0;
 #pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        uint32_t raw[32];
-        tc::tmem_ld32(tmem + D + lane_base + c0, raw);
-        tc::wait_ld();
-        uint32_t bits = 0;
-#pragma unroll
-        for (int e = 0; e < 32; ++e) bits |= (__uint_as_float(raw[e]) >= 0.f ? 1u : 0u) << e;
-        sg[c0 / 32] = bits;
-      }
-      if (live) {
-        if (D == 128) *reinterpret_cast<uint4*>(a.packed_signs + n * (D / 8)) = make_uint4(sg[0], sg[1], sg[2], sg[D / 32 - 1]);
-        else *reinterpret_cast<uint2*>(a.packed_signs + n * (D / 8)) = make_uint2(sg[0], sg[D / 32 - 1]);
-      }
+      for (int e = 0; e < 32; ++e) bits |= (__uint_as_float(raw[e]) >= 0.f ? 1u : 0u) << e;
+      if (live) *reinterpret_cast<uint32_t*>(a.packed_signs + n * (D / 8) + 4 * part) = bits;
     }
     tc::fence_before_sync();
-    __syncthreads();  // the next tile overwrites the A tiles and the accumulators
+    __syncthreads();  // the next tile overwrites the A tiles, the partial sums and the accumulators
   }
   if (s_abort) {
     if (tid == 0) atomicAdd(&g_compress_faults, 1ull);
@@ -275,9 +279,8 @@ __global__ void __launch_bounds__(128, 1) compress_tc_kernel(const CompressArgs 
 template <int D, int IB, bool IS_KEY>
 int launch(const CompressArgs& a, cudaStream_t stream) {
   constexpr size_t smem_req = (size_t)(IS_KEY ? 4 : 2) * D * D * 2 + (size_t)(IS_KEY ? 2 : 1) * 128 * D * 2;
-  // co-resident CTAs overlap each other's load / MMA / epilogue phases; each takes at most 256 of the
-  // 512 tensor-memory columns, so two per SM always fit
-  constexpr int per_sm = smem_req * 2 + 8192 <= 227 * 1024 ? 2 : 1;
+  // one CTA of 4 D threads per SM (16 warps at head_dim 128): the register file does not hold two
+  constexpr int per_sm = 1;
   auto kern = compress_tc_kernel<D, IB, IS_KEY>;
   TQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_req));
   const int tiles = (int)((a.n_vec + 127) / 128);
@@ -287,7 +290,7 @@ int launch(const CompressArgs& a, cudaStream_t stream) {
   if (grid > tiles) grid = tiles;
   {
     ProfScope prof(IS_KEY ? kProfCompressKeys : kProfCompressValues, stream);
-    kern<<<grid, 128, smem_req, stream>>>(b);
+    kern<<<grid, 4 * D, smem_req, stream>>>(b);
   }
   TQ_CUDA_OK(cudaGetLastError());
   return TQ_OK;
