@@ -427,9 +427,9 @@ def main():
     # ---- roofline of the dominant kernel (fused attention: tensor-core bound) ---------------
     peaks = measured_peaks()
     attn_ms = ms_sum[3] / max(launches[3], 1)
-    # 2d (q.K_hat) + 2d (q_s.sign) + 2d (P.V_hat) per causal pair; the query preparation and output
-    # back-rotation the kernel also performs (6 d^2 per query row, 3 % more) are not counted
-    flops = 6.0 * D * causal_pairs(batch, seq)
+    # algorithmic flops of the fused kernel: 2d (q.K_hat) + 2d (q_s.sign) + 2d (P.V_hat) per causal pair, plus
+    # per query row the preparation q [Pi ; coeff S]^T (2 * 2d * d) and the output back-rotation (2 d^2)
+    flops = 6.0 * D * causal_pairs(batch, seq) + 6.0 * D * D * batch * HQ * seq
     achieved = flops / (attn_ms * 1e-3) / 1e12 if attn_ms > 0 else None
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
                 "frac": (achieved / peaks["tflops"]) if achieved else None,

@@ -150,6 +150,38 @@ def main(ref_root: str) -> None:
             out = mod(hidden, attention_mask=mask)[0]
         fam[f"out_bits{bits}"] = npy(out)
     np.savez_compressed(os.path.join(HERE, "family_gpt2.npz"), **fam)
+
+    # ---- 5. standalone quantisers (turboquant.py, lloyd_max.py) on CPU ----------------
+    from turboquant_pytorch.lloyd_max import LloydMaxCodebook
+    from turboquant_pytorch.turboquant import TurboQuantKVCache, TurboQuantMSE, TurboQuantProd
+    sa = {}
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(96, 128, generator=g)
+    x = x / x.norm(dim=-1, keepdim=True)
+    y = torch.randn(96, 128, generator=g)
+    sa["x"], sa["y"] = npy(x), npy(y)
+    for bits in (2, 3, 4):
+        mse = TurboQuantMSE(128, bits, seed=42, device="cpu")
+        x_hat, idx = mse(x)
+        sa[f"mse_idx_b{bits}"], sa[f"mse_xhat_b{bits}"] = npy(idx).astype(np.int32), npy(x_hat)
+        prod = TurboQuantProd(128, bits, seed=42, device="cpu")
+        c = prod.quantize(x)
+        sa[f"prod_idx_b{bits}"] = npy(c["mse_indices"]).astype(np.int32)
+        sa[f"prod_signs_b{bits}"] = npy(c["qjl_signs"]).astype(np.int8)
+        sa[f"prod_rnorm_b{bits}"] = npy(c["residual_norm"])
+        sa[f"prod_ip_b{bits}"] = npy(prod.inner_product(y, c))
+        sa[f"prod_proj_b{bits}"] = npy((x - prod.dequantize(c)) @ prod.S.T)   # to discount sign flips near zero
+    cb = LloydMaxCodebook(128, 3, use_triton=False)
+    sa["codebook_distortion_d128_b3"] = np.float64(cb.distortion)
+    sa["codebook_idx"] = npy(cb.quantize(x * 1.0)).astype(np.int32)
+    cache = TurboQuantKVCache(128, 128, bits=3, seed=42, device="cpu")
+    cache.append(x[:40], y[:40])
+    cache.append(x[40:], y[40:])
+    sa["cache_scores"] = npy(cache.attention_scores(y[:1]))
+    sa["cache_values"] = npy(cache.get_values())
+    mem = cache.memory_usage_bits()
+    sa["cache_mem"] = np.array([mem["key_bits"], mem["value_bits"], mem["total_bits"], mem["fp16_bits"]], dtype=np.int64)
+    np.savez_compressed(os.path.join(HERE, "standalone.npz"), **sa)
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))

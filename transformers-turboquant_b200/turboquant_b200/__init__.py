@@ -9,8 +9,14 @@ from .compressors import (TurboQuantCompressorMSE, TurboQuantCompressorV2, devic
 from .plugin import (TurboQuantAttentionBase, UnsupportedModelError, apply_turboquant,
                      get_attention_class, register_family)
 from . import families  # noqa: F401,E402  (registers the adapters)
+from .kernels import (asymmetric_attention_scores, lloyd_max_dequantize, lloyd_max_quantize,  # noqa: E402
+                      pack_bits, unpack_bits)
+from .lloyd_max import LloydMaxCodebook, solve_lloyd_max  # noqa: E402
+from .turboquant import TurboQuantKVCache, TurboQuantMSE, TurboQuantProd  # noqa: E402
 
 __version__ = "0.1.0"
 __all__ = ["apply_turboquant", "register_family", "get_attention_class", "UnsupportedModelError",
            "TurboQuantAttentionBase", "TurboQuantCompressorV2", "TurboQuantCompressorMSE",
-           "fused_attention", "device_fault_count"]
+           "fused_attention", "device_fault_count", "pack_bits", "unpack_bits", "lloyd_max_quantize",
+           "lloyd_max_dequantize", "asymmetric_attention_scores", "LloydMaxCodebook", "solve_lloyd_max",
+           "TurboQuantMSE", "TurboQuantProd", "TurboQuantKVCache"]
