@@ -22,6 +22,11 @@ import ctypes
 import json
 import math
 import os
+
+# NCCL prints a version banner on STDOUT at its VERSION (and WARN) debug level, and NCCL_DEBUG_FILE does not
+# move it; stdout must carry the JSON line only, so that level is lowered before torch loads NCCL.
+if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+    os.environ["NCCL_DEBUG"] = "NONE"
 import sys
 import threading
 import time
