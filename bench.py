@@ -52,10 +52,11 @@ def parse():
     ap.add_argument("--bits", type=int, default=3)
     ap.add_argument("--seq", type=int, default=S, help="sequence length (default: the named workload)")
     ap.add_argument("--batch", type=int, default=B)
-    ap.add_argument("--workload", default="op", choices=["op", "llama8b", "deepseek7b", "quality"],
+    ap.add_argument("--workload", default="op", choices=["op", "llama8b", "deepseek7b", "quality", "decode"],
                     help="op: the op-level headline workload (default); llama8b / deepseek7b: end-to-end prefill of a "
                          "random-init model of that shape through apply_turboquant; quality: estimator quality "
-                         "metrics on a Qwen2.5-3B-shaped attention layer")
+                         "metrics on a Qwen2.5-3B-shaped attention layer; decode: one new token per sequence against a long "
+                         "compressed KV cache (split-KV kernel)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -301,12 +302,72 @@ def run_quality(args):
     print(json.dumps({"metric": "tq_estimator_quality", "workload": "qwen2.5-3b-shaped attention, synthetic", "results": out}))
 
 
+def run_decode(args):
+    """Decode step against a resident compressed KV cache: one query token per sequence (32 query / 8 KV heads,
+    d = 128) attends to Sk = 32768 cached keys, batch 8 — the per-GPU share of the scaling shape K,V
+    [64, 8, 32768, 128] over 8 GPUs.  The cache is compressed once outside the timed region; a step is the
+    fused attention call.  The work is bound by the packed bytes: per key (16 (b-1) + 16 + 4) + (16 b + 2)."""
+    import turboquant_b200 as tq
+    from turboquant_b200 import _lib
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    batch, sk, bits = 8, 32768, args.bits
+    g = torch.Generator(device=dev).manual_seed(0)
+    k = torch.randn(batch, HKV, sk, D, generator=g, device=dev).to(torch.bfloat16)
+    v = torch.randn(batch, HKV, sk, D, generator=g, device=dev).to(torch.bfloat16)
+    q = torch.randn(batch, HQ, 1, D, generator=g, device=dev).to(torch.bfloat16)
+    kc = tq.TurboQuantCompressorV2(D, bits, 42, device=str(dev))
+    vc = tq.TurboQuantCompressorMSE(D, bits, 10042, device=str(dev))
+    ck, cv = kc.compress(k), vc.compress(v)
+    del k, v
+
+    def timed(steps):
+        for _ in range(max(args.warmup, 3)):
+            tq.fused_attention(q, ck, cv, kc, vc, causal=True)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            out = tq.fused_attention(q, ck, cv, kc, vc, causal=True)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps, out
+
+    sampler = ClockSampler(0)
+    sampler.start()
+    _lib.check(_lib.lib.tq_profile_begin(max(args.steps, 1) + max(args.warmup, 3)))
+    ms, out = timed(args.steps)
+    ms_sum, launches = (ctypes.c_float * 5)(), (ctypes.c_int * 5)()
+    _lib.check(_lib.lib.tq_profile_end(ms_sum, launches))
+    clocks = sampler.finish()
+    kern_ms = ms_sum[3] / max(launches[3], 1)
+    keys = batch * HKV * sk
+    bytes_per_key = (16 * (bits - 1) + 16 + 4) + (16 * bits + 2)
+    peaks = measured_peaks()
+    achieved = keys * bytes_per_key / (kern_ms * 1e-3) / 1e9
+    line = {"metric": "tq_decode_keys_per_s", "value": keys / (ms * 1e-3), "unit": "keys/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "decode_b8_h32_kv8_sk32768", "batch_per_gpu": batch, "q_heads": HQ, "kv_heads": HKV,
+                       "new_tokens": 1, "cached_keys": sk, "head_dim": D, "bits": bits,
+                       "l2": f"packed cache ({keys * bytes_per_key / 1e6:.0f} MB) exceeds the 126 MB L2; no flush"},
+            "clocks": clocks, "gpu_launches": int(sum(launches)),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                         "kernel": "decode_kernel + combine_kernel", "ms_per_launch": kern_ms,
+                         "peak_source": peaks["source"]},
+            "device_wait_faults": tq.device_fault_count(dev), "output_norm": float(out.float().norm())}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     args = parse()
     if args.workload in MODEL_SHAPES:
         return run_model(args)
     if args.workload == "quality":
         return run_quality(args)
+    if args.workload == "decode":
+        return run_decode(args)
     if args.impl == "reference":
         return run_reference(args)
 

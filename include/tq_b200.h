@@ -171,6 +171,9 @@ int tq_prepare_queries(const void* q, int dtype, int64_t B, int64_t Hq, int64_t 
 /* Scratch bytes tq_attention_scores / tq_attention_fwd need for the given problem. */
 size_t tq_attention_workspace_bytes(int64_t B, int64_t Hq, int64_t Sq, int d, int mode);
 
+/* Decode-sized calls (query rows per KV head (Hq/Hkv)*Sq <= 16, Sk >= 256, d = 128, no mask, TQ_MODE_BF16)
+ * are served by a split-KV kernel that streams the packed bytes once; same arguments, same result.
+ * The reference has no counterpart: it disables the KV cache (patch.py:80-81). */
 /* Fused compressed attention: out = softmax(scores*sm_scale + mask) @ V_hat, computed
  * from packed keys and values without materialising scores or decompressed K/V.
  *   causal != 0 : query i (aligned to the end of the keys) sees keys <= i + Sk - Sq.

@@ -548,7 +548,7 @@ size_t tq_attention_workspace_bytes(int64_t B, int64_t Hq, int64_t Sq, int d, in
   // bf16 figure is the larger of the two.
   const size_t f32 = (n * 2 * d * 4 + 255) & ~(size_t)255;
   if (mode == TQ_MODE_FP32) return f32;
-  const size_t b16 = workspace_bytes_bf16((int64_t)n, d);
+  const size_t b16 = workspace_bytes_bf16(B * Hq, Sq, d);
   return b16 > f32 ? b16 : f32;
 }
 

@@ -770,10 +770,11 @@ static int launch_attention_tc(const AttnArgs& a, int64_t B, __nv_bfloat16* o_ro
 
 static inline size_t round256(size_t v) { return (v + 255) & ~(size_t)255; }
 
-// workspace layout (bf16 mode): [ w_cat | w_unrot | q_cat | o_rot ]
-size_t workspace_bytes_bf16(int64_t n_q, int d) {
+// workspace layout (bf16 mode): [ w_cat | w_unrot | q_cat | o_rot | partial results of the split-KV kernel ]
+size_t workspace_bytes_bf16(int64_t BHq, int64_t Sq, int d) {
+  const int64_t n_q = BHq * Sq;
   return round256((size_t)2 * d * d * 2) + round256((size_t)d * d * 2) + round256((size_t)n_q * 2 * d * 2) +
-         round256((size_t)n_q * d * 2);
+         round256((size_t)n_q * d * 2) + (Sq <= 16 ? decode_workspace_bytes(BHq) : 0);
 }
 
 // q_cat bf16 [n, 2d] = [ q Pi^T | coeff * q S^T ] on the tensor cores; `w_cat` is 2*d*d bf16 of scratch.
@@ -817,7 +818,8 @@ int attention_fwd_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_t 
   ws += round256((size_t)n_q * 2 * d * 2);
   __nv_bfloat16* o_rot = reinterpret_cast<__nv_bfloat16*>(ws);
 
-  const bool pairs = d == 128 && use_sm_pairs();
+  const bool decode = decode_applies(a, d) && Sq <= 16;
+  const bool pairs = d == 128 && use_sm_pairs() && !decode;
   build_wunrot_kernel<<<d, d, 0, stream>>>(a.Pi_v, d, w_unrot, pairs ? d / 2 : 0);
   TQ_CUDA_OK(cudaGetLastError());
   if (pairs) {
@@ -833,7 +835,10 @@ int attention_fwd_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_t 
 
   a.q_cat = q_cat;
   int st;
-  if (d == 128)
+  if (decode)
+    st = attention_decode(a, B, bits, q_cat, o_rot, reinterpret_cast<uint8_t*>(o_rot) + round256((size_t)n_q * d * 2),
+                          stream);
+  else if (d == 128)
     st = bits == 2   ? launch_attention_tc<128, 2>(a, B, o_rot, stream)
          : bits == 3 ? launch_attention_tc<128, 3>(a, B, o_rot, stream)
                      : launch_attention_tc<128, 4>(a, B, o_rot, stream);
