@@ -219,3 +219,33 @@ def test_long_sequence_tensor_core_vs_fp32_kernel_and_oracle(Hq, Hkv):
     want = torch.softmax(sc / d ** 0.5 + orc.causal_mask(S, S)[-32:], -1) @ vals
     assert rel_err(out32[1:2, -1:, -32:], want) < 4e-3   # fp32 arithmetic, but the output is stored as bf16 here
     assert rel_err(out16[1:2, -1:, -32:], want) < TOL["bf16"]
+
+
+@pytest.mark.parametrize("Sq", [1, 200])
+def test_compress_and_attention_replay_from_a_cuda_graph(Sq):
+    """The whole path (compress keys, compress values, fused attention; prefill- and decode-sized) is
+    capturable: no synchronisation, no allocation inside the library, work on the capture stream only.
+    A replay on new inputs in the same buffers reproduces the eager result."""
+    from turboquant_b200 import fused_attention
+    d, bits, B, Hq, Hkv, Sk = 128, 3, 2, 8, 2, 512
+    kc, vc = device_compressors(d, bits, mode="bf16")
+    q, k, v = (t.cuda() for t in _case(B, Hq, Hkv, Sq, Sk, d, seed=3, dtype=torch.bfloat16))
+
+    def run():
+        return fused_attention(q, kc.compress(k), vc.compress(v), kc, vc, causal=True, mode="bf16")
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            run()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out_g = run()
+    q2, k2, v2 = (t.cuda() for t in _case(B, Hq, Hkv, Sq, Sk, d, seed=4, dtype=torch.bfloat16))
+    q.copy_(q2); k.copy_(k2); v.copy_(v2)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out_g, run())
+
