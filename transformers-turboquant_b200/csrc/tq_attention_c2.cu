@@ -52,7 +52,7 @@ int read_c2_faults(unsigned long long* out) {
 
 // Diagnostics: stage timestamps of the first cluster's leader CTA, see tq_trace_read.
 constexpr int kTraceCap2 = 4096;
-__device__ int g_trace2_on = 0;
+static int g_trace2_host_on = 0;  // selects the tracing build of the kernel at launch
 __device__ long long g_trace2[2 * kTraceCap2];
 
 int trace_enable_c2(int on) {
@@ -60,7 +60,7 @@ int trace_enable_c2(int on) {
   static long long fill[2 * kTraceCap2];
   for (int i = 0; i < 2 * kTraceCap2; ++i) fill[i] = -1;
   TQ_CUDA_OK(cudaMemcpyToSymbol(g_trace2, fill, sizeof(fill)));
-  TQ_CUDA_OK(cudaMemcpyToSymbol(g_trace2_on, &v, sizeof(v)));
+  g_trace2_host_on = v;
   return TQ_OK;
 }
 int trace_read_c2(long long* host_buf, int max_records, int* n_out) {
@@ -73,11 +73,15 @@ int trace_read_c2(long long* host_buf, int max_records, int* n_out) {
 
 namespace {
 
+// The tracing build of the kernel (TRACE = true) is launched only while tracing is enabled; in the
+// production build every mark compiles to nothing.
+template <bool TRACE>
 struct Tracer2 {
   bool on;
   int role, n;
-  __device__ Tracer2(bool on_, int role_) : on(on_), role(role_), n(0) {}
+  __device__ Tracer2(bool on_, int role_) : on(TRACE && on_), role(role_), n(0) {}
   __device__ __forceinline__ void mark(int ev, int tile) {
+    if (!TRACE) return;
     if (!on || n >= kTraceCap2 / 4) return;
     const int i = role * (kTraceCap2 / 4) + n++;
     g_trace2[2 * i] = ((long long)role << 32) | ((long long)ev << 16) | (long long)tile;
@@ -85,6 +89,7 @@ struct Tracer2 {
   }
   // wall-clock nanoseconds next to the SM clock: their ratio over a CTA's life is the SM frequency under load
   __device__ __forceinline__ void mark_ns(int ev, int tile) {
+    if (!TRACE) return;
     if (!on || n >= kTraceCap2 / 4) return;
     const int i = role * (kTraceCap2 / 4) + n++;
     long long ns;
@@ -156,7 +161,7 @@ struct C2Smem {
   static_assert(2 * D <= 2 * kBN, "the Q_cat accumulator borrows both score tiles");
 };
 
-template <int D, int BITS>
+template <int D, int BITS, bool TRACE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
   using L = C2Smem<D, BITS>;
@@ -224,7 +229,7 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
 
   // The softmax warps fetch the raw query tile first of all (8 threads per 128-byte core matrix of the A
   // operand), so that the DRAM latency overlaps the barrier / tensor-memory set-up below.
-  const long long t_entry = clock64();
+  const long long t_entry = TRACE ? clock64() : 0;
   constexpr int NA = kBM * (D / 8) / kSoftmax;
   uint4 qv[NA];
   if (tid < kSoftmax) {
@@ -240,7 +245,7 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
       }
     }
   }
-  const long long t_q = clock64();
+  const long long t_q = TRACE ? clock64() : 0;
   if (warp == kPvWarp) {
     // barrier initialisation, one barrier per lane and round; then lane 0 starts the bulk copies of the
     // constant operands of the prologue and epilogue MMAs (no register staging)
@@ -272,10 +277,10 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
   if (warp == kCtlWarp) tc::tmem_alloc2(tc::smem_u32(&tmem_slot), L::kCols);
   fill_pair_lut<KB>(lutK, a.cen_k, tid, kThreads);
   fill_pair_lut<VB>(lutV, a.cen_v, tid, kThreads);
-  const long long t_i = clock64();
+  const long long t_i = TRACE ? clock64() : 0;
   tc::fence_before_sync();
   __syncthreads();
-  const long long t_s = clock64();
+  const long long t_s = TRACE ? clock64() : 0;
   tc::cluster_sync();  // the peer's barriers and tensor memory exist before anyone signals or issues
   tc::fence_after_sync();
   const bool dead = s_abort != 0;  // an earlier bounded wait expired: do nothing but keep the cluster barriers paired
@@ -284,7 +289,7 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
   const uint32_t tmem_o = tmem_base + L::kColO;
   bool ok = true;
   // traced: the heaviest cluster of the last (head pair, batch), which runs late in the launch
-  Tracer2 tr(g_trace2_on != 0 && blockIdx.x == 0 && blockIdx.y == gridDim.y - 1 && blockIdx.z == gridDim.z - 1 && lane == 0 &&
+  Tracer2<TRACE> tr(blockIdx.x == 0 && blockIdx.y == gridDim.y - 1 && blockIdx.z == gridDim.z - 1 && lane == 0 &&
                  (warp == 0 || warp == kSoftmax / 32 || warp >= kCtlWarp),
              warp == 0 ? 0 : warp == kSoftmax / 32 ? 1 : warp == kCtlWarp ? 2 : 3);
 
@@ -295,7 +300,7 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
     const int qi = q0 + row;
     const int64_t qrow = (b * a.Hq + head) * a.Sq + qi;
     const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
-    if (tr.on) {  // kernel entry, measured before the set-up
+    if (TRACE && tr.on) {  // kernel entry, measured before the set-up
       const int i = tr.role * (kTraceCap2 / 4) + tr.n++;
       g_trace2[2 * i] = ((long long)tr.role << 32) | (25ll << 16) | 999ll;
       g_trace2[2 * i + 1] = t_entry;
@@ -784,7 +789,7 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
 template <int D, int BITS>
 int launch_c2(const AttnArgs& a, const PairArgs& x, int64_t B, cudaStream_t stream) {
   constexpr size_t smem = C2Smem<D, BITS>::kTotal > 120 * 1024 ? C2Smem<D, BITS>::kTotal : 120 * 1024;
-  auto kern = attention_c2_kernel<D, BITS>;
+  auto kern = g_trace2_host_on ? attention_c2_kernel<D, BITS, true> : attention_c2_kernel<D, BITS, false>;
   TQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int pair_heads = ((a.Hq / a.Hkv) % 2 == 0) ? 1 : 0;
   const int64_t blocks = (a.Sq + kBM - 1) / kBM;
