@@ -528,6 +528,7 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
     // This CTA decodes keys [k0 + 64 rank, +64) of K_hat (all 2D contraction columns) and value
     // coordinates [D/2 rank, +D/2) of all 128 keys of V_hat.
     const int p = tid - kSoftmax;
+    __builtin_assume(p >= 0 && p < kProducers);      // lets the compiler drop the always-true unit guards below
     constexpr int GPK = G / 2;                       // 16-coordinate items per key row
     constexpr int GPV = G / 4;                       // ... per half value row
     constexpr int UK = L::kIdxK / 8, US = L::kSgn / 8, UV = L::kIdxV / 8;  // 8-byte units staged per tile
@@ -628,7 +629,7 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
             for (int x = 0; x < KB; ++x) w |= (uint64_t)sk[x] << (16 * x);
             gw[i][0] = (uint32_t)w & ((1u << (8 * KB)) - 1);
             gw[i][1] = (uint32_t)(w >> (8 * KB));
-            sb[i] = ~(uint32_t)*reinterpret_cast<const uint16_t*>(pk + L::kIdxK + kkey[i] * G + kgp[i] * 2);
+            sb[i] = 0xffffu ^ (uint32_t)*reinterpret_cast<const uint16_t*>(pk + L::kIdxK + kkey[i] * G + kgp[i] * 2);
             const float rho = rho_s[ps][kkey[i]], nkf = nk_s[ps][kkey[i]];
             rr[i] = tc::pack_bf16x2(rho, rho);
             nk2[i] = __floats2bfloat162_rn(nkf, nkf);
@@ -646,7 +647,11 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
               for (int q = 0; q < 4; ++q) {
                 const __nv_bfloat162 prod = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&kq[q]), nk2[i]);
                 kq[q] = *reinterpret_cast<const uint32_t*>(&prod);
-                sq[q] = rr[i] ^ ((((sb[i] >> (8 * half + 2 * q)) & 3u) * 0x40008000u) & 0x80008000u);
+                // sign bits 2q, 2q+1 of this half -> bits 15 and 31: x * (2^15 + 2^30) puts bit i of x at i + 15 and
+                // i + 30; with x < 2^15 (upper half of sb is zero, shift >= 1) no two terms meet, so only the
+                // unshifted case needs the two bits isolated first
+                const uint32_t x = (half == 0 && q == 0) ? (sb[i] & 3u) : (sb[i] >> (8 * half + 2 * q));
+                sq[q] = rr[i] ^ ((x * 0x40008000u) & 0x80008000u);
               }
               const int g = 2 * kgp[i] + half;
               *reinterpret_cast<uint4*>(kd + g * 128) = make_uint4(kq[0], kq[1], kq[2], kq[3]);
