@@ -116,10 +116,12 @@ __device__ __forceinline__ void fill_pair_lut(uint32_t* lut, const float* __rest
   for (int e = tid; e < (1 << (2 * B)); e += nthreads)
     lut[e] = tc::pack_bf16x2(cen[e & ((1 << B) - 1)], cen[e >> B]);
 }
+// `bits` holds exactly 8 B-bit indices (nothing above bit 8 B), so the last pair needs no mask
 template <int B>
 __device__ __forceinline__ void decode_group(const uint32_t* lut, uint32_t bits, uint32_t (&out)[4]) {
 #pragma unroll
-  for (int q = 0; q < 4; ++q) out[q] = lut[(bits >> (2 * q * B)) & ((1u << (2 * B)) - 1)];
+  for (int q = 0; q < 3; ++q) out[q] = lut[(bits >> (2 * q * B)) & ((1u << (2 * B)) - 1)];
+  out[3] = lut[bits >> (6 * B)];
 }
 
 template <int D, int BITS>
@@ -625,8 +627,12 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
           if (i * kProducers + p < kHalfN * GPK) {
             const uint16_t* sk = reinterpret_cast<const uint16_t*>(pk + kkey[i] * (G * KB) + kgp[i] * 2 * KB);
             uint64_t w = 0;
+            if constexpr (KB == 2) {
+              w = *reinterpret_cast<const uint32_t*>(sk);  // 4-byte aligned: rows are 32 bytes, items 4
+            } else {
 #pragma unroll
-            for (int x = 0; x < KB; ++x) w |= (uint64_t)sk[x] << (16 * x);
+              for (int x = 0; x < KB; ++x) w |= (uint64_t)sk[x] << (16 * x);
+            }
             gw[i][0] = (uint32_t)w & ((1u << (8 * KB)) - 1);
             gw[i][1] = (uint32_t)(w >> (8 * KB));
             sb[i] = 0xffffu ^ (uint32_t)*reinterpret_cast<const uint16_t*>(pk + L::kIdxK + kkey[i] * G + kgp[i] * 2);
@@ -678,8 +684,14 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
             const uint16_t* sv =
                 reinterpret_cast<const uint16_t*>(pk + L::kIdxK + L::kSgn + vkey[i] * VROW + vgp[i] * 2 * VB);
             uint64_t w = 0;
+            if constexpr (VB == 2) {
+              w = *reinterpret_cast<const uint32_t*>(sv);
+            } else if constexpr (VB == 4) {
+              w = *reinterpret_cast<const uint64_t*>(sv);
+            } else {
 #pragma unroll
-            for (int x = 0; x < VB; ++x) w |= (uint64_t)sv[x] << (16 * x);
+              for (int x = 0; x < VB; ++x) w |= (uint64_t)sv[x] << (16 * x);
+            }
             gw[i][0] = (uint32_t)w & (VB == 4 ? 0xffffffffu : ((1u << (8 * (VB & 3))) - 1));
             gw[i][1] = (uint32_t)(w >> (8 * VB));
             const float nvf = nv_s[ps][vkey[i]];
