@@ -35,14 +35,18 @@ int read_wait_faults(unsigned long long* out) {
 
 // Diagnostics: stage timestamps (SM clock) of one CTA of the attention kernel, see tq_trace_read.
 constexpr int kTraceCap = 4096;
-__device__ int g_trace_on = 0;
+static int g_trace_host_on = 0;  // selects the tracing build of the attention kernel at launch
 __device__ long long g_trace[2 * kTraceCap];
-// One tracer per traced thread: role r appends to its own third of the buffer, no atomics.
+// One tracer per traced thread: role r appends to its own third of the buffer, no atomics.  The tracing
+// build of the kernel (TRACE = true) is launched only while tracing is enabled; in the production build
+// every mark compiles to nothing.
+template <bool TRACE>
 struct Tracer {
   bool on;
   int role, n;
-  __device__ Tracer(bool on_, int role_) : on(on_), role(role_), n(0) {}
+  __device__ Tracer(bool on_, int role_) : on(TRACE && on_), role(role_), n(0) {}
   __device__ __forceinline__ void mark(int ev, int tile) {
+    if (!TRACE) return;
     if (!on || n >= kTraceCap / 3) return;
     const int i = role * (kTraceCap / 3) + n++;
     g_trace[2 * i] = ((long long)role << 32) | ((long long)ev << 16) | (long long)tile;
@@ -257,7 +261,7 @@ struct WsSmem {
   static_assert(kColO + 2 * D <= kCols, "tensor memory over-subscribed");
 };
 
-template <int D, int BITS>
+template <int D, int BITS, bool TRACE>
 __global__ void __launch_bounds__(kWsThreads, 1)
 attention_ws_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const int pair_heads) {
   using L = WsSmem<D, BITS>;
@@ -332,7 +336,7 @@ attention_ws_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
   tc::fence_after_sync();
   const uint32_t tmem_base = tmem_slot;
   bool ok = true;
-  Tracer tr(g_trace_on != 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 &&
+  Tracer<TRACE> tr(blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 &&
                 (warp == 0 || warp == 8 || warp == kMmaWarp),
             warp == 0 ? 0 : warp == 8 ? 1 : 2);
 
@@ -722,7 +726,7 @@ int trace_enable(int on) {
   static long long fill[2 * kTraceCap];
   for (int i = 0; i < 2 * kTraceCap; ++i) fill[i] = -1;
   TQ_CUDA_OK(cudaMemcpyToSymbol(g_trace, fill, sizeof(fill)));
-  TQ_CUDA_OK(cudaMemcpyToSymbol(g_trace_on, &v, sizeof(v)));
+  g_trace_host_on = v;
   return TQ_OK;
 }
 int trace_read(long long* host_buf, int max_records, int* n_out) {
@@ -753,7 +757,7 @@ static int launch_attention_tc(const AttnArgs& a, int64_t B, __nv_bfloat16* o_ro
   // every CTA takes all 512 tensor-memory columns, so keep it alone on its SM: ask for more than
   // half of the shared memory even when the tiles (d = 64) would need less
   constexpr size_t smem = WsSmem<D, BITS>::kTotal > 120 * 1024 ? WsSmem<D, BITS>::kTotal : 120 * 1024;
-  auto kern = attention_ws_kernel<D, BITS>;
+  auto kern = g_trace_host_on ? attention_ws_kernel<D, BITS, true> : attention_ws_kernel<D, BITS, false>;
   TQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   // two query tiles per CTA: two heads of one GQA group when the group size is even, otherwise
   // two consecutive position blocks of one head
