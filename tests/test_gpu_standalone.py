@@ -26,7 +26,7 @@ def test_pack_unpack_quantize_dequantize_wrappers(b):
     assert packed.dtype == torch.uint8 and np.array_equal(packed.cpu().numpy(), orc.pack_bits(idx, b))
     assert np.array_equal(unpack_bits(packed, b, 128).cpu().numpy(), idx)
     if b <= 4:
-        from turboquant_b200.lloyd_max import solve_lloyd_max
+        from turboquant_b200.scalar_codebook import solve_lloyd_max
         cen, bnd = solve_lloyd_max(128, b)
         y = torch.from_numpy(rng.standard_normal((300, 128)).astype(np.float32) / np.sqrt(128))
         q = lloyd_max_quantize(y.cuda(), bnd.cuda(), b)

@@ -9,7 +9,7 @@ import torch
 @pytest.mark.parametrize("d", [64, 128])
 @pytest.mark.parametrize("bits", [1, 2, 3, 4])
 def test_solver_matches_reference_to_the_bit(d, bits, golden_constants):
-    from turboquant_b200.lloyd_max import solve_lloyd_max
+    from turboquant_b200.scalar_codebook import solve_lloyd_max
     cen, bnd = solve_lloyd_max(d, bits)
     assert cen.dtype == torch.float32 and bnd.dtype == torch.float32
     assert np.array_equal(cen.numpy(), golden_constants[f"lm_centroids_d{d}_b{bits}"])
@@ -18,14 +18,14 @@ def test_solver_matches_reference_to_the_bit(d, bits, golden_constants):
 
 
 def test_exact_beta_codebook_is_close_to_the_gaussian_one():
-    from turboquant_b200.lloyd_max import solve_lloyd_max
+    from turboquant_b200.scalar_codebook import solve_lloyd_max
     g, _ = solve_lloyd_max(128, 3)
     e, _ = solve_lloyd_max(128, 3, use_exact=True)
     assert e.shape == g.shape and float((e - g).abs().max()) < 2e-3 and float((e - g).abs().max()) > 0
 
 
 def test_codebook_cpu_semantics_and_distortion():
-    from turboquant_b200.lloyd_max import LloydMaxCodebook
+    from turboquant_b200.scalar_codebook import LloydMaxCodebook
     g = np.load(__import__("os").path.join(__import__("os").path.dirname(__file__), "golden", "standalone.npz"))
     cb = LloydMaxCodebook(128, 3)
     assert cb.n_levels == 8 and abs(cb.distortion - float(g["codebook_distortion_d128_b3"])) < 1e-12
@@ -48,7 +48,7 @@ def test_reference_import_names_resolve():
 
 
 def test_rotation_and_sketch_generators_match_reference_constants():
-    from turboquant_b200.turboquant import generate_qjl_matrix, generate_rotation_matrix
+    from turboquant_b200.quantizers import generate_qjl_matrix, generate_rotation_matrix
     pi = generate_rotation_matrix(128, seed=42, device="cpu")
     assert np.allclose(pi[0, :4].numpy(), [0.174885, 0.120727, 0.085467, -0.145567], atol=1e-6)
     assert torch.allclose(pi @ pi.T, torch.eye(128), atol=1e-5)

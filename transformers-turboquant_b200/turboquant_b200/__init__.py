@@ -11,8 +11,8 @@ from .plugin import (TurboQuantAttentionBase, UnsupportedModelError, apply_turbo
 from . import families  # noqa: F401,E402  (registers the adapters)
 from .kernels import (asymmetric_attention_scores, lloyd_max_dequantize, lloyd_max_quantize,  # noqa: E402
                       pack_bits, unpack_bits)
-from .lloyd_max import LloydMaxCodebook, solve_lloyd_max  # noqa: E402
-from .turboquant import TurboQuantKVCache, TurboQuantMSE, TurboQuantProd  # noqa: E402
+from .scalar_codebook import LloydMaxCodebook, solve_lloyd_max  # noqa: E402
+from .quantizers import TurboQuantKVCache, TurboQuantMSE, TurboQuantProd  # noqa: E402
 
 __version__ = "0.1.0"
 __all__ = ["apply_turboquant", "register_family", "get_attention_class", "UnsupportedModelError",

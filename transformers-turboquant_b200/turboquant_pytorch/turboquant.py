@@ -1,3 +1,3 @@
 """Import-name compatibility for `turboquant_pytorch.turboquant`."""
-from turboquant_b200.turboquant import (TurboQuantKVCache, TurboQuantMSE, TurboQuantProd,  # noqa: F401
+from turboquant_b200.quantizers import (TurboQuantKVCache, TurboQuantMSE, TurboQuantProd,  # noqa: F401
                                         generate_qjl_matrix, generate_rotation_matrix)
