@@ -19,6 +19,8 @@
 #include <math.h>
 #include <stdlib.h>
 
+#include <type_traits>
+
 #include "tq_attention.cuh"
 #include "tq_common.cuh"
 #include "tq_simt.cuh"
@@ -66,13 +68,30 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-// `nbits` bits at bit offset `bit` of a little-endian word array (bit + nbits may cross one word boundary)
-// SPLIT says whether the field can cross into the next word (3-bit rows); otherwise one shift does.
-template <int NW, bool SPLIT>
-__device__ __forceinline__ uint32_t field(const uint32_t (&w)[NW], int word, int shift, uint32_t mask) {
-  if (!SPLIT) return (w[word] >> shift) & mask;
-  const uint64_t win = (static_cast<uint64_t>(w[word + 1 < NW ? word + 1 : word]) << 32) | w[word];
-  return static_cast<uint32_t>(win >> shift) & mask;
+// NBITS bits of a little-endian word array at bit offset 8 * BYTE + r, with BYTE known at compile time and
+// the run-time part r <= MAXR.  Stays inside one word when it can (one shift, one mask); otherwise takes the
+// four bytes starting at BYTE out of two neighbouring words with one byte permute first.
+template <int NW, int BYTE, int MAXR, int NBITS>
+__device__ __forceinline__ uint32_t field(const uint32_t (&w)[NW], int r) {
+  constexpr int word = BYTE / 4, bo = BYTE % 4;
+  constexpr uint32_t mask = (1u << NBITS) - 1;
+  static_assert(MAXR + NBITS <= 32, "field wider than a window");
+  if constexpr (8 * bo + MAXR + NBITS <= 32) {
+    return (w[word] >> (8 * bo + r)) & mask;
+  } else {
+    constexpr uint32_t sel = bo == 1 ? 0x4321u : bo == 2 ? 0x5432u : 0x6543u;
+    const uint32_t win = __byte_perm(w[word], w[word + 1 < NW ? word + 1 : word], sel);
+    return (win >> r) & mask;
+  }
+}
+
+// f(integral_constant<int, I>) for I = FROM .. TO-1: a loop whose index is usable as a template argument
+template <int FROM, int TO, class F>
+__device__ __forceinline__ void static_for(F&& f) {
+  if constexpr (FROM < TO) {
+    f(std::integral_constant<int, FROM>{});
+    static_for<FROM + 1, TO>(f);
+  }
 }
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
@@ -212,8 +231,8 @@ __global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a)
         const float rho = cur.nk[nt] > 0.f ? __fdividef(cur.rn[nt], cur.nk[nt]) : 0.f;
         rr[nt] = bf16x2(rho, rho);
       }
-#pragma unroll
-      for (int ks = 0; ks < 16; ++ks) {
+      static_for<0, 16>([&](auto ks_c) {
+        constexpr int ks = decltype(ks_c)::value;
         uint32_t qa[4];
         qa[0] = *reinterpret_cast<const uint32_t*>(&q_s[gq * kQPitch + 16 * ks + 2 * tq]);
         qa[1] = *reinterpret_cast<const uint32_t*>(&q_s[(gq + 8) * kQPitch + 16 * ks + 2 * tq]);
@@ -222,12 +241,11 @@ __global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a)
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
           uint32_t b0, b1;
-          if (ks < 8) {
+          if constexpr (ks < 8) {
             // coordinates 16 ks + 2 tq, +1 (b0) and + 8, + 9 (b1): two adjacent indices = one table entry
-            constexpr uint32_t pm = (1u << (2 * KB)) - 1;
-            const int bit0 = 16 * KB * ks, sh = (bit0 % 32) + 2 * KB * tq;
-            const uint32_t p0 = field<KW, KB == 3>(kw[nt], bit0 / 32, sh, pm);
-            const uint32_t p1 = field<KW, KB == 3>(kw[nt], bit0 / 32, sh + 8 * KB, pm);
+            // (the 16 indices of this k-step start at byte 2 KB ks; a pair is 2 KB bits wide)
+            const uint32_t p0 = field<KW, 2 * KB * ks, 6 * KB, 2 * KB>(kw[nt], 2 * KB * tq);
+            const uint32_t p1 = field<KW, 2 * KB * ks + KB, 6 * KB, 2 * KB>(kw[nt], 2 * KB * tq);
             b0 = lutK[p0];
             b1 = lutK[p1];
           } else {
@@ -238,7 +256,7 @@ __global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a)
           }
           mma16816(s[nt], qa, b0, b1);
         }
-      }
+      });
     }
     // ================= online softmax on the fragments =================
     // s[nt][0..1]: row gq, keys blk + 8 nt + 2 tq, +1;  s[nt][2..3]: row gq + 8, same keys
@@ -307,17 +325,16 @@ __global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a)
           vw[kq][4 * i] = v.x; vw[kq][4 * i + 1] = v.y; vw[kq][4 * i + 2] = v.z; vw[kq][4 * i + 3] = v.w;
         }
       }
-#pragma unroll
-      for (int ct = 0; ct < D / 8; ++ct) {
+      static_for<0, D / 8>([&](auto ct_c) {
+        constexpr int ct = decltype(ct_c)::value;
         // coordinate 8 ct + gq of the four keys
-        constexpr uint32_t vm = (1u << VB) - 1;
-        const int bit0 = 8 * VB * ct, sh = (bit0 % 32) + VB * gq;
+        // (the 8 indices of this coordinate tile start at byte VB ct of the row)
         uint32_t e[4];
 #pragma unroll
-        for (int kq = 0; kq < 4; ++kq) e[kq] = lutV[field<VW, VB == 3>(vw[kq], bit0 / 32, sh, vm)];
+        for (int kq = 0; kq < 4; ++kq) e[kq] = lutV[field<VW, VB * ct, 7 * VB, VB>(vw[kq], VB * gq)];
         const uint32_t b0 = __byte_perm(e[0], e[1], 0x5410), b1 = __byte_perm(e[2], e[3], 0x5410);
         mma16816(o[ct], pa, b0, b1);
-      }
+      });
     }
     cur = nxt;
     __syncwarp();  // every lane is done with this stage before the next iteration refills it
