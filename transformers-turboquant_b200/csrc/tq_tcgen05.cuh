@@ -109,11 +109,6 @@ __device__ __forceinline__ bool mbar_wait_or_abort(uint32_t bar, uint32_t parity
   }
   return true;
 }
-__device__ __forceinline__ uint32_t add_f16x2(uint32_t a, uint32_t b) {
-  uint32_t r;
-  asm("add.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-  return r;
-}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -125,23 +120,6 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
   return r;
 }
-// Packed fp32 pairs (one instruction per two lanes of work): {d0, d1} = {a0, a1} * b + c and
-// {acc0, acc1} += {x0, x1}.
-__device__ __forceinline__ void ffma2(float& d0, float& d1, float a0, float a1, float b, float c) {
-  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
-      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmov.b64 rc, {%5, %5};\n\t"
-      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
-      : "=f"(d0), "=f"(d1)
-      : "f"(a0), "f"(a1), "f"(b), "f"(c));
-}
-__device__ __forceinline__ void fadd2(float& acc0, float& acc1, float x0, float x1) {
-  asm("{\n\t.reg .b64 ra, rx;\n\t"
-      "mov.b64 ra, {%0, %1};\n\tmov.b64 rx, {%2, %3};\n\t"
-      "add.rn.f32x2 ra, ra, rx;\n\tmov.b64 {%0, %1}, ra;\n\t}"
-      : "+f"(acc0), "+f"(acc1)
-      : "f"(x0), "f"(x1));
-}
-
 // ---- proxies and ordering ----------------------------------------------------------------
 
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
