@@ -525,7 +525,7 @@ def main():
                        "seq_len": seq, "head_dim": D, "bits": bits, "causal": True,
                        "l2": "inputs (402 MB per step) exceed the 126 MB L2; no flush",
                        "causal_pairs_per_s": causal_pairs(batch, seq) * world / (ms_per_step * 1e-3)},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": (int(sum(launches)) + 2 * args.steps) * world,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": (int(sum(launches)) + 3 * args.steps) * world,  # + the three constant-operand builders per step
             "roofline": roofline, "cpu_baseline": cpu, "device_wait_faults": faults}
     print(json.dumps(line), flush=True)
     if dist is not None:

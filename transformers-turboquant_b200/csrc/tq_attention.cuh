@@ -58,6 +58,7 @@ struct PairArgs {
   int64_t q_stride_b, q_stride_h, q_stride_s;
   const __nv_bfloat16* w_cat;    // [2d, d] = [Pi ; coeff S]
   const __nv_bfloat16* w_unrot;  // [d, d]  = Pi_v^T
+  const uint32_t* luts;          // pair tables: 4^(bits-1) key entries, then 4^bits value entries (bf16x2 words)
 };
 
 // SM-pair (2-CTA cluster) tensor-core kernel, head_dim 128; needs no per-query scratch.

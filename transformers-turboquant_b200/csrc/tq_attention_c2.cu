@@ -111,11 +111,6 @@ constexpr int kPvWarp = kThreads / 32 - 1;    // issues the P V_hat MMAs in the 
 constexpr int kSoftmaxArrivals = 2 * kSoftmax / 32;     // softmax warps of both CTAs
 constexpr int kProducerArrivals = 2 * kProducers / 32;  // producer warps of both CTAs
 
-template <int B>
-__device__ __forceinline__ void fill_pair_lut(uint32_t* lut, const float* __restrict__ cen, int tid, int nthreads) {
-  for (int e = tid; e < (1 << (2 * B)); e += nthreads)
-    lut[e] = tc::pack_bf16x2(cen[e & ((1 << B) - 1)], cen[e >> B]);
-}
 // `bits` holds exactly 8 B-bit indices (nothing above bit 8 B), so the last pair needs no mask
 template <int B>
 __device__ __forceinline__ void decode_group(const uint32_t* lut, uint32_t bits, uint32_t (&out)[4]) {
@@ -176,9 +171,9 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
   __shared__ float rho_s[2][kHalfN];
   __shared__ float nv_s[2][kBN];          // value norms of all keys of the tile
   __shared__ float xmax[2][kSoftmax / kBM][kBM];  // [tile parity][column part][row]
-  __shared__ uint32_t lutK[1 << (2 * KB)];
-  __shared__ uint32_t lutV[1 << (2 * VB)];
-  __shared__ __align__(8) uint64_t bars[4 * kStages + 8 + 2 + 4 + 7];
+  __shared__ __align__(16) uint32_t lutK[1 << (2 * KB)];  // pair tables, bulk-copied from their global image
+  __shared__ __align__(16) uint32_t lutV[1 << (2 * VB)];
+  __shared__ __align__(8) uint64_t bars[4 * kStages + 22];
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
   volatile int* abort_flag = &s_abort;
@@ -223,6 +218,7 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
   const uint32_t w_full = bar0 + 8u * (4 * kStages + 18);                   // local, bulk-copy bytes
   const uint32_t u_full = bar0 + 8u * (4 * kStages + 19);                   // local, bulk-copy bytes
   const uint32_t u_peer = bar0 + 8u * (4 * kStages + 20);                   // leader: the peer's Pi_v^T half is in
+  const uint32_t lut_full = bar0 + 8u * (4 * kStages + 21);                 // local, bulk-copy bytes
   // one arrival on a barrier that lives in rank 0: local form there, cluster address from the peer
   auto arrive_leader = [&](uint32_t bar) {
     if (rank == 0) tc::mbar_arrive(bar);
@@ -251,7 +247,7 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
   if (warp == kPvWarp) {
     // barrier initialisation, one barrier per lane and round; then lane 0 starts the bulk copies of the
     // constant operands of the prologue and epilogue MMAs (no register staging)
-    constexpr int kBars = 4 * kStages + 21;
+    constexpr int kBars = 4 * kStages + 22;
     for (int i = lane; i < kBars; i += 32) {
       const int r = i - 4 * kStages;
       uint32_t count = 1;                                     // commit / bulk-copy / single-thread barriers
@@ -273,12 +269,14 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
         tc::bulk_load(tc::smem_u32(smem_raw + L::kWOff), x.w_cat + (int64_t)rank * D * D, L::kWBytes, w_full);
         tc::mbar_arrive_expect_tx(u_full, L::kUBytes);
         tc::bulk_load(tc::smem_u32(smem_raw + L::kUOff), x.w_unrot + (int64_t)rank * (D / 2) * D, L::kUBytes, u_full);
+        // the decode tables too: nobody waits for them here, the producers do before their first tile
+        tc::mbar_arrive_expect_tx(lut_full, (uint32_t)(sizeof(lutK) + sizeof(lutV)));
+        tc::bulk_load(tc::smem_u32(lutK), x.luts, (uint32_t)sizeof(lutK), lut_full);
+        tc::bulk_load(tc::smem_u32(lutV), x.luts + (1 << (2 * KB)), (uint32_t)sizeof(lutV), lut_full);
       }
     }
   }
   if (warp == kCtlWarp) tc::tmem_alloc2(tc::smem_u32(&tmem_slot), L::kCols);
-  fill_pair_lut<KB>(lutK, a.cen_k, tid, kThreads);
-  fill_pair_lut<VB>(lutV, a.cen_v, tid, kThreads);
   const long long t_i = TRACE ? clock64() : 0;
   tc::fence_before_sync();
   __syncthreads();
@@ -591,7 +589,10 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
       vkey[i] = (e % 8) + 8 * (e / (8 * GPV));
       vgp[i] = (e / 8) % GPV;
     }
-    if (n_tiles > 0) prefetch(0);
+    if (n_tiles > 0) {
+      prefetch(0);
+      ok = tc::mbar_wait_or_abort(lut_full, 0, abort_flag);  // the decode tables have landed
+    }
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int st = j % kStages, u = j / kStages, ps = j & 1;
       uint8_t* pk = smem_raw + L::kPkOff + ps * L::kPkStage;

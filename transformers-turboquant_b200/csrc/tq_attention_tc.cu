@@ -84,6 +84,18 @@ __global__ void build_wunrot_kernel(const float* __restrict__ Pi_v, int d, __nv_
   w_unrot[operand_index(j, i, d, tile_rows)] = __float2bfloat16_rn(Pi_v[i * d + j]);
 }
 
+// Pair tables of the SM-pair kernel: entry (i1 << B | i0) = bf16x2 (C[i0], C[i1]); 4^(bits-1) key entries
+// followed by 4^bits value entries, so that the kernel can bulk-copy them into shared memory.
+__global__ void build_luts_kernel(const float* __restrict__ cen_k, const float* __restrict__ cen_v, int kb, int vb,
+                                  uint32_t* __restrict__ luts) {
+  const int nk = 1 << (2 * kb), nv = 1 << (2 * vb);
+  for (int e = threadIdx.x; e < nk + nv; e += blockDim.x) {
+    const float* cen = e < nk ? cen_k : cen_v;
+    const int b = e < nk ? kb : vb, i = e < nk ? e : e - nk;
+    luts[e] = tc::pack_bf16x2(cen[i & ((1 << b) - 1)], cen[i >> b]);
+  }
+}
+
 // ---- row GEMM ----------------------------------------------------------------------------
 
 struct RowsGemmArgs {
@@ -774,10 +786,12 @@ static int launch_attention_tc(const AttnArgs& a, int64_t B, __nv_bfloat16* o_ro
 
 static inline size_t round256(size_t v) { return (v + 255) & ~(size_t)255; }
 
-// workspace layout (bf16 mode): [ w_cat | w_unrot | q_cat | o_rot | partial results of the split-KV kernel ]
+// workspace layout (bf16 mode): [ w_cat | w_unrot | decode tables | q_cat | o_rot | partial results of the
+// split-KV kernel ]
+constexpr size_t kLutBytes = 2048;  // (4^3 + 4^4) words at most
 size_t workspace_bytes_bf16(int64_t BHq, int64_t Sq, int d) {
   const int64_t n_q = BHq * Sq;
-  return round256((size_t)2 * d * d * 2) + round256((size_t)d * d * 2) + round256((size_t)n_q * 2 * d * 2) +
+  return round256((size_t)2 * d * d * 2) + round256((size_t)d * d * 2) + kLutBytes + round256((size_t)n_q * 2 * d * 2) +
          round256((size_t)n_q * d * 2) + (Sq <= 16 ? decode_workspace_bytes(BHq) : 0);
 }
 
@@ -818,6 +832,8 @@ int attention_fwd_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_t 
   ws += round256((size_t)2 * d * d * 2);
   __nv_bfloat16* w_unrot = reinterpret_cast<__nv_bfloat16*>(ws);
   ws += round256((size_t)d * d * 2);
+  uint32_t* luts = reinterpret_cast<uint32_t*>(ws);
+  ws += kLutBytes;
   __nv_bfloat16* q_cat = reinterpret_cast<__nv_bfloat16*>(ws);
   ws += round256((size_t)n_q * 2 * d * 2);
   __nv_bfloat16* o_rot = reinterpret_cast<__nv_bfloat16*>(ws);
@@ -831,7 +847,9 @@ int attention_fwd_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_t 
     // bulk-copies its half of either constant operand (d rows of w_cat, d/2 rows of w_unrot)
     build_wcat_kernel<<<d, d, 0, stream>>>(Pi_k, S_eff, d, sqrtf(1.5707963267948966f) / (float)d, w_cat, d);
     TQ_CUDA_OK(cudaGetLastError());
-    const PairArgs x{q, dtype, sb, sh, ss, w_cat, w_unrot};
+    build_luts_kernel<<<1, 128, 0, stream>>>(a.cen_k, a.cen_v, bits - 1, bits, luts);
+    TQ_CUDA_OK(cudaGetLastError());
+    const PairArgs x{q, dtype, sb, sh, ss, w_cat, w_unrot, luts};
     return attention_c2(a, x, B, d, bits, stream);
   }
   if (int st = prepare_queries_bf16(q, dtype, B, Hq, Sq, d, sb, sh, ss, Pi_k, S_eff, w_cat, q_cat, stream)) return st;
