@@ -281,7 +281,7 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
   tc::fence_before_sync();
   __syncthreads();
   const long long t_s = TRACE ? clock64() : 0;
-  tc::cluster_sync();  // the peer's barriers and tensor memory exist before anyone signals or issues
+  tc::cluster_sync_relaxed();  // the peer's barriers and tensor memory exist before anyone signals or issues
   tc::fence_after_sync();
   const bool dead = s_abort != 0;  // an earlier bounded wait expired: do nothing but keep the cluster barriers paired
   const int n_tiles = dead ? 0 : n_tiles_live;
@@ -800,7 +800,7 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
   if (!ok && atomicExch(&s_abort, 2) != 2) atomicAdd(&g_c2_faults, 1ull);  // one fault per CTA
   tc::fence_before_sync();
   __syncthreads();
-  tc::cluster_sync();  // neither CTA leaves (or frees tensor memory) while the pair's MMAs or signals may touch it
+  tc::cluster_sync_relaxed();  // neither CTA leaves (or frees tensor memory) while the pair's MMAs or signals may touch it
   if (warp == kCtlWarp) tc::tmem_dealloc2(tmem_base, L::kCols);
 }
 

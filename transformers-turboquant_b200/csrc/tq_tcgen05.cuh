@@ -226,6 +226,13 @@ __device__ __forceinline__ void cluster_sync() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// The same rendezvous without a cluster-scope release of this thread's earlier writes (measured at ~2 700
+// cycles per call against a few hundred): enough where what the peer must see has been published by
+// fence.mbarrier_init (barrier initialisation) or is not data at all (nobody leaves before both are done).
+__device__ __forceinline__ void cluster_sync_relaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+}
 // Shared-memory address of the same variable in CTA `rank` of the cluster.
 __device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
   uint32_t r;
