@@ -103,3 +103,28 @@ def test_llama_bf16_is_causal_and_close_to_fp32_mode():
     assert torch.equal(a[:, :-1], b2[:, :-1])         # HF passes no mask under sdpa: causality is ours
     assert not torch.equal(a[:, -1], b2[:, -1])
     assert rel_err(a, ref) < 1e-1                     # whole model (weights included) in bf16 vs fp32
+
+
+@pytest.mark.parametrize("kind", ["gpt2", "llama"])
+def test_single_training_step_completes(kind):
+    """The reference's fine-tuning check (tests/test_sft.py:19-43: one optimiser step on a patched
+    model finishes) without the trainer or a download.  Compression, scoring and the value
+    reconstruction are no-grad in the reference (compressors.py:98,163,270,296), so attention
+    output is a constant: the output projection learns, the q/k/v projections receive nothing."""
+    from turboquant_b200 import apply_turboquant
+    model, _ = _build(kind)
+    model = apply_turboquant(copy.deepcopy(model).cuda().to(torch.bfloat16), bits=3, seed=42).train()
+    ids = torch.randint(0, 512, (2, 32), generator=torch.Generator().manual_seed(3)).cuda()
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
+    out_w, in_w = (("c_proj", "c_attn") if kind == "gpt2" else ("o_proj", "q_proj"))
+    attn = next(m for m in model.modules() if hasattr(m, "key_compressor"))
+    before = getattr(attn, out_w).weight.detach().clone()
+    loss = model(input_ids=ids, labels=ids).loss
+    assert torch.isfinite(loss)
+    loss.backward()
+    g = getattr(attn, out_w).weight.grad
+    assert g is not None and torch.isfinite(g).all() and g.abs().sum() > 0
+    assert getattr(attn, in_w).weight.grad is None
+    opt.step()
+    assert not torch.equal(before, getattr(attn, out_w).weight.detach())
+    assert model.config.use_cache is False

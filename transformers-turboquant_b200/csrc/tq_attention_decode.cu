@@ -2,16 +2,23 @@
 // keys.  There is no counterpart in the reference, which disables the KV cache and recomputes full
 // attention per generated token (patch.py:80-81); this serves a cache kept in the library's wire format.
 //
-// The work is bound by the packed bytes (about 100 B per key at 3 bits), not by the contractions, so the
-// keys of one (batch, KV head) are split over `nsplit` CTAs and every CTA streams its range once:
-//   * a warp takes 16 keys at a time and decodes K_hat = [C[idx] ; (rn / n) sign] (the key norm n multiplies
-//     the finished score in fp32) STRAIGHT INTO the B
-//     fragments of mma.sync.m16n8k16 (bf16, fp32 accumulation) -- no shared-memory operand tile, each
-//     element is decoded exactly once by the lane that feeds it to the tensor core; the 16 query rows of
-//     the KV head (all its query heads x positions, zero-padded) are the A operand;
+// The work is bound by the packed bytes (about 100 B per key at 3 bits) and by the instructions that turn them
+// into tensor-core operands, not by the contractions, so the keys of one (batch, KV head) are split over
+// `nsplit` CTAs and every CTA streams its range once:
+//   * a warp takes 16 keys at a time and decodes K_hat = [C[idx] ; sign] STRAIGHT INTO the B fragments of
+//     mma.sync.m16n8k16 (bf16, fp32 accumulation) -- no shared-memory operand tile, each element is decoded
+//     exactly once by the lane that feeds it to the tensor core.  The contraction index of an MMA may be
+//     permuted freely as long as both operands agree, so a lane's four k-slots of a k-step are FOUR ADJACENT
+//     coordinates: one byte (3-bit mode) of the packed index row, or one nibble of the sign row, is one table
+//     look-up that returns both B registers, and the matching A registers are one 64-bit load of the staged
+//     query row.  The centroid half and the sign half accumulate separately and meet in fp32 as
+//     n <q Pi^T, C[idx]> + rn <q S^T, sign>, so the sign operand is exactly +-1;
 //   * online softmax on the C fragments (row maxima by two quad shuffles, running maximum raised lazily);
-//   * P (bf16, with the value norms folded in) is re-used as the A fragment of O += P V_hat, whose B
-//     fragments are decoded from the packed value indices the same way;
+//   * P (bf16, with the value norms folded in) is re-used as the A fragment of O += P V_hat.  The output
+//     column of an MMA may be permuted too: lane group gq owns coordinates 16 gq .. 16 gq + 15, which are
+//     contiguous bits of a packed value row; two adjacent indices are one look-up (a bf16 pair along the
+//     coordinate) and one byte permute per B register turns two keys' pairs into the pairs along the key
+//     that the fragment wants;
 //   * the four warps of a CTA merge through shared memory, the splits through a small fp32 workspace
 //     (`combine_kernel`), in the rotated output space; the caller rotates back.
 // The legacy tensor-core path is deliberate here: M = 16 rows do not fill a tcgen05 tile, and what has to
@@ -31,7 +38,9 @@ namespace {
 constexpr int kRows = 16;        // query rows per KV head (M of the MMA)
 constexpr int kWarps = 4;
 constexpr int kBlockKeys = 16;   // keys per warp iteration
-constexpr int kQPitch = 2 * 128 + 8;  // bf16 elements per staged query row (padded against bank conflicts)
+constexpr int kDecodeStages = 3; // packed-row buffers per warp: the block in use and the copies in flight
+constexpr int kQPitch = 2 * 128 + 16;  // bf16 elements per staged query row: rows 8 banks apart, so the
+                                        // 64-bit loads of a half warp (4 rows x 4 lanes) hit 32 different banks
 
 struct DecodeArgs {
   const __nv_bfloat16* q_cat;  // [B*Hq*Sq, 2d]
@@ -68,23 +77,6 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-// NBITS bits of a little-endian word array at bit offset 8 * BYTE + r, with BYTE known at compile time and
-// the run-time part r <= MAXR.  Stays inside one word when it can (one shift, one mask); otherwise takes the
-// four bytes starting at BYTE out of two neighbouring words with one byte permute first.
-template <int NW, int BYTE, int MAXR, int NBITS>
-__device__ __forceinline__ uint32_t field(const uint32_t (&w)[NW], int r) {
-  constexpr int word = BYTE / 4, bo = BYTE % 4;
-  constexpr uint32_t mask = (1u << NBITS) - 1;
-  static_assert(MAXR + NBITS <= 32, "field wider than a window");
-  if constexpr (8 * bo + MAXR + NBITS <= 32) {
-    return (w[word] >> (8 * bo + r)) & mask;
-  } else {
-    constexpr uint32_t sel = bo == 1 ? 0x4321u : bo == 2 ? 0x5432u : 0x6543u;
-    const uint32_t win = __byte_perm(w[word], w[word + 1 < NW ? word + 1 : word], sel);
-    return (win >> r) & mask;
-  }
-}
-
 // f(integral_constant<int, I>) for I = FROM .. TO-1: a loop whose index is usable as a template argument
 template <int FROM, int TO, class F>
 __device__ __forceinline__ void static_for(F&& f) {
@@ -98,28 +90,97 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src)
   const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
 }
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gmem_src) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(gmem_src) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait_all_but() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+// table look-ups by 32-bit shared address (the tables are written once, before the barrier that ends set-up,
+// and every address depends on packed data loaded after it)
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+  uint2 v;
+  asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+// (field << SH) for the NBITS-bit field at compile-time bit BIT of a little-endian word array: the byte offset of
+// entry `field` in a table whose entries are 2^SH bytes apart.  One shift and one mask; a funnel shift first
+// when the field straddles two words.
+template <int BIT, int NBITS, int SH, int NW>
+__device__ __forceinline__ uint32_t scaled_field(const uint32_t (&w)[NW]) {
+  constexpr int word = BIT / 32, bo = BIT % 32;
+  constexpr uint32_t mask = ((1u << NBITS) - 1) << SH;
+  static_assert(SH + NBITS <= 32 && word < NW, "field out of range");
+  if constexpr (bo + NBITS <= 32) {
+    if constexpr (bo > SH) return (w[word] >> (bo - SH)) & mask;
+    else if constexpr (bo < SH) return (w[word] << (SH - bo)) & mask;
+    else return w[word] & mask;
+  } else {
+    static_assert(bo + NBITS <= 32 || (bo >= SH && word + 1 < NW), "straddling field");
+    return __funnelshift_r(w[word], w[word + 1 < NW ? word + 1 : word], bo - SH) & mask;
+  }
+}
+
+// Shared-memory tables of the decode.  Every table is replicated so that the lanes of a warp read different
+// banks whatever their indices are (entry e, copy k at byte (e * COPIES + k) * ENTRY); the byte offset of a
+// look-up is `lane's copy | scaled_field`.
+template <int BITS>
+struct Tables {
+  static constexpr int KB = BITS - 1, VB = BITS;
+  // keys: four adjacent indices -> both B registers (8 bytes) while that table is small; at 3 bits per index
+  // two adjacent indices -> one register
+  static constexpr bool kQuad = KB <= 2;
+  static constexpr int kIdxBitsK = kQuad ? 4 * KB : 2 * KB;
+  static constexpr int kEntryK = kQuad ? 8 : 4;
+  static constexpr int kCopiesK = KB == 1 ? 16 : KB == 2 ? 4 : 32;
+  static constexpr int kShiftK = KB == 1 ? 7 : KB == 2 ? 5 : 7;  // log2(kEntryK * kCopiesK)
+  static constexpr int kBytesK = (1 << kIdxBitsK) * kEntryK * kCopiesK;
+  // values: two adjacent indices -> a bf16 pair along the coordinate
+  static constexpr int kCopiesV = VB == 4 ? 8 : 32;
+  static constexpr int kShiftV = VB == 4 ? 5 : 7;  // log2(4 * kCopiesV)
+  static constexpr int kBytesV = (1 << (2 * VB)) * 4 * kCopiesV;
+  static_assert((1 << kShiftK) == kEntryK * kCopiesK && (1 << kShiftV) == 4 * kCopiesV, "table strides");
+};
 
 template <int BITS>
 __global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a) {
+  using T = Tables<BITS>;
   constexpr int D = 128, KB = BITS - 1, VB = BITS;
-  constexpr int KW = 4 * KB, VW = 4 * VB;  // 32-bit words of one packed key / value index row
   constexpr float kLog2e = 1.4426950408889634f;
-  // packed bytes of the block a warp works on and of its next one (copied ahead with cp.async):
+  // packed bytes of the block a warp works on and of the ones after it (copied ahead with cp.async):
   // 16 key-index rows, 16 sign rows, 16 value-index rows
-  constexpr int kStageBytes = kBlockKeys * 16 * (KB + 1 + VB);
+  // + the fp16 norms of the 16 keys: key vector norms, residual norms, value vector norms (32 bytes each)
+  constexpr int kRowBytes = kBlockKeys * 16 * (KB + 1 + VB);
+  constexpr int kStageBytes = kRowBytes + 128;
+  constexpr int kStages = BITS == 4 ? 2 : kDecodeStages;
   constexpr int kQBytes = kRows * kQPitch * 2;
-  constexpr int kMergeBytes = kWarps * kRows * (D + 4) * 4;
-  constexpr int kLoopBytes = kQBytes + kWarps * 2 * kStageBytes;
-  // one pool: staged queries + packed-row stages while the keys stream, the warps' partial outputs afterwards
-  __shared__ __align__(16) uint8_t pool[kLoopBytes > kMergeBytes ? kLoopBytes : kMergeBytes];
-  __shared__ uint32_t lutK[1 << (2 * KB)];  // two key indices -> bf16x2 (C[i0], C[i1])
-  __shared__ uint32_t lutV[1 << VB];        // one value index -> bf16 in the low half
-  __shared__ float mrg_ml[kWarps][kRows][2];
+  constexpr int kMergeBytes = kWarps * 8 * (D + 4) * 4;  // eight rows at a time
+  constexpr int kLoopBytes = kQBytes + kWarps * kStages * kStageBytes;
+  // One shared array: the tables, the merge bookkeeping, then a pool: staged queries + packed-row stages while the keys stream, the warps'
+  // partial outputs afterwards.
+  constexpr int kOffK = 0, kOffV = T::kBytesK;
+  constexpr int kOffS = T::kBytesK + T::kBytesV;   // four adjacent sign bits -> (b0, b1), +-1 in bf16: 16 x 8 bytes
+  constexpr int kOffMl = kOffS + 128;              // [kWarps][kRows][2] floats
+  constexpr int kOffPool = kOffMl + kWarps * kRows * 2 * 4;
+  constexpr int kPoolBytes = kLoopBytes > kMergeBytes ? kLoopBytes : kMergeBytes;
+  static_assert(kOffPool % 16 == 0 && kOffPool + kPoolBytes <= 48 * 1024, "static shared memory");
+  __shared__ __align__(128) uint8_t smem[kOffPool + kPoolBytes];
+  uint8_t* lutK = smem + kOffK;
+  uint8_t* lutV = smem + kOffV;
+  uint2* lutS = reinterpret_cast<uint2*>(smem + kOffS);
+  float (*mrg_ml)[kRows][2] = reinterpret_cast<float (*)[kRows][2]>(smem + kOffMl);
+  uint8_t* pool = smem + kOffPool;
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(pool);
-  auto stage_ptr = [&](int w, int st) { return pool + kQBytes + (w * 2 + st) * kStageBytes; };
-  float (*mrg_o)[kRows][D + 4] = reinterpret_cast<float (*)[kRows][D + 4]>(pool);
+  auto stage_ptr = [&](int w, int st) { return pool + kQBytes + (w * kStages + st) * kStageBytes; };
+  float (*mrg_o)[8][D + 4] = reinterpret_cast<float (*)[8][D + 4]>(pool);
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int gq = lane / 4, tq = lane % 4;
@@ -129,28 +190,56 @@ __global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a)
   const int64_t kv_base = (b * a.Hkv + kvh) * a.Sk;
   const int shift = (int)(a.Sk - a.Sq);
 
-  // ---- stage the query rows (row r = g * Sq + s of query head kvh * G + g), centroid tables ----
+  // ---- stage the query rows (row r = g * Sq + s of query head kvh * G + g), build the tables ----
+  // Within each half of a row (rotated coordinates, sketch coordinates) coordinate 32 t + 4 j + e is stored at
+  // 16 j + 4 t + e: lane t of a quad owns coordinates 32 t .. 32 t + 31 (contiguous bits of a packed row), and
+  // its four coordinates of k-step j are one 64-bit load.
   for (int e = tid; e < kRows * (2 * D / 8); e += kWarps * 32) {
-    const int r = e / (2 * D / 8), c = e % (2 * D / 8);
+    const int r = e / (2 * D / 8), m = e % (2 * D / 8);
     uint4 v = make_uint4(0, 0, 0, 0);
     if (r < R) {
       const int64_t h = kvh * G + r / a.Sq, s = r % a.Sq;
-      v = reinterpret_cast<const uint4*>(a.q_cat + ((b * a.Hq + h) * a.Sq + s) * (2 * D))[c];
+      v = reinterpret_cast<const uint4*>(a.q_cat + ((b * a.Hq + h) * a.Sq + s) * (2 * D))[m];
     }
-    *reinterpret_cast<uint4*>(&q_s[r * kQPitch + c * 8]) = v;
+    const int half = m / 16, mm = m % 16;  // coordinates 8 mm .. 8 mm + 7 of the half: t = mm / 4, j = 2 (mm % 4), + 1
+    __nv_bfloat16* dst = &q_s[r * kQPitch + 128 * half + 32 * (mm % 4) + 4 * (mm / 4)];
+    *reinterpret_cast<uint2*>(dst) = make_uint2(v.x, v.y);
+    *reinterpret_cast<uint2*>(dst + 16) = make_uint2(v.z, v.w);
   }
-  for (int e = tid; e < (1 << (2 * KB)); e += kWarps * 32)
-    lutK[e] = bf16x2(a.cen_k[e & ((1 << KB) - 1)], a.cen_k[e >> KB]);
-  for (int e = tid; e < (1 << VB); e += kWarps * 32) lutV[e] = bf16x2(a.cen_v[e], 0.f);
+  {
+    constexpr uint32_t km = (1u << KB) - 1, vm = (1u << VB) - 1;
+    for (int e = tid; e < (1 << T::kIdxBitsK) * T::kCopiesK; e += kWarps * 32) {
+      const uint32_t i = e / T::kCopiesK;
+      uint32_t* dst = reinterpret_cast<uint32_t*>(lutK + e * T::kEntryK);
+      dst[0] = bf16x2(__ldg(a.cen_k + (i & km)), __ldg(a.cen_k + ((i >> KB) & km)));
+      if constexpr (T::kQuad) dst[1] = bf16x2(__ldg(a.cen_k + ((i >> (2 * KB)) & km)), __ldg(a.cen_k + ((i >> (3 * KB)) & km)));
+    }
+    for (int e = tid; e < (1 << (2 * VB)) * T::kCopiesV; e += kWarps * 32) {
+      const uint32_t i = e / T::kCopiesV;
+      reinterpret_cast<uint32_t*>(lutV)[e] = bf16x2(__ldg(a.cen_v + (i & vm)), __ldg(a.cen_v + (i >> VB)));
+    }
+    if (tid < 16) {  // a set bit is a positive sign
+      const uint32_t pos = 0x3f80u, neg = 0xbf80u;
+      lutS[tid] = make_uint2(((tid & 1) ? pos : neg) | (((tid & 2) ? pos : neg) << 16),
+                             ((tid & 4) ? pos : neg) | (((tid & 8) ? pos : neg) << 16));
+    }
+  }
   __syncthreads();
+  // a look-up address is (table address) + (lane's copy | entry): the first is a constant of the build that the
+  // load takes as its immediate, the second one three-input logic operation on the shifted packed word
+  const uint32_t lutK_base = smem_u32(lutK), lutV_base = smem_u32(lutV), lutS_base = smem_u32(lutS);
+  const uint32_t laneK = (uint32_t)((lane % T::kCopiesK) * T::kEntryK), laneV = (uint32_t)((lane % T::kCopiesV) * 4);
 
-  // per-lane row facts: this lane's C-fragment rows are gq and gq + 8
+  // Rows past R hold zero queries; their results are never read, so they are not masked.  Masking is needed
+  // only in blocks that reach past the first visible limit, which is the same for the whole warp.
   int row_lim[2];  // last visible key of the row (causal), or Sk - 1
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = gq + 8 * h;
-    row_lim[h] = (r < R) ? (a.causal ? (r % (int)a.Sq) + shift : (int)a.Sk - 1) : -1;
+    row_lim[h] = (r < R && a.causal) ? (r % (int)a.Sq) + shift : (int)a.Sk - 1;
   }
+  const int lim_min = a.causal ? shift : (int)a.Sk - 1;
+  const bool hi_rows = R > 8;  // else the A registers of rows 8..15 are zero and are not loaded
   const float cexp = a.sm_scale * kLog2e;
   float o[D / 8][4];
 #pragma unroll
@@ -161,118 +250,133 @@ __global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a)
 
   const int k_lo = split * a.keys_per_split;
   const int k_hi = min((int)a.Sk, k_lo + a.keys_per_split);
+  const uint8_t* kidx_base = a.key_idx + kv_base * (16 * KB);
+  const uint8_t* ksgn_base = a.key_sgn + kv_base * 16;
+  const uint8_t* vidx_base = a.val_idx + kv_base * (16 * VB);
+  // two adjacent fp16 norms are one 4-byte copy when that copy is aligned
+  const bool pair_ok = (kv_base & 1) == 0 && ((reinterpret_cast<uintptr_t>(a.key_vn) | reinterpret_cast<uintptr_t>(a.key_rn) |
+                                               reinterpret_cast<uintptr_t>(a.val_vn)) & 3) == 0;
+  const uint16_t* norm_src = (lane < 8 ? a.key_vn : lane < 16 ? a.key_rn : a.val_vn) + kv_base + 2 * (lane % 8);
   // copy the packed rows of keys [blk, blk + 16) into stage `st` (rows of consecutive keys are contiguous in
-  // each array); rows past the end of the sequence become zeros
+  // each array, 16 (KB + 1 + VB) = 32 BITS units of 16 bytes); rows past the end of the sequence become zeros
   auto stage = [&](int blk, int st) {
     uint8_t* dst = stage_ptr(warp, st);
-    constexpr int UK = kBlockKeys * KB, US = kBlockKeys, UV = kBlockKeys * VB;  // 16-byte units
-    for (int u = lane; u < UK + US + UV; u += 32) {
+    constexpr int UK = kBlockKeys * KB, US = kBlockKeys;  // 16-byte units of index and sign rows; value rows follow
+    const bool whole = blk + kBlockKeys <= (int)a.Sk;
+#pragma unroll
+    for (int it = 0; it < BITS; ++it) {
+      const int u = lane + 32 * it;
       const uint8_t* src;
       int key;
-      if (u < UK) { key = blk + u / KB; src = a.key_idx + (kv_base + blk) * (16 * KB) + 16 * u; }
-      else if (u < UK + US) { key = blk + (u - UK); src = a.key_sgn + (kv_base + blk) * 16 + 16 * (u - UK); }
-      else { key = blk + (u - UK - US) / VB; src = a.val_idx + (kv_base + blk) * (16 * VB) + 16 * (u - UK - US); }
-      if (key < a.Sk) cp_async16(dst + 16 * u, src);
+      if (u < UK) { key = blk + u / KB; src = kidx_base + (int64_t)blk * (16 * KB) + 16 * u; }
+      else if (u < UK + US) { key = blk + (u - UK); src = ksgn_base + (int64_t)blk * 16 + 16 * (u - UK); }
+      else { key = blk + (u - UK - US) / VB; src = vidx_base + (int64_t)blk * (16 * VB) + 16 * (u - UK - US); }
+      if (whole || key < a.Sk) cp_async16(dst + 16 * u, src);
       else *reinterpret_cast<uint4*>(dst + 16 * u) = make_uint4(0, 0, 0, 0);
     }
-  };
-  // fp16 norms this lane needs for a block: of the two keys it decodes (vector and residual norm) and of the
-  // four keys of its score / probability columns (key and value vector norms)
-  struct Norms { float nk[2], rn[2], kn[4], nv[4]; };
-  auto load_norms = [&](int blk, Norms& n) {
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-      const int key = blk + 8 * nt + gq;
-      n.nk[nt] = key < a.Sk ? fp16_value(a.key_vn[kv_base + key]) : 0.f;
-      n.rn[nt] = key < a.Sk ? fp16_value(a.key_rn[kv_base + key]) : 0.f;
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int key = blk + 8 * (i >> 1) + 2 * tq + (i & 1);
-      n.kn[i] = key < a.Sk ? fp16_value(a.key_vn[kv_base + key]) : 0.f;
-      n.nv[i] = key < a.Sk ? fp16_value(a.val_vn[kv_base + key]) : 0.f;
-    }
-  };
-  Norms cur, nxt;
-  const int blk0 = k_lo + kBlockKeys * warp;
-  if (blk0 < k_hi) {
-    stage(blk0, 0);
-    load_norms(blk0, cur);
-  }
-  cp_async_commit();
-  int st = 0;
-  for (int blk = blk0; blk < k_hi; blk += kBlockKeys * kWarps, st ^= 1) {
-    {
-      const int nb = blk + kBlockKeys * kWarps;
-      if (nb < k_hi) {
-        stage(nb, st ^ 1);
-        load_norms(nb, nxt);
+    // norms: lanes 0..23 copy one aligned pair of fp16 each; ragged or unaligned blocks go element by element
+    // (the block is used a later iteration, after a __syncwarp)
+    uint8_t* nd = dst + kRowBytes;
+    if (pair_ok && whole) {
+      if (lane < 24) cp_async4(nd + 4 * lane, norm_src + blk);
+    } else {
+      for (int u = lane; u < 3 * kBlockKeys; u += 32) {
+        const int arr = u / kBlockKeys, key = blk + u % kBlockKeys;
+        const uint16_t* src = arr == 0 ? a.key_vn : arr == 1 ? a.key_rn : a.val_vn;
+        reinterpret_cast<uint16_t*>(nd)[u] = key < a.Sk ? src[kv_base + key] : (uint16_t)0;
       }
+    }
+  };
+  // blocks of this warp: blk0, blk0 + 64, ...; their packed rows are copied kStages - 1 blocks ahead
+  const int blk0 = k_lo + kBlockKeys * warp;
+#pragma unroll
+  for (int s = 0; s < kStages - 1; ++s) {
+    const int pb = blk0 + s * kBlockKeys * kWarps;
+    if (pb < k_hi) stage(pb, s);
+    cp_async_commit();
+  }
+  int st = 0;
+  for (int blk = blk0; blk < k_hi; blk += kBlockKeys * kWarps, st = (st + 1 == kStages ? 0 : st + 1)) {
+    {
+      const int pb = blk + (kStages - 1) * kBlockKeys * kWarps;
+      if (pb < k_hi) stage(pb, st == 0 ? kStages - 1 : st - 1);  // the stage the previous iteration read
       cp_async_commit();
-      cp_async_wait_all_but_one();  // this block's rows have landed; the next block's may still be in flight
+      cp_async_wait_all_but<kStages - 1>();  // this block's rows have landed; later blocks' may still be in flight
       __syncwarp();
     }
     const uint8_t* stg = stage_ptr(warp, st);
-    // ================= scores: S[nt] (16 rows x 8 keys), nt = 0, 1 =================
-    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    // ================= scores: centroid half s1[nt], sign half s2[nt] (16 rows x 8 keys each) =================
+    float s1[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    float s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
     {
-      uint32_t kw[2][KW], sg[2][4], rr[2];
+      // this lane's share of keys blk + gq and blk + 8 + gq: the packed indices of coordinates 32 tq .. 32 tq + 31
+      // (4 KB bytes at byte 4 KB tq of the row) and the sign bits of the same sketch coordinates (word tq)
+      uint32_t kw[2][KB], sg[2][1];
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
-        const uint4* pi = reinterpret_cast<const uint4*>(stg + (8 * nt + gq) * (16 * KB));
+        const uint8_t* row = stg + (8 * nt + gq) * (16 * KB) + 4 * KB * tq;
+        if constexpr (KB == 2) {
+          const uint2 v = *reinterpret_cast<const uint2*>(row);
+          kw[nt][0] = v.x; kw[nt][1] = v.y;
+        } else {
 #pragma unroll
-        for (int i = 0; i < KB; ++i) {
-          const uint4 v = pi[i];
-          kw[nt][4 * i] = v.x; kw[nt][4 * i + 1] = v.y; kw[nt][4 * i + 2] = v.z; kw[nt][4 * i + 3] = v.w;
+          for (int i = 0; i < KB; ++i) kw[nt][i] = reinterpret_cast<const uint32_t*>(row)[i];
         }
-        const uint4 sv = *reinterpret_cast<const uint4*>(stg + kBlockKeys * 16 * KB + (8 * nt + gq) * 16);
-        sg[nt][0] = ~sv.x; sg[nt][1] = ~sv.y; sg[nt][2] = ~sv.z; sg[nt][3] = ~sv.w;  // set bit = negative
-        // the key norm multiplies the finished score in fp32 (below); the sketch half carries rn / n
-        const float rho = cur.nk[nt] > 0.f ? __fdividef(cur.rn[nt], cur.nk[nt]) : 0.f;
-        rr[nt] = bf16x2(rho, rho);
+        sg[nt][0] = reinterpret_cast<const uint32_t*>(stg + kBlockKeys * 16 * KB + (8 * nt + gq) * 16)[tq];
       }
       static_for<0, 16>([&](auto ks_c) {
-        constexpr int ks = decltype(ks_c)::value;
+        constexpr int ks = decltype(ks_c)::value, j = ks % 8;
+        // k-slots (2 tq, 2 tq + 1, 2 tq + 8, 2 tq + 9) of this k-step = coordinates 32 tq + 4 j .. + 3 of the half
         uint32_t qa[4];
-        qa[0] = *reinterpret_cast<const uint32_t*>(&q_s[gq * kQPitch + 16 * ks + 2 * tq]);
-        qa[1] = *reinterpret_cast<const uint32_t*>(&q_s[(gq + 8) * kQPitch + 16 * ks + 2 * tq]);
-        qa[2] = *reinterpret_cast<const uint32_t*>(&q_s[gq * kQPitch + 16 * ks + 8 + 2 * tq]);
-        qa[3] = *reinterpret_cast<const uint32_t*>(&q_s[(gq + 8) * kQPitch + 16 * ks + 8 + 2 * tq]);
+        const uint2 lo = *reinterpret_cast<const uint2*>(&q_s[gq * kQPitch + 16 * ks + 4 * tq]);
+        qa[0] = lo.x; qa[2] = lo.y;
+        qa[1] = 0; qa[3] = 0;
+        if (hi_rows) {
+          const uint2 hi = *reinterpret_cast<const uint2*>(&q_s[(gq + 8) * kQPitch + 16 * ks + 4 * tq]);
+          qa[1] = hi.x; qa[3] = hi.y;
+        }
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
-          uint32_t b0, b1;
-          if constexpr (ks < 8) {
-            // coordinates 16 ks + 2 tq, +1 (b0) and + 8, + 9 (b1): two adjacent indices = one table entry
-            // (the 16 indices of this k-step start at byte 2 KB ks; a pair is 2 KB bits wide)
-            const uint32_t p0 = field<KW, 2 * KB * ks, 6 * KB, 2 * KB>(kw[nt], 2 * KB * tq);
-            const uint32_t p1 = field<KW, 2 * KB * ks + KB, 6 * KB, 2 * KB>(kw[nt], 2 * KB * tq);
-            b0 = lutK[p0];
-            b1 = lutK[p1];
+          if constexpr (ks >= 8) {
+            const uint2 e = lds64(lutS_base + scaled_field<4 * j, 4, 3>(sg[nt]));
+            mma16816(s2[nt], qa, e.x, e.y);
+          } else if constexpr (T::kQuad) {
+            const uint2 e = lds64(lutK_base + (laneK | scaled_field<4 * KB * j, 4 * KB, T::kShiftK>(kw[nt])));
+            mma16816(s1[nt], qa, e.x, e.y);
           } else {
-            // sign bits of sketch coordinates 16 (ks - 8) + 2 tq, +1 and + 8, + 9
-            const uint32_t hw = sg[nt][(ks - 8) / 2] >> (16 * ((ks - 8) & 1));
-            b0 = rr[nt] ^ ((((hw >> (2 * tq)) & 3u) * 0x40008000u) & 0x80008000u);
-            b1 = rr[nt] ^ ((((hw >> (2 * tq + 8)) & 3u) * 0x40008000u) & 0x80008000u);
+            const uint32_t b0 = lds32(lutK_base + (laneK | scaled_field<4 * KB * j, 2 * KB, T::kShiftK>(kw[nt])));
+            const uint32_t b1 = lds32(lutK_base + (laneK | scaled_field<4 * KB * j + 2 * KB, 2 * KB, T::kShiftK>(kw[nt])));
+            mma16816(s1[nt], qa, b0, b1);
           }
-          mma16816(s[nt], qa, b0, b1);
         }
       });
     }
     // ================= online softmax on the fragments =================
     // s[nt][0..1]: row gq, keys blk + 8 nt + 2 tq, +1;  s[nt][2..3]: row gq + 8, same keys
+    // score * sm_scale * log2(e) = cexp (n <q Pi^T, C[idx]> + rn <q S^T, sign>), all in fp32
     float mx[2] = {-INFINITY, -INFINITY};
-    float kn[4];  // key norms (times the softmax scale) of this lane's score columns
+    {
+      // norms of this lane's score columns (keys blk + 8 nt + 2 tq, + 1), times the softmax scale
+      float kn[4], rn[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) kn[i] = cur.kn[i] * cexp;
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int key = blk + 8 * nt + 2 * tq + (i & 1), h = i >> 1;
-        const float x = (key <= row_lim[h] && key < k_hi) ? s[nt][i] * kn[2 * nt + (i & 1)] : -INFINITY;
-        s[nt][i] = x;
-        mx[h] = fmaxf(mx[h], x);
+      for (int nt = 0; nt < 2; ++nt) {
+        const float2 k2 = __half22float2(*reinterpret_cast<const __half2*>(stg + kRowBytes + 16 * nt + 4 * tq));
+        const float2 r2 = __half22float2(*reinterpret_cast<const __half2*>(stg + kRowBytes + 32 + 16 * nt + 4 * tq));
+        kn[2 * nt] = k2.x * cexp; kn[2 * nt + 1] = k2.y * cexp;
+        rn[2 * nt] = r2.x * cexp; rn[2 * nt + 1] = r2.y * cexp;
       }
+      const bool need_mask = blk + kBlockKeys - 1 > lim_min;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int c = 2 * nt + (i & 1), h = i >> 1;
+          float x = fmaf(s2[nt][i], rn[c], s1[nt][i] * kn[c]);
+          if (need_mask && blk + 8 * nt + 2 * tq + (i & 1) > row_lim[h]) x = -INFINITY;
+          s1[nt][i] = x;
+          mx[h] = fmaxf(mx[h], x);
+        }
+    }
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
@@ -297,15 +401,21 @@ __global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a)
     // P, with the value norms folded in for the MMA (the row sum uses the plain probabilities)
     uint32_t pa[4];
     {
-      float p[2][4];
+      float p[2][4], nv[4];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        const float2 v2 = __half22float2(*reinterpret_cast<const __half2*>(stg + kRowBytes + 64 + 16 * nt + 4 * tq));
+        nv[2 * nt] = v2.x; nv[2 * nt + 1] = v2.y;
+      }
+      const float mref[2] = {m_run[0] == -INFINITY ? 0.f : m_run[0], m_run[1] == -INFINITY ? 0.f : m_run[1]};
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int h = i >> 1;
-          const float pv = ex2(s[nt][i] - (m_run[h] == -INFINITY ? 0.f : m_run[h]));
+          const float pv = ex2(s1[nt][i] - mref[h]);
           l_run[h] += pv;
-          p[nt][i] = pv * cur.nv[2 * nt + (i & 1)];
+          p[nt][i] = pv * nv[2 * nt + (i & 1)];
         }
       pa[0] = bf16x2(p[0][0], p[0][1]);  // row gq,     keys 2 tq, +1
       pa[1] = bf16x2(p[0][2], p[0][3]);  // row gq + 8, keys 2 tq, +1
@@ -313,73 +423,82 @@ __global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a)
       pa[3] = bf16x2(p[1][2], p[1][3]);  // row gq + 8, keys 8 + 2 tq, +1
     }
     // ================= O += P V_hat =================
+    // Output column n of MMA tile ct is coordinate 16 n + ct, so lane group gq decodes coordinates
+    // 16 gq .. 16 gq + 15 of its four keys (blk + 2 tq, +1, + 8 + 2 tq, + 9 + 2 tq): 16 VB contiguous bits of a row.
     {
-      uint32_t vw[4][VW];  // packed value indices of keys blk + 2 tq, +1, + 8 + 2 tq, + 9 + 2 tq
+      uint32_t vw[4][2];
 #pragma unroll
       for (int kq = 0; kq < 4; ++kq) {
-        const uint4* pv = reinterpret_cast<const uint4*>(stg + kBlockKeys * 16 * (KB + 1) +
-                                                         (8 * (kq >> 1) + 2 * tq + (kq & 1)) * (16 * VB));
-#pragma unroll
-        for (int i = 0; i < VB; ++i) {
-          const uint4 v = pv[i];
-          vw[kq][4 * i] = v.x; vw[kq][4 * i + 1] = v.y; vw[kq][4 * i + 2] = v.z; vw[kq][4 * i + 3] = v.w;
+        const uint8_t* row = stg + kBlockKeys * 16 * (KB + 1) + (8 * (kq >> 1) + 2 * tq + (kq & 1)) * (16 * VB);
+        if constexpr (VB == 2) {
+          vw[kq][0] = reinterpret_cast<const uint32_t*>(row)[gq];
+          vw[kq][1] = 0;
+        } else if constexpr (VB == 4) {
+          const uint2 v = reinterpret_cast<const uint2*>(row)[gq];
+          vw[kq][0] = v.x;
+          vw[kq][1] = v.y;
+        } else {  // 6 bytes at byte 6 gq: two words, then 0 or 16 bits down
+          const uint32_t* w = reinterpret_cast<const uint32_t*>(row) + ((6 * gq) >> 2);
+          const uint32_t w0 = w[0], w1 = w[1], sh = 16 * (gq & 1);
+          vw[kq][0] = __funnelshift_r(w0, w1, sh);
+          vw[kq][1] = w1 >> sh;
         }
       }
-      static_for<0, D / 8>([&](auto ct_c) {
-        constexpr int ct = decltype(ct_c)::value;
-        // coordinate 8 ct + gq of the four keys
-        // (the 8 indices of this coordinate tile start at byte VB ct of the row)
+      static_for<0, D / 16>([&](auto c2_c) {
+        constexpr int ct = 2 * decltype(c2_c)::value;
+        // indices ct, ct + 1 of the lane's 16: one look-up per key gives the bf16 pair along the coordinate; the
+        // fragments want pairs along the key
         uint32_t e[4];
 #pragma unroll
-        for (int kq = 0; kq < 4; ++kq) e[kq] = lutV[field<VW, VB * ct, 7 * VB, VB>(vw[kq], VB * gq)];
-        const uint32_t b0 = __byte_perm(e[0], e[1], 0x5410), b1 = __byte_perm(e[2], e[3], 0x5410);
-        mma16816(o[ct], pa, b0, b1);
+        for (int kq = 0; kq < 4; ++kq) e[kq] = lds32(lutV_base + (laneV | scaled_field<VB * ct, 2 * VB, T::kShiftV>(vw[kq])));
+        mma16816(o[ct], pa, __byte_perm(e[0], e[1], 0x5410), __byte_perm(e[2], e[3], 0x5410));
+        mma16816(o[ct + 1], pa, __byte_perm(e[0], e[1], 0x7632), __byte_perm(e[2], e[3], 0x7632));
       });
     }
-    cur = nxt;
-    __syncwarp();  // every lane is done with this stage before the next iteration refills it
+    __syncwarp();  // every lane is done with this stage before a later iteration refills it
   }
 
   // ---- merge: lanes of a quad (row sums), the four warps, then this split's partial result ----
   asm volatile("cp.async.wait_group 0;" ::: "memory");
-  __syncthreads();  // the pool changes hands: every warp is done with the queries and its stages
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
     l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
   }
+  const int64_t unit = (b * a.Hkv + kvh) * a.nsplit + split;
+  // eight rows at a time (rows 8..15 only when some of them are real): the pool changes hands at each barrier
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
-    const int r = gq + 8 * h;
+    if (h == 1 && !hi_rows) break;
+    __syncthreads();  // every warp is done with the queries and its stages / with the previous eight rows
 #pragma unroll
-    for (int ct = 0; ct < D / 8; ++ct) {
-      mrg_o[warp][r][8 * ct + 2 * tq] = o[ct][2 * h];
-      mrg_o[warp][r][8 * ct + 2 * tq + 1] = o[ct][2 * h + 1];
+    for (int ct = 0; ct < D / 8; ++ct) {  // C-fragment columns 2 tq, 2 tq + 1 of tile ct
+      mrg_o[warp][gq][16 * (2 * tq) + ct] = o[ct][2 * h];
+      mrg_o[warp][gq][16 * (2 * tq + 1) + ct] = o[ct][2 * h + 1];
     }
     if (tq == 0) {
-      mrg_ml[warp][r][0] = m_run[h];
-      mrg_ml[warp][r][1] = l_run[h];
+      mrg_ml[warp][gq + 8 * h][0] = m_run[h];
+      mrg_ml[warp][gq + 8 * h][1] = l_run[h];
     }
-  }
-  __syncthreads();
-  const int64_t unit = (b * a.Hkv + kvh) * a.nsplit + split;
-  for (int e = tid; e < kRows * D; e += kWarps * 32) {
-    const int r = e / D, c = e % D;
-    float m = -INFINITY;
+    __syncthreads();
+    for (int e = tid; e < 8 * D; e += kWarps * 32) {
+      const int r8 = e / D, c = e % D, r = r8 + 8 * h;
+      float m = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < kWarps; ++w) m = fmaxf(m, mrg_ml[w][r][0]);
-    float acc = 0.f, l = 0.f;
+      for (int w = 0; w < kWarps; ++w) m = fmaxf(m, mrg_ml[w][r][0]);
+      float acc = 0.f, l = 0.f;
 #pragma unroll
-    for (int w = 0; w < kWarps; ++w) {
-      const float mw = mrg_ml[w][r][0];
-      const float f = (mw == -INFINITY) ? 0.f : ex2(mw - m);
-      acc = fmaf(mrg_o[w][r][c], f, acc);
-      l = fmaf(mrg_ml[w][r][1], f, l);
-    }
-    a.part_o[(unit * kRows + r) * D + c] = acc;
-    if (c == 0) {
-      a.part_ml[(unit * kRows + r) * 2] = m;
-      a.part_ml[(unit * kRows + r) * 2 + 1] = l;
+      for (int w = 0; w < kWarps; ++w) {
+        const float mw = mrg_ml[w][r][0];
+        const float f = (mw == -INFINITY) ? 0.f : ex2(mw - m);
+        acc = fmaf(mrg_o[w][r8][c], f, acc);
+        l = fmaf(mrg_ml[w][r][1], f, l);
+      }
+      a.part_o[(unit * kRows + r) * D + c] = acc;
+      if (c == 0) {
+        a.part_ml[(unit * kRows + r) * 2] = m;
+        a.part_ml[(unit * kRows + r) * 2 + 1] = l;
+      }
     }
   }
 }
@@ -425,24 +544,48 @@ bool decode_applies(const AttnArgs& a, int d) {
   return decode_enabled() && d == 128 && a.mask == nullptr && a.Hkv > 0 && (a.Hq / a.Hkv) * a.Sq <= kRows && a.Sk >= 4 * kBlockKeys * kWarps;
 }
 
-constexpr int64_t kMaxExtraUnits = 512;  // bound on (resident CTAs the splits are sized for): 3 per SM
+constexpr int64_t kMaxExtraUnits = 640;  // bound on the CTAs the splits are sized for (resident CTAs of the device)
 
 size_t decode_workspace_bytes(int64_t BHq) {
-  // at most (3 SM counts + B * Hkv) <= (512 + B * Hq) partial results of 16 rows x (128 + 2) floats
+  // at most (kMaxExtraUnits + B * Hkv) <= (kMaxExtraUnits + B * Hq) partial results of 16 rows x (128 + 2) floats
   return ((size_t)(kMaxExtraUnits + BHq) * kRows * (128 + 2) * sizeof(float) + 255) & ~(size_t)255;
+}
+
+// CTAs of decode_kernel<bits> that one SM holds (registers and shared memory decide)
+static int resident_ctas(int bits) {
+  static int cached[5] = {0, 0, 0, 0, 0};
+  if (cached[bits] == 0) {
+    int n = 0;
+    if (bits == 2) cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, decode_kernel<2>, kWarps * 32, 0);
+    else if (bits == 3) cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, decode_kernel<3>, kWarps * 32, 0);
+    else cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, decode_kernel<4>, kWarps * 32, 0);
+    cached[bits] = n > 0 ? n : 1;
+  }
+  return cached[bits];
 }
 
 int attention_decode(const AttnArgs& a, int64_t B, int bits, const void* q_cat, void* o_rot, void* part_ws,
                      cudaStream_t stream) {
   const int64_t units = B * a.Hkv;
-  // enough CTAs for three per SM (what registers allow to be resident), each with at least 64 keys (one
-  // 16-key block per warp)
-  int64_t want = 3 * (int64_t)sm_count();
-  if (want > kMaxExtraUnits) want = kMaxExtraUnits;
-  int nsplit = (int)(want / units);  // rounded down: one CTA too many would wait for a whole extra wave
-  const int max_split = (int)((a.Sk + kBlockKeys * kWarps - 1) / (kBlockKeys * kWarps));
-  if (nsplit > max_split) nsplit = max_split;
-  if (nsplit < 1) nsplit = 1;
+  // One wave of CTAs, each with at least 64 keys (one 16-key block per warp).  The SMs run their resident
+  // CTAs side by side and finish with the fullest one, so among the split counts that fit, take the one that
+  // fills the SMs most evenly (the largest such count: more warps per SM hide more latency).
+  const int64_t sms = sm_count();
+  int64_t slots = sms * resident_ctas(bits);
+  if (slots > kMaxExtraUnits) slots = kMaxExtraUnits;
+  int64_t n_max = slots / units;
+  const int64_t max_split = (a.Sk + kBlockKeys * kWarps - 1) / (kBlockKeys * kWarps);
+  if (n_max > max_split) n_max = max_split;
+  int nsplit = 1;
+  double best = 0.0;
+  for (int64_t n = 1; n <= n_max; ++n) {
+    const int64_t ctas = units * n, per_sm = (ctas + sms - 1) / sms;
+    const double fill = (double)ctas / (double)(per_sm * sms);
+    if (fill >= best - 1e-9) {
+      best = fill;
+      nsplit = (int)n;
+    }
+  }
   TQ_REQUIRE(units * nsplit <= kMaxExtraUnits + B * a.Hq, "partial-result workspace too small for %d splits", nsplit);
   int per = (int)((a.Sk + nsplit - 1) / nsplit);
   per = (per + kBlockKeys * kWarps - 1) / (kBlockKeys * kWarps) * (kBlockKeys * kWarps);
