@@ -70,6 +70,13 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// 8x8 transpose of 16-bit elements across the warp: lane (g, t) gives row g, columns 2 t, 2 t + 1 and receives
+// column g, rows 2 t, 2 t + 1
+__device__ __forceinline__ uint32_t transpose8x8(uint32_t v) {
+  uint32_t r;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(v));
+  return r;
+}
 // D (16x8, fp32) += A (16x16, bf16, row) * B (16x8, bf16, col)
 __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -150,9 +157,10 @@ struct Tables {
   static_assert((1 << kShiftK) == kEntryK * kCopiesK && (1 << kShiftV) == 4 * kCopiesV, "table strides");
 };
 
-template <int BITS>
+template <int BITS, int NT>
 __global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a) {
   using T = Tables<BITS>;
+  constexpr bool kQInRegs = NT == 1;
   constexpr int D = 128, KB = BITS - 1, VB = BITS;
   constexpr float kLog2e = 1.4426950408889634f;
   // packed bytes of the block a warp works on and of the ones after it (copied ahead with cp.async):
@@ -230,23 +238,42 @@ __global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a)
   const uint32_t lutK_base = smem_u32(lutK), lutV_base = smem_u32(lutV), lutS_base = smem_u32(lutS);
   const uint32_t laneK = (uint32_t)((lane % T::kCopiesK) * T::kEntryK), laneV = (uint32_t)((lane % T::kCopiesV) * 4);
 
-  // Rows past R hold zero queries; their results are never read, so they are not masked.  Masking is needed
-  // only in blocks that reach past the first visible limit, which is the same for the whole warp.
-  int row_lim[2];  // last visible key of the row (causal), or Sk - 1
+  // Query rows are the N dimension of every MMA (tiles of 8): NT = 1 serves up to 8 rows, NT = 2 up to 16.  Rows
+  // past R hold zero queries; their results are never read, so they are not masked.  Masking is needed only in
+  // blocks that reach past the first visible limit, which is the same for the whole warp.
+  // This lane's columns of the score / output fragments are query rows 8 t + 2 tq + e, e = 0, 1.
+  int row_lim[NT][2];  // last visible key of the row (causal), or Sk - 1
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const int r = gq + 8 * h;
-    row_lim[h] = (r < R && a.causal) ? (r % (int)a.Sq) + shift : (int)a.Sk - 1;
-  }
+  for (int t = 0; t < NT; ++t)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int r = 8 * t + 2 * tq + e;
+      row_lim[t][e] = (r < R && a.causal) ? (r % (int)a.Sq) + shift : (int)a.Sk - 1;
+    }
   const int lim_min = a.causal ? shift : (int)a.Sk - 1;
-  const bool hi_rows = R > 8;  // else the A registers of rows 8..15 are zero and are not loaded
   const float cexp = a.sm_scale * kLog2e;
-  float o[D / 8][4];
+  // O^T fragments: o[t][ct][i] is coordinate 16 gq + 2 ct + (i >> 1) of query row 8 t + 2 tq + (i & 1)
+  float o[NT][D / 16][4];
 #pragma unroll
-  for (int ct = 0; ct < D / 8; ++ct)
+  for (int t = 0; t < NT; ++t)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) o[ct][i] = 0.f;
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    for (int ct = 0; ct < D / 16; ++ct)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o[t][ct][i] = 0.f;
+  float m_run[NT][2], l_run[NT][2];  // l_run: this lane's keys only until the end
+#pragma unroll
+  for (int t = 0; t < NT; ++t)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      m_run[t][e] = -INFINITY;
+      l_run[t][e] = 0.f;
+    }
+  // B fragments of Q^T (k-slots of k-step ks x query row gq of tile t): kept in registers when one tile is all
+  uint2 qr[kQInRegs ? 16 : 1];
+  if constexpr (kQInRegs) {
+#pragma unroll
+    for (int ks = 0; ks < 16; ++ks) qr[ks] = *reinterpret_cast<const uint2*>(&q_s[gq * kQPitch + 16 * ks + 4 * tq]);
+  }
 
   const int k_lo = split * a.keys_per_split;
   const int k_hi = min((int)a.Sk, k_lo + a.keys_per_split);
@@ -305,126 +332,138 @@ __global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a)
       __syncwarp();
     }
     const uint8_t* stg = stage_ptr(warp, st);
-    // ================= scores: centroid half s1[nt], sign half s2[nt] (16 rows x 8 keys each) =================
-    float s1[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-    float s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    // ============ scores, transposed: S^T (16 keys x 8 query rows per tile); centroid half s1, sign half s2 ============
+    float s1[NT][4], s2[NT][4];
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        s1[t][i] = 0.f;
+        s2[t][i] = 0.f;
+      }
     {
-      // this lane's share of keys blk + gq and blk + 8 + gq: the packed indices of coordinates 32 tq .. 32 tq + 31
-      // (4 KB bytes at byte 4 KB tq of the row) and the sign bits of the same sketch coordinates (word tq)
+      // this lane's share of keys blk + gq and blk + 8 + gq (rows gq, gq + 8 of the A operand): the packed indices
+      // of coordinates 32 tq .. 32 tq + 31 (4 KB bytes at byte 4 KB tq of the row) and the sign bits of the same
+      // sketch coordinates (word tq)
       uint32_t kw[2][KB], sg[2][1];
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt) {
-        const uint8_t* row = stg + (8 * nt + gq) * (16 * KB) + 4 * KB * tq;
+      for (int h = 0; h < 2; ++h) {
+        const uint8_t* row = stg + (8 * h + gq) * (16 * KB) + 4 * KB * tq;
         if constexpr (KB == 2) {
           const uint2 v = *reinterpret_cast<const uint2*>(row);
-          kw[nt][0] = v.x; kw[nt][1] = v.y;
+          kw[h][0] = v.x; kw[h][1] = v.y;
         } else {
 #pragma unroll
-          for (int i = 0; i < KB; ++i) kw[nt][i] = reinterpret_cast<const uint32_t*>(row)[i];
+          for (int i = 0; i < KB; ++i) kw[h][i] = reinterpret_cast<const uint32_t*>(row)[i];
         }
-        sg[nt][0] = reinterpret_cast<const uint32_t*>(stg + kBlockKeys * 16 * KB + (8 * nt + gq) * 16)[tq];
+        sg[h][0] = reinterpret_cast<const uint32_t*>(stg + kBlockKeys * 16 * KB + (8 * h + gq) * 16)[tq];
       }
       static_for<0, 16>([&](auto ks_c) {
         constexpr int ks = decltype(ks_c)::value, j = ks % 8;
-        // k-slots (2 tq, 2 tq + 1, 2 tq + 8, 2 tq + 9) of this k-step = coordinates 32 tq + 4 j .. + 3 of the half
-        uint32_t qa[4];
-        const uint2 lo = *reinterpret_cast<const uint2*>(&q_s[gq * kQPitch + 16 * ks + 4 * tq]);
-        qa[0] = lo.x; qa[2] = lo.y;
-        qa[1] = 0; qa[3] = 0;
-        if (hi_rows) {
-          const uint2 hi = *reinterpret_cast<const uint2*>(&q_s[(gq + 8) * kQPitch + 16 * ks + 4 * tq]);
-          qa[1] = hi.x; qa[3] = hi.y;
+        // k-slots (2 tq, 2 tq + 1, 2 tq + 8, 2 tq + 9) of this k-step = coordinates 32 tq + 4 j .. + 3 of the half;
+        // A registers: a0 / a2 = row gq, first / second slot pair; a1 / a3 = row gq + 8
+        uint32_t ka[4];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if constexpr (ks >= 8) {
+            const uint2 e = lds64(lutS_base + scaled_field<4 * j, 4, 3>(sg[h]));
+            ka[h] = e.x; ka[2 + h] = e.y;
+          } else if constexpr (T::kQuad) {
+            const uint2 e = lds64(lutK_base + (laneK | scaled_field<4 * KB * j, 4 * KB, T::kShiftK>(kw[h])));
+            ka[h] = e.x; ka[2 + h] = e.y;
+          } else {
+            ka[h] = lds32(lutK_base + (laneK | scaled_field<4 * KB * j, 2 * KB, T::kShiftK>(kw[h])));
+            ka[2 + h] = lds32(lutK_base + (laneK | scaled_field<4 * KB * j + 2 * KB, 2 * KB, T::kShiftK>(kw[h])));
+          }
         }
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-          if constexpr (ks >= 8) {
-            const uint2 e = lds64(lutS_base + scaled_field<4 * j, 4, 3>(sg[nt]));
-            mma16816(s2[nt], qa, e.x, e.y);
-          } else if constexpr (T::kQuad) {
-            const uint2 e = lds64(lutK_base + (laneK | scaled_field<4 * KB * j, 4 * KB, T::kShiftK>(kw[nt])));
-            mma16816(s1[nt], qa, e.x, e.y);
-          } else {
-            const uint32_t b0 = lds32(lutK_base + (laneK | scaled_field<4 * KB * j, 2 * KB, T::kShiftK>(kw[nt])));
-            const uint32_t b1 = lds32(lutK_base + (laneK | scaled_field<4 * KB * j + 2 * KB, 2 * KB, T::kShiftK>(kw[nt])));
-            mma16816(s1[nt], qa, b0, b1);
-          }
+        for (int t = 0; t < NT; ++t) {
+          uint2 qb;
+          if constexpr (kQInRegs) qb = qr[ks];
+          else qb = *reinterpret_cast<const uint2*>(&q_s[(8 * t + gq) * kQPitch + 16 * ks + 4 * tq]);
+          if constexpr (ks >= 8) mma16816(s2[t], ka, qb.x, qb.y);
+          else mma16816(s1[t], ka, qb.x, qb.y);
         }
       });
     }
     // ================= online softmax on the fragments =================
-    // s[nt][0..1]: row gq, keys blk + 8 nt + 2 tq, +1;  s[nt][2..3]: row gq + 8, same keys
+    // s[t][i]: key blk + gq + 8 (i >> 1), query row 8 t + 2 tq + (i & 1)
     // score * sm_scale * log2(e) = cexp (n <q Pi^T, C[idx]> + rn <q S^T, sign>), all in fp32
-    float mx[2] = {-INFINITY, -INFINITY};
+    const uint16_t* nrm = reinterpret_cast<const uint16_t*>(stg + kRowBytes);  // [3][16] fp16: n, rn, value n
+    float mx[NT][2];
     {
-      // norms of this lane's score columns (keys blk + 8 nt + 2 tq, + 1), times the softmax scale
-      float kn[4], rn[4];
+      float kn[2], rn[2];
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt) {
-        const float2 k2 = __half22float2(*reinterpret_cast<const __half2*>(stg + kRowBytes + 16 * nt + 4 * tq));
-        const float2 r2 = __half22float2(*reinterpret_cast<const __half2*>(stg + kRowBytes + 32 + 16 * nt + 4 * tq));
-        kn[2 * nt] = k2.x * cexp; kn[2 * nt + 1] = k2.y * cexp;
-        rn[2 * nt] = r2.x * cexp; rn[2 * nt + 1] = r2.y * cexp;
+      for (int h = 0; h < 2; ++h) {
+        kn[h] = fp16_value(nrm[gq + 8 * h]) * cexp;
+        rn[h] = fp16_value(nrm[16 + gq + 8 * h]) * cexp;
       }
       const bool need_mask = blk + kBlockKeys - 1 > lim_min;
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
+      for (int t = 0; t < NT; ++t) {
+        mx[t][0] = -INFINITY;
+        mx[t][1] = -INFINITY;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const int c = 2 * nt + (i & 1), h = i >> 1;
-          float x = fmaf(s2[nt][i], rn[c], s1[nt][i] * kn[c]);
-          if (need_mask && blk + 8 * nt + 2 * tq + (i & 1) > row_lim[h]) x = -INFINITY;
-          s1[nt][i] = x;
-          mx[h] = fmaxf(mx[h], x);
+          const int h = i >> 1, e = i & 1;
+          float x = fmaf(s2[t][i], rn[h], s1[t][i] * kn[h]);
+          if (need_mask && blk + gq + 8 * h > row_lim[t][e]) x = -INFINITY;
+          s1[t][i] = x;
+          mx[t][e] = fmaxf(mx[t][e], x);
         }
+      }
     }
+    bool grow_lane = false;
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
-      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-    }
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {  // the 16 keys of a query row sit in the 8 lane groups
+        mx[t][e] = fmaxf(mx[t][e], __shfl_xor_sync(0xffffffffu, mx[t][e], 4));
+        mx[t][e] = fmaxf(mx[t][e], __shfl_xor_sync(0xffffffffu, mx[t][e], 8));
+        mx[t][e] = fmaxf(mx[t][e], __shfl_xor_sync(0xffffffffu, mx[t][e], 16));
+        grow_lane |= mx[t][e] > m_run[t][e] + 8.f;
+      }
     // running maximum raised lazily (only when some row of the warp outgrew it by 2^8)
-    const bool grow = __any_sync(0xffffffffu, mx[0] > m_run[0] + 8.f || mx[1] > m_run[1] + 8.f);
-    if (grow) {
+    if (__any_sync(0xffffffffu, grow_lane)) {
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const float m_new = fmaxf(m_run[h], mx[h]);
-        const float alpha = (m_run[h] == -INFINITY) ? 0.f : ex2(m_run[h] - m_new);
-        m_run[h] = m_new;
-        l_run[h] *= alpha;
+      for (int t = 0; t < NT; ++t)
 #pragma unroll
-        for (int ct = 0; ct < D / 8; ++ct) {
-          o[ct][2 * h] *= alpha;
-          o[ct][2 * h + 1] *= alpha;
+        for (int e = 0; e < 2; ++e) {
+          const float m_new = fmaxf(m_run[t][e], mx[t][e]);
+          const float alpha = (m_run[t][e] == -INFINITY) ? 0.f : ex2(m_run[t][e] - m_new);
+          m_run[t][e] = m_new;
+          l_run[t][e] *= alpha;
+#pragma unroll
+          for (int ct = 0; ct < D / 16; ++ct) {
+            o[t][ct][e] *= alpha;
+            o[t][ct][2 + e] *= alpha;
+          }
         }
-      }
     }
-    // P, with the value norms folded in for the MMA (the row sum uses the plain probabilities)
-    uint32_t pa[4];
+    // P^T, with the value norms folded in for the MMA (the row sum uses the plain probabilities).  The C fragment
+    // of S^T (key rows, query columns) becomes the B fragment of the next MMA (key k-slots, query column gq) by
+    // one 8x8 transpose across the warp per eight keys.
+    uint32_t pb[NT][2];
     {
-      float p[2][4], nv[4];
+      const float nv[2] = {fp16_value(nrm[32 + gq]), fp16_value(nrm[32 + gq + 8])};
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt) {
-        const float2 v2 = __half22float2(*reinterpret_cast<const __half2*>(stg + kRowBytes + 64 + 16 * nt + 4 * tq));
-        nv[2 * nt] = v2.x; nv[2 * nt + 1] = v2.y;
-      }
-      const float mref[2] = {m_run[0] == -INFINITY ? 0.f : m_run[0], m_run[1] == -INFINITY ? 0.f : m_run[1]};
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
+      for (int t = 0; t < NT; ++t) {
+        float p[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const int h = i >> 1;
-          const float pv = ex2(s1[nt][i] - mref[h]);
-          l_run[h] += pv;
-          p[nt][i] = pv * nv[2 * nt + (i & 1)];
+          const int h = i >> 1, e = i & 1;
+          const float pv = ex2(s1[t][i] - (m_run[t][e] == -INFINITY ? 0.f : m_run[t][e]));
+          l_run[t][e] += pv;
+          p[i] = pv * nv[h];
         }
-      pa[0] = bf16x2(p[0][0], p[0][1]);  // row gq,     keys 2 tq, +1
-      pa[1] = bf16x2(p[0][2], p[0][3]);  // row gq + 8, keys 2 tq, +1
-      pa[2] = bf16x2(p[1][0], p[1][1]);  // row gq,     keys 8 + 2 tq, +1
-      pa[3] = bf16x2(p[1][2], p[1][3]);  // row gq + 8, keys 8 + 2 tq, +1
+        pb[t][0] = transpose8x8(bf16x2(p[0], p[1]));  // keys blk + 2 tq, + 1       of query row 8 t + gq
+        pb[t][1] = transpose8x8(bf16x2(p[2], p[3]));  // keys blk + 8 + 2 tq, + 1   of query row 8 t + gq
+      }
     }
-    // ================= O += P V_hat =================
-    // Output column n of MMA tile ct is coordinate 16 n + ct, so lane group gq decodes coordinates
-    // 16 gq .. 16 gq + 15 of its four keys (blk + 2 tq, +1, + 8 + 2 tq, + 9 + 2 tq): 16 VB contiguous bits of a row.
+    // ================= O^T += V_hat^T P^T =================
+    // Row m of MMA tile ct is any coordinate we like: lane group gq owns coordinates 16 gq .. 16 gq + 15
+    // (16 VB contiguous bits of a packed row), tile ct takes 16 gq + 2 ct (row gq) and 16 gq + 2 ct + 1 (row gq + 8).
+    // The k-slots are this lane's four keys blk + 2 tq, + 1, + 8 + 2 tq, + 9 + 2 tq.
     {
       uint32_t vw[4][2];
 #pragma unroll
@@ -444,45 +483,52 @@ __global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a)
           vw[kq][1] = w1 >> sh;
         }
       }
-      static_for<0, D / 16>([&](auto c2_c) {
-        constexpr int ct = 2 * decltype(c2_c)::value;
-        // indices ct, ct + 1 of the lane's 16: one look-up per key gives the bf16 pair along the coordinate; the
-        // fragments want pairs along the key
+      static_for<0, D / 16>([&](auto ct_c) {
+        constexpr int ct = decltype(ct_c)::value;
+        // indices 2 ct, 2 ct + 1 of the lane's 16: one look-up per key gives the bf16 pair along the coordinate; the
+        // fragment wants pairs along the key
         uint32_t e[4];
 #pragma unroll
-        for (int kq = 0; kq < 4; ++kq) e[kq] = lds32(lutV_base + (laneV | scaled_field<VB * ct, 2 * VB, T::kShiftV>(vw[kq])));
-        mma16816(o[ct], pa, __byte_perm(e[0], e[1], 0x5410), __byte_perm(e[2], e[3], 0x5410));
-        mma16816(o[ct + 1], pa, __byte_perm(e[0], e[1], 0x7632), __byte_perm(e[2], e[3], 0x7632));
+        for (int kq = 0; kq < 4; ++kq)
+          e[kq] = lds32(lutV_base + (laneV | scaled_field<2 * VB * ct, 2 * VB, T::kShiftV>(vw[kq])));
+        const uint32_t va[4] = {__byte_perm(e[0], e[1], 0x5410), __byte_perm(e[0], e[1], 0x7632),
+                                __byte_perm(e[2], e[3], 0x5410), __byte_perm(e[2], e[3], 0x7632)};
+#pragma unroll
+        for (int t = 0; t < NT; ++t) mma16816(o[t][ct], va, pb[t][0], pb[t][1]);
       });
     }
     __syncwarp();  // every lane is done with this stage before a later iteration refills it
   }
 
-  // ---- merge: lanes of a quad (row sums), the four warps, then this split's partial result ----
+  // ---- merge: lane groups (row sums), the four warps, then this split's partial result ----
   asm volatile("cp.async.wait_group 0;" ::: "memory");
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
-    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
-  }
-  const int64_t unit = (b * a.Hkv + kvh) * a.nsplit + split;
-  // eight rows at a time (rows 8..15 only when some of them are real): the pool changes hands at each barrier
+  for (int t = 0; t < NT; ++t)
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    if (h == 1 && !hi_rows) break;
+    for (int e = 0; e < 2; ++e) {
+      l_run[t][e] += __shfl_xor_sync(0xffffffffu, l_run[t][e], 4);
+      l_run[t][e] += __shfl_xor_sync(0xffffffffu, l_run[t][e], 8);
+      l_run[t][e] += __shfl_xor_sync(0xffffffffu, l_run[t][e], 16);
+    }
+  const int64_t unit = (b * a.Hkv + kvh) * a.nsplit + split;
+  // eight query rows (one tile) at a time: the pool changes hands at each barrier
+#pragma unroll
+  for (int t = 0; t < NT; ++t) {
     __syncthreads();  // every warp is done with the queries and its stages / with the previous eight rows
 #pragma unroll
-    for (int ct = 0; ct < D / 8; ++ct) {  // C-fragment columns 2 tq, 2 tq + 1 of tile ct
-      mrg_o[warp][gq][16 * (2 * tq) + ct] = o[ct][2 * h];
-      mrg_o[warp][gq][16 * (2 * tq + 1) + ct] = o[ct][2 * h + 1];
-    }
-    if (tq == 0) {
-      mrg_ml[warp][gq + 8 * h][0] = m_run[h];
-      mrg_ml[warp][gq + 8 * h][1] = l_run[h];
+    for (int ct = 0; ct < D / 16; ++ct)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) mrg_o[warp][2 * tq + (i & 1)][16 * gq + 2 * ct + (i >> 1)] = o[t][ct][i];
+    if (gq == 0) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        mrg_ml[warp][8 * t + 2 * tq + e][0] = m_run[t][e];
+        mrg_ml[warp][8 * t + 2 * tq + e][1] = l_run[t][e];
+      }
     }
     __syncthreads();
     for (int e = tid; e < 8 * D; e += kWarps * 32) {
-      const int r8 = e / D, c = e % D, r = r8 + 8 * h;
+      const int r8 = e / D, c = e % D, r = r8 + 8 * t;
       float m = -INFINITY;
 #pragma unroll
       for (int w = 0; w < kWarps; ++w) m = fmaxf(m, mrg_ml[w][r][0]);
@@ -551,17 +597,20 @@ size_t decode_workspace_bytes(int64_t BHq) {
   return ((size_t)(kMaxExtraUnits + BHq) * kRows * (128 + 2) * sizeof(float) + 255) & ~(size_t)255;
 }
 
-// CTAs of decode_kernel<bits> that one SM holds (registers and shared memory decide)
-static int resident_ctas(int bits) {
-  static int cached[5] = {0, 0, 0, 0, 0};
-  if (cached[bits] == 0) {
-    int n = 0;
-    if (bits == 2) cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, decode_kernel<2>, kWarps * 32, 0);
-    else if (bits == 3) cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, decode_kernel<3>, kWarps * 32, 0);
-    else cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, decode_kernel<4>, kWarps * 32, 0);
-    cached[bits] = n > 0 ? n : 1;
+// CTAs of decode_kernel<bits, nt> that one SM holds (registers and shared memory decide)
+template <int BITS, int NT>
+static int occupancy_of() {
+  int n = 0;
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, decode_kernel<BITS, NT>, kWarps * 32, 0);
+  return n > 0 ? n : 1;
+}
+static int resident_ctas(int bits, int nt) {
+  static int cached[5][3] = {};
+  if (cached[bits][nt] == 0) {
+    if (nt == 1) cached[bits][nt] = bits == 2 ? occupancy_of<2, 1>() : bits == 3 ? occupancy_of<3, 1>() : occupancy_of<4, 1>();
+    else cached[bits][nt] = bits == 2 ? occupancy_of<2, 2>() : bits == 3 ? occupancy_of<3, 2>() : occupancy_of<4, 2>();
   }
-  return cached[bits];
+  return cached[bits][nt];
 }
 
 int attention_decode(const AttnArgs& a, int64_t B, int bits, const void* q_cat, void* o_rot, void* part_ws,
@@ -571,7 +620,8 @@ int attention_decode(const AttnArgs& a, int64_t B, int bits, const void* q_cat, 
   // CTAs side by side and finish with the fullest one, so among the split counts that fit, take the one that
   // fills the SMs most evenly (the largest such count: more warps per SM hide more latency).
   const int64_t sms = sm_count();
-  int64_t slots = sms * resident_ctas(bits);
+  const int nt = (a.Hq / a.Hkv) * a.Sq > 8 ? 2 : 1;  // tiles of eight query rows
+  int64_t slots = sms * resident_ctas(bits, nt);
   if (slots > kMaxExtraUnits) slots = kMaxExtraUnits;
   int64_t n_max = slots / units;
   const int64_t max_split = (a.Sk + kBlockKeys * kWarps - 1) / (kBlockKeys * kWarps);
@@ -597,9 +647,16 @@ int attention_decode(const AttnArgs& a, int64_t B, int bits, const void* q_cat, 
   dim3 grid((unsigned)nsplit, (unsigned)a.Hkv, (unsigned)B);
   {
     ProfScope prof(kProfAttention, stream);
-    if (bits == 2) decode_kernel<2><<<grid, kWarps * 32, 0, stream>>>(da);
-    else if (bits == 3) decode_kernel<3><<<grid, kWarps * 32, 0, stream>>>(da);
-    else decode_kernel<4><<<grid, kWarps * 32, 0, stream>>>(da);
+    const unsigned threads = kWarps * 32;
+    if (nt == 1) {
+      if (bits == 2) decode_kernel<2, 1><<<grid, threads, 0, stream>>>(da);
+      else if (bits == 3) decode_kernel<3, 1><<<grid, threads, 0, stream>>>(da);
+      else decode_kernel<4, 1><<<grid, threads, 0, stream>>>(da);
+    } else {
+      if (bits == 2) decode_kernel<2, 2><<<grid, threads, 0, stream>>>(da);
+      else if (bits == 3) decode_kernel<3, 2><<<grid, threads, 0, stream>>>(da);
+      else decode_kernel<4, 2><<<grid, threads, 0, stream>>>(da);
+    }
     TQ_CUDA_OK(cudaGetLastError());
     combine_kernel<<<(unsigned)units, 128, 0, stream>>>(part_o, part_ml, nsplit, a.Hq, a.Hkv, a.Sq,
                                                         static_cast<__nv_bfloat16*>(o_rot));
