@@ -108,14 +108,14 @@ __device__ __forceinline__ void cp_async_wait_all_but() { asm volatile("cp.async
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 // table look-ups by 32-bit shared address (the tables are written once, before the barrier that ends set-up,
 // and every address depends on packed data loaded after it)
-__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
-  uint32_t v;
-  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-  return v;
-}
 __device__ __forceinline__ uint2 lds64(uint32_t addr) {
   uint2 v;
   asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
   return v;
 }
 // (field << SH) for the NBITS-bit field at compile-time bit BIT of a little-endian word array: the byte offset of
@@ -142,14 +142,17 @@ __device__ __forceinline__ uint32_t scaled_field(const uint32_t (&w)[NW]) {
 template <int BITS>
 struct Tables {
   static constexpr int KB = BITS - 1, VB = BITS;
-  // keys: four adjacent indices -> both B registers (8 bytes) while that table is small; at 3 bits per index
-  // two adjacent indices -> one register
-  static constexpr bool kQuad = KB <= 2;
-  static constexpr int kIdxBitsK = kQuad ? 4 * KB : 2 * KB;
-  static constexpr int kEntryK = kQuad ? 8 : 4;
-  static constexpr int kCopiesK = KB == 1 ? 16 : KB == 2 ? 4 : 32;
-  static constexpr int kShiftK = KB == 1 ? 7 : KB == 2 ? 5 : 7;  // log2(kEntryK * kCopiesK)
+  // keys: two adjacent indices -> one operand register (a bf16 pair along the coordinate), one copy per lane.
+  // (A wider entry, four indices -> two registers by one 64-bit load, costs more than it saves: with the few
+  // copies that fit its loads collide, and its register pair has to be moved apart for the MMA.)
+  static constexpr int kIdxBitsK = 2 * KB;
+  static constexpr int kEntryK = 4;
+  static constexpr int kCopiesK = 32;
+  static constexpr int kShiftK = 7;  // log2(kEntryK * kCopiesK)
   static constexpr int kBytesK = (1 << kIdxBitsK) * kEntryK * kCopiesK;
+  // signs: four adjacent sign bits -> two registers of +-1 pairs by one 64-bit load; the 16 entries cover the
+  // 32 banks exactly once, so no copies are needed
+  static constexpr int kBytesS = 16 * 8;
   // values: two adjacent indices -> a bf16 pair along the coordinate
   static constexpr int kCopiesV = VB == 4 ? 8 : 32;
   static constexpr int kShiftV = VB == 4 ? 5 : 7;  // log2(4 * kCopiesV)
@@ -175,15 +178,15 @@ __global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a)
   // One shared array: the tables, the merge bookkeeping, then a pool: staged queries + packed-row stages while the keys stream, the warps'
   // partial outputs afterwards.
   constexpr int kOffK = 0, kOffV = T::kBytesK;
-  constexpr int kOffS = T::kBytesK + T::kBytesV;   // four adjacent sign bits -> (b0, b1), +-1 in bf16: 16 x 8 bytes
-  constexpr int kOffMl = kOffS + 128;              // [kWarps][kRows][2] floats
+  constexpr int kOffS = T::kBytesK + T::kBytesV;
+  constexpr int kOffMl = kOffS + T::kBytesS;       // [kWarps][kRows][2] floats
   constexpr int kOffPool = kOffMl + kWarps * kRows * 2 * 4;
   constexpr int kPoolBytes = kLoopBytes > kMergeBytes ? kLoopBytes : kMergeBytes;
   static_assert(kOffPool % 16 == 0 && kOffPool + kPoolBytes <= 48 * 1024, "static shared memory");
   __shared__ __align__(128) uint8_t smem[kOffPool + kPoolBytes];
   uint8_t* lutK = smem + kOffK;
   uint8_t* lutV = smem + kOffV;
-  uint2* lutS = reinterpret_cast<uint2*>(smem + kOffS);
+  uint8_t* lutS = smem + kOffS;
   float (*mrg_ml)[kRows][2] = reinterpret_cast<float (*)[kRows][2]>(smem + kOffMl);
   uint8_t* pool = smem + kOffPool;
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(pool);
@@ -218,9 +221,7 @@ __global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a)
     constexpr uint32_t km = (1u << KB) - 1, vm = (1u << VB) - 1;
     for (int e = tid; e < (1 << T::kIdxBitsK) * T::kCopiesK; e += kWarps * 32) {
       const uint32_t i = e / T::kCopiesK;
-      uint32_t* dst = reinterpret_cast<uint32_t*>(lutK + e * T::kEntryK);
-      dst[0] = bf16x2(__ldg(a.cen_k + (i & km)), __ldg(a.cen_k + ((i >> KB) & km)));
-      if constexpr (T::kQuad) dst[1] = bf16x2(__ldg(a.cen_k + ((i >> (2 * KB)) & km)), __ldg(a.cen_k + ((i >> (3 * KB)) & km)));
+      reinterpret_cast<uint32_t*>(lutK)[e] = bf16x2(__ldg(a.cen_k + (i & km)), __ldg(a.cen_k + (i >> KB)));
     }
     for (int e = tid; e < (1 << (2 * VB)) * T::kCopiesV; e += kWarps * 32) {
       const uint32_t i = e / T::kCopiesV;
@@ -228,15 +229,15 @@ __global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a)
     }
     if (tid < 16) {  // a set bit is a positive sign
       const uint32_t pos = 0x3f80u, neg = 0xbf80u;
-      lutS[tid] = make_uint2(((tid & 1) ? pos : neg) | (((tid & 2) ? pos : neg) << 16),
-                             ((tid & 4) ? pos : neg) | (((tid & 8) ? pos : neg) << 16));
+      reinterpret_cast<uint2*>(lutS)[tid] = make_uint2(((tid & 1) ? pos : neg) | (((tid & 2) ? pos : neg) << 16),
+                                                       ((tid & 4) ? pos : neg) | (((tid & 8) ? pos : neg) << 16));
     }
   }
   __syncthreads();
   // a look-up address is (table address) + (lane's copy | entry): the first is a constant of the build that the
   // load takes as its immediate, the second one three-input logic operation on the shifted packed word
   const uint32_t lutK_base = smem_u32(lutK), lutV_base = smem_u32(lutV), lutS_base = smem_u32(lutS);
-  const uint32_t laneK = (uint32_t)((lane % T::kCopiesK) * T::kEntryK), laneV = (uint32_t)((lane % T::kCopiesV) * 4);
+  const uint32_t lane4 = (uint32_t)(lane * 4), laneV = (uint32_t)((lane % T::kCopiesV) * 4);
 
   // Query rows are the N dimension of every MMA (tiles of 8): NT = 1 serves up to 8 rows, NT = 2 up to 16.  Rows
   // past R hold zero queries; their results are never read, so they are not masked.  Masking is needed only in
@@ -286,20 +287,26 @@ __global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a)
   const uint16_t* norm_src = (lane < 8 ? a.key_vn : lane < 16 ? a.key_rn : a.val_vn) + kv_base + 2 * (lane % 8);
   // copy the packed rows of keys [blk, blk + 16) into stage `st` (rows of consecutive keys are contiguous in
   // each array, 16 (KB + 1 + VB) = 32 BITS units of 16 bytes); rows past the end of the sequence become zeros
+  // unit u = lane + 32 it of a stage (it < BITS) is 16 bytes of one array: where it starts for block 0, how far
+  // it moves per key, and which key of the block it belongs to
+  const uint8_t* unit_src[BITS];
+  int unit_step[BITS], unit_key[BITS];
+#pragma unroll
+  for (int it = 0; it < BITS; ++it) {
+    constexpr int UK = kBlockKeys * KB, US = kBlockKeys;  // 16-byte units of index and sign rows; value rows follow
+    const int u = lane + 32 * it;
+    if (u < UK) { unit_src[it] = kidx_base + 16 * u; unit_step[it] = 16 * KB; unit_key[it] = u / KB; }
+    else if (u < UK + US) { unit_src[it] = ksgn_base + 16 * (u - UK); unit_step[it] = 16; unit_key[it] = u - UK; }
+    else { unit_src[it] = vidx_base + 16 * (u - UK - US); unit_step[it] = 16 * VB; unit_key[it] = (u - UK - US) / VB; }
+  }
   auto stage = [&](int blk, int st) {
     uint8_t* dst = stage_ptr(warp, st);
-    constexpr int UK = kBlockKeys * KB, US = kBlockKeys;  // 16-byte units of index and sign rows; value rows follow
     const bool whole = blk + kBlockKeys <= (int)a.Sk;
 #pragma unroll
     for (int it = 0; it < BITS; ++it) {
-      const int u = lane + 32 * it;
-      const uint8_t* src;
-      int key;
-      if (u < UK) { key = blk + u / KB; src = kidx_base + (int64_t)blk * (16 * KB) + 16 * u; }
-      else if (u < UK + US) { key = blk + (u - UK); src = ksgn_base + (int64_t)blk * 16 + 16 * (u - UK); }
-      else { key = blk + (u - UK - US) / VB; src = vidx_base + (int64_t)blk * (16 * VB) + 16 * (u - UK - US); }
-      if (whole || key < a.Sk) cp_async16(dst + 16 * u, src);
-      else *reinterpret_cast<uint4*>(dst + 16 * u) = make_uint4(0, 0, 0, 0);
+      uint8_t* d = dst + 16 * (lane + 32 * it);
+      if (whole || blk + unit_key[it] < a.Sk) cp_async16(d, unit_src[it] + (int64_t)blk * unit_step[it]);
+      else *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
     }
     // norms: lanes 0..23 copy one aligned pair of fp16 each; ragged or unaligned blocks go element by element
     // (the block is used a later iteration, after a __syncwarp)
@@ -368,12 +375,9 @@ __global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a)
           if constexpr (ks >= 8) {
             const uint2 e = lds64(lutS_base + scaled_field<4 * j, 4, 3>(sg[h]));
             ka[h] = e.x; ka[2 + h] = e.y;
-          } else if constexpr (T::kQuad) {
-            const uint2 e = lds64(lutK_base + (laneK | scaled_field<4 * KB * j, 4 * KB, T::kShiftK>(kw[h])));
-            ka[h] = e.x; ka[2 + h] = e.y;
           } else {
-            ka[h] = lds32(lutK_base + (laneK | scaled_field<4 * KB * j, 2 * KB, T::kShiftK>(kw[h])));
-            ka[2 + h] = lds32(lutK_base + (laneK | scaled_field<4 * KB * j + 2 * KB, 2 * KB, T::kShiftK>(kw[h])));
+            ka[h] = lds32(lutK_base + (lane4 | scaled_field<4 * KB * j, 2 * KB, T::kShiftK>(kw[h])));
+            ka[2 + h] = lds32(lutK_base + (lane4 | scaled_field<4 * KB * j + 2 * KB, 2 * KB, T::kShiftK>(kw[h])));
           }
         }
 #pragma unroll
