@@ -354,8 +354,10 @@ def run_decode(args):
             "clocks": clocks, "gpu_launches": int(sum(launches)),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "traffic": None,
-                         "kernel": "decode_kernel + combine_kernel", "ms_per_launch": kern_ms,
+                         "kernel": "decode_kernel", "ms_per_launch": kern_ms,
                          "peak_source": peaks["source"]},
+            "kernel_ms": {"prepare_queries": ms_sum[2] / max(launches[2], 1), "decode": kern_ms,
+                          "merge_and_back_rotation": ms_sum[4] / max(launches[4], 1)},
             "device_wait_faults": tq.device_fault_count(dev), "output_norm": float(out.float().norm())}
     print(json.dumps(line), flush=True)
 

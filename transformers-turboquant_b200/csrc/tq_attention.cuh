@@ -43,12 +43,13 @@ int attention_fwd_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_t 
 
 size_t workspace_bytes_bf16(int64_t BHq, int64_t Sq, int d);
 
-// Split-KV kernel for decode-sized calls (few query rows per KV head, long keys; tq_attention_decode.cu):
-// q_cat bf16 [n_q, 2d] in, rotated outputs bf16 [n_q, d] out, `part_ws` of decode_workspace_bytes(B * Hq).
+// Decode-sized calls (few query rows per KV head, long keys; tq_attention_decode.cu), three launches: query
+// preparation into `q_cat` (bf16 [n_q, 2d]), the split-KV kernel, then merge + back-rotation into a.out.
+// `part_ws` holds decode_workspace_bytes(B * Hq).
 bool decode_applies(const AttnArgs& a, int d);
 size_t decode_workspace_bytes(int64_t BHq);
-int attention_decode(const AttnArgs& a, int64_t B, int bits, const void* q_cat, void* o_rot, void* part_ws,
-                     cudaStream_t stream);
+int attention_decode(const AttnArgs& a, int64_t B, int bits, const void* q, int q_dtype, int64_t sb, int64_t sh,
+                     int64_t ss, const float* Pi_k, const float* S_eff, void* q_cat, void* part_ws, cudaStream_t stream);
 
 // Raw queries and the constant bf16 operands of the SM-pair kernel, which prepares its own query tile
 // (q [Pi ; coeff S]^T) and rotates its output back (o Pi_v) on the tensor pipe.

@@ -38,6 +38,7 @@ namespace {
 constexpr int kRows = 16;        // query rows per KV head (M of the MMA)
 constexpr int kWarps = 4;
 constexpr int kBlockKeys = 16;   // keys per warp iteration
+constexpr int kMaxExtraUnits = 640;  // bound on the CTAs the splits are sized for (resident CTAs of the device)
 constexpr int kDecodeStages = 3; // packed-row buffers per warp: the block in use and the copies in flight
 constexpr int kQPitch = 2 * 128 + 16;  // bf16 elements per staged query row: rows 8 banks apart, so the
                                         // 64-bit loads of a half warp (4 rows x 4 lanes) hit 32 different banks
@@ -553,28 +554,108 @@ __global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a)
   }
 }
 
-// out_rot[row of (b, h, s)][c] = sum_splits O_s 2^(m_s - m) / sum_splits l_s 2^(m_s - m), bf16
-__global__ void __launch_bounds__(128) combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                                      int nsplit, int64_t Hq, int64_t Hkv, int64_t Sq,
-                                                      __nv_bfloat16* __restrict__ o_rot) {
+__device__ __forceinline__ float load_elem(const void* base, int dtype, int64_t off) {
+  if (dtype == TQ_F32) return static_cast<const float*>(base)[off];
+  if (dtype == TQ_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(base)[off]);
+  return __half2float(static_cast<const __half*>(base)[off]);
+}
+__device__ __forceinline__ void store_elem(void* base, int dtype, int64_t off, float v) {
+  if (dtype == TQ_F32) static_cast<float*>(base)[off] = v;
+  else if (dtype == TQ_BF16) static_cast<__nv_bfloat16*>(base)[off] = __float2bfloat16_rn(v);
+  else static_cast<__half*>(base)[off] = __float2half_rn(v);
+}
+
+// q_cat rows of one (batch, KV head): [q_rot | coeff q_rot S_eff^T] with q_rot = q Pi_k^T (the residual sketch
+// lives in rotated coordinates), fp32 arithmetic on the fp32 matrices, rounded to bf16 once.  A decode-sized
+// call has a few hundred query rows at most, which is no work for a tensor-core tile pipeline: one CTA per
+// (batch, KV head); a warp takes four matrix rows (coalesced 512-byte loads, all in flight at once) and reduces
+// each dot product across its lanes.
+__global__ void __launch_bounds__(1024) decode_prepare_kernel(const void* __restrict__ q, int dtype, int64_t sb, int64_t sh,
+                                                              int64_t ss, int64_t Hq, int64_t Hkv, int64_t Sq,
+                                                              const float* __restrict__ Pi_k, const float* __restrict__ S_eff,
+                                                              float coeff, __nv_bfloat16* __restrict__ q_cat) {
   constexpr int D = 128;
-  const int64_t unit = blockIdx.x;  // b * Hkv + kvh
-  const int64_t b = unit / Hkv, kvh = unit % Hkv;
+  __shared__ __align__(16) float buf[3][kRows][D];  // raw queries, rotated queries, sketch projections
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  const int64_t b = blockIdx.x / Hkv, kvh = blockIdx.x % Hkv;
   const int G = (int)(Hq / Hkv), R = G * (int)Sq;
-  const int c = threadIdx.x;
-  for (int r = 0; r < R; ++r) {
-    float m = -INFINITY;
-    for (int s = 0; s < nsplit; ++s) m = fmaxf(m, part_ml[((unit * nsplit + s) * kRows + r) * 2]);
-    float acc = 0.f, l = 0.f;
-    for (int s = 0; s < nsplit; ++s) {
-      const int64_t u = (unit * nsplit + s) * kRows + r;
-      const float ms = part_ml[u * 2];
-      const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
-      acc = fmaf(part_o[u * D + c], f, acc);
-      l = fmaf(part_ml[u * 2 + 1], f, l);
+  for (int e = tid; e < R * D; e += 1024) {
+    const int r = e / D, c = e % D;
+    buf[0][r][c] = load_elem(q, dtype, b * sb + (kvh * G + r / Sq) * sh + (r % Sq) * ss + c);
+  }
+#pragma unroll
+  for (int stage = 0; stage < 2; ++stage) {
+    const float* W = stage == 0 ? Pi_k : S_eff;
+    float4 w[4];
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj) w[jj] = __ldg(reinterpret_cast<const float4*>(W + (int64_t)(4 * warp + jj) * D) + lane);
+    __syncthreads();  // the stage's input rows are complete
+    for (int r = 0; r < R; ++r) {
+      const float4 x = *reinterpret_cast<const float4*>(&buf[stage][r][4 * lane]);
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        float p = fmaf(w[jj].x, x.x, fmaf(w[jj].y, x.y, fmaf(w[jj].z, x.z, w[jj].w * x.w)));
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) p += __shfl_xor_sync(0xffffffffu, p, d);
+        if (lane == jj) buf[stage + 1][r][4 * warp + jj] = p;
+      }
     }
-    const int64_t h = kvh * G + r / Sq, s = r % Sq;
-    o_rot[((b * Hq + h) * Sq + s) * D + c] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+  }
+  __syncthreads();
+  for (int e = tid; e < R * 2 * D; e += 1024) {
+    const int r = e / (2 * D), c = e % (2 * D);
+    const int64_t row = (b * Hq + kvh * G + r / Sq) * Sq + r % Sq;
+    const float v = c < D ? buf[1][r][c] : coeff * buf[2][r][c - D];
+    q_cat[row * (2 * D) + c] = __float2bfloat16_rn(v);
+  }
+}
+
+// One query row per CTA: merge the splits (O = sum_s O_s 2^(m_s - m) / sum_s l_s 2^(m_s - m)), rotate back
+// (out = O Pi_v) and store in the caller's dtype and strides; fp32 throughout.  512 threads = 128 output
+// columns x 4 parts of each sum, so that every thread has all its loads in flight at once.
+__global__ void __launch_bounds__(512) decode_finish_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                                            int nsplit, int64_t Hq, int64_t Hkv, int64_t Sq,
+                                                            const float* __restrict__ Pi_v, void* __restrict__ out,
+                                                            int out_dtype, int64_t osb, int64_t osh, int64_t oss) {
+  constexpr int D = 128;
+  __shared__ float f_s[kMaxExtraUnits + 1];
+  __shared__ float part[4][D];
+  __shared__ float o_s[D];
+  const int tid = threadIdx.x, lane = tid % 32, j = tid % D, p = tid / D;
+  const int r = blockIdx.x;
+  const int64_t unit = blockIdx.y, b = unit / Hkv, kvh = unit % Hkv;
+  const int G = (int)(Hq / Hkv);
+  const float* ml = part_ml + (unit * nsplit * kRows + r) * 2;  // split s: ml[s * kRows * 2], + 1
+  // every warp finds the maximum and the total weight by itself; warp 0 also publishes the factors
+  float m = -INFINITY;
+  for (int s = lane; s < nsplit; s += 32) m = fmaxf(m, ml[(int64_t)s * kRows * 2]);
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+  float l = 0.f;
+  for (int s = lane; s < nsplit; s += 32) {
+    const float ms = ml[(int64_t)s * kRows * 2];
+    const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
+    if (tid < 32) f_s[s] = f;
+    l = fmaf(ml[(int64_t)s * kRows * 2 + 1], f, l);
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) l += __shfl_xor_sync(0xffffffffu, l, d);
+  __syncthreads();
+  float acc = 0.f;
+#pragma unroll 4
+  for (int s = p; s < nsplit; s += 4) acc = fmaf(part_o[((unit * nsplit + s) * kRows + r) * D + j], f_s[s], acc);
+  part[p][j] = acc;
+  __syncthreads();
+  if (tid < D) o_s[tid] = l > 0.f ? (part[0][tid] + part[1][tid] + part[2][tid] + part[3][tid]) / l : 0.f;
+  __syncthreads();
+  float y = 0.f;
+#pragma unroll
+  for (int c = 0; c < D / 4; ++c) y = fmaf(o_s[32 * p + c], __ldg(Pi_v + (32 * p + c) * D + j), y);
+  part[p][j] = y;
+  __syncthreads();
+  if (tid < D) {
+    const int64_t h = kvh * G + r / Sq, sq = r % Sq;
+    store_elem(out, out_dtype, b * osb + h * osh + sq * oss + tid, part[0][tid] + part[1][tid] + part[2][tid] + part[3][tid]);
   }
 }
 
@@ -594,7 +675,6 @@ bool decode_applies(const AttnArgs& a, int d) {
   return decode_enabled() && d == 128 && a.mask == nullptr && a.Hkv > 0 && (a.Hq / a.Hkv) * a.Sq <= kRows && a.Sk >= 4 * kBlockKeys * kWarps;
 }
 
-constexpr int64_t kMaxExtraUnits = 640;  // bound on the CTAs the splits are sized for (resident CTAs of the device)
 
 size_t decode_workspace_bytes(int64_t BHq) {
   // at most (kMaxExtraUnits + B * Hkv) <= (kMaxExtraUnits + B * Hq) partial results of 16 rows x (128 + 2) floats
@@ -617,14 +697,22 @@ static int resident_ctas(int bits, int nt) {
   return cached[bits][nt];
 }
 
-int attention_decode(const AttnArgs& a, int64_t B, int bits, const void* q_cat, void* o_rot, void* part_ws,
-                     cudaStream_t stream) {
+int attention_decode(const AttnArgs& a, int64_t B, int bits, const void* q, int q_dtype, int64_t sb, int64_t sh,
+                     int64_t ss, const float* Pi_k, const float* S_eff, void* q_cat, void* part_ws, cudaStream_t stream) {
   const int64_t units = B * a.Hkv;
+  const int R = (int)((a.Hq / a.Hkv) * a.Sq);
+  {
+    ProfScope prof(kProfPrepareQueries, stream);
+    decode_prepare_kernel<<<(unsigned)units, 1024, 0, stream>>>(q, q_dtype, sb, sh, ss, a.Hq, a.Hkv, a.Sq, Pi_k, S_eff,
+                                                               sqrtf(1.5707963267948966f) / 128.f,
+                                                               static_cast<__nv_bfloat16*>(q_cat));
+    TQ_CUDA_OK(cudaGetLastError());
+  }
   // One wave of CTAs, each with at least 64 keys (one 16-key block per warp).  The SMs run their resident
   // CTAs side by side and finish with the fullest one, so among the split counts that fit, take the one that
   // fills the SMs most evenly (the largest such count: more warps per SM hide more latency).
   const int64_t sms = sm_count();
-  const int nt = (a.Hq / a.Hkv) * a.Sq > 8 ? 2 : 1;  // tiles of eight query rows
+  const int nt = R > 8 ? 2 : 1;  // tiles of eight query rows
   int64_t slots = sms * resident_ctas(bits, nt);
   if (slots > kMaxExtraUnits) slots = kMaxExtraUnits;
   int64_t n_max = slots / units;
@@ -662,9 +750,10 @@ int attention_decode(const AttnArgs& a, int64_t B, int bits, const void* q_cat, 
       else decode_kernel<4, 2><<<grid, threads, 0, stream>>>(da);
     }
     TQ_CUDA_OK(cudaGetLastError());
-    combine_kernel<<<(unsigned)units, 128, 0, stream>>>(part_o, part_ml, nsplit, a.Hq, a.Hkv, a.Sq,
-                                                        static_cast<__nv_bfloat16*>(o_rot));
   }
+  ProfScope prof(kProfBackRotation, stream);
+  decode_finish_kernel<<<dim3((unsigned)R, (unsigned)units), 512, 0, stream>>>(
+      part_o, part_ml, nsplit, a.Hq, a.Hkv, a.Sq, a.Pi_v, a.out, a.out_dtype, a.o_stride_b, a.o_stride_h, a.o_stride_s);
   TQ_CUDA_OK(cudaGetLastError());
   return TQ_OK;
 }

@@ -840,6 +840,9 @@ int attention_fwd_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_t 
 
   const bool decode = decode_applies(a, d) && Sq <= 16;
   const bool pairs = d == 128 && use_sm_pairs() && !decode;
+  if (decode)  // its own small kernels on both sides of the split-KV kernel; none of the bf16 operand images
+    return attention_decode(a, B, bits, q, dtype, sb, sh, ss, Pi_k, S_eff, q_cat,
+                            reinterpret_cast<uint8_t*>(o_rot) + round256((size_t)n_q * d * 2), stream);
   build_wunrot_kernel<<<d, d, 0, stream>>>(a.Pi_v, d, w_unrot, pairs ? d / 2 : 0);
   TQ_CUDA_OK(cudaGetLastError());
   if (pairs) {
@@ -857,10 +860,7 @@ int attention_fwd_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_t 
 
   a.q_cat = q_cat;
   int st;
-  if (decode)
-    st = attention_decode(a, B, bits, q_cat, o_rot, reinterpret_cast<uint8_t*>(o_rot) + round256((size_t)n_q * d * 2),
-                          stream);
-  else if (d == 128)
+  if (d == 128)
     st = bits == 2   ? launch_attention_tc<128, 2>(a, B, o_rot, stream)
          : bits == 3 ? launch_attention_tc<128, 3>(a, B, o_rot, stream)
                      : launch_attention_tc<128, 4>(a, B, o_rot, stream);
