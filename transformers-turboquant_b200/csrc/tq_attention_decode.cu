@@ -2,27 +2,36 @@
 // keys.  There is no counterpart in the reference, which disables the KV cache and recomputes full
 // attention per generated token (patch.py:80-81); this serves a cache kept in the library's wire format.
 //
+// Three launches per call: `decode_prepare_kernel` (q_cat = [q Pi^T | coeff q Pi^T S^T], fp32), `decode_kernel`
+// (below) and `decode_finish_kernel` (merge of the splits + back-rotation by Pi_v, fp32).
+//
 // The work is bound by the packed bytes (about 100 B per key at 3 bits) and by the instructions that turn them
 // into tensor-core operands, not by the contractions, so the keys of one (batch, KV head) are split over
-// `nsplit` CTAs and every CTA streams its range once:
-//   * a warp takes 16 keys at a time and decodes K_hat = [C[idx] ; sign] STRAIGHT INTO the B fragments of
-//     mma.sync.m16n8k16 (bf16, fp32 accumulation) -- no shared-memory operand tile, each element is decoded
-//     exactly once by the lane that feeds it to the tensor core.  The contraction index of an MMA may be
-//     permuted freely as long as both operands agree, so a lane's four k-slots of a k-step are FOUR ADJACENT
-//     coordinates: one byte (3-bit mode) of the packed index row, or one nibble of the sign row, is one table
-//     look-up that returns both B registers, and the matching A registers are one 64-bit load of the staged
-//     query row.  The centroid half and the sign half accumulate separately and meet in fp32 as
+// `nsplit` CTAs and every CTA streams its range once (packed rows and fp16 norms copied three blocks ahead
+// with cp.async):
+//   * everything is computed TRANSPOSED, so that the few query rows are the N = 8 dimension of
+//     mma.sync.m16n8k16 (bf16, fp32 accumulation) and the long dimensions fill M = 16:
+//     S^T (16 keys x 8 query rows) = K_hat Q^T and O^T (16 coordinates x 8 query rows) += V_hat^T P^T.
+//     One tile of eight query rows (NT = 1) keeps its Q^T fragments in registers; 9..16 rows take two tiles;
+//   * a warp takes 16 keys at a time and decodes K_hat = [C[idx] ; sign] STRAIGHT INTO the A fragments -- no
+//     shared-memory operand tile, each element is decoded exactly once by the lane that feeds it to the tensor
+//     core.  The contraction index of an MMA may be permuted freely as long as both operands agree, so lane t of
+//     a quad owns coordinates 32 t .. 32 t + 31 of its two keys (contiguous bits of a packed row, one or two
+//     words) and its four k-slots of k-step j are coordinates 32 t + 4 j .. + 3: two adjacent indices are one
+//     look-up in a per-lane copy of a bf16-pair table (no bank conflicts), four adjacent sign bits one 64-bit
+//     look-up.  The centroid half and the sign half accumulate separately and meet in fp32 as
 //     n <q Pi^T, C[idx]> + rn <q S^T, sign>, so the sign operand is exactly +-1;
-//   * online softmax on the C fragments (row maxima by two quad shuffles, running maximum raised lazily);
-//   * P (bf16, with the value norms folded in) is re-used as the A fragment of O += P V_hat.  The output
-//     column of an MMA may be permuted too: lane group gq owns coordinates 16 gq .. 16 gq + 15, which are
+//   * online softmax on the C fragments (maxima over the keys by three shuffles across the lane groups,
+//     running maximum raised lazily);
+//   * P^T (bf16, with the value norms folded in) becomes the B fragment of the second MMA by one 8x8
+//     transpose across the warp (movmatrix) per eight keys;
+//   * the row index of the second MMA may be permuted too: lane group g owns coordinates 16 g .. 16 g + 15,
 //     contiguous bits of a packed value row; two adjacent indices are one look-up (a bf16 pair along the
-//     coordinate) and one byte permute per B register turns two keys' pairs into the pairs along the key
-//     that the fragment wants;
-//   * the four warps of a CTA merge through shared memory, the splits through a small fp32 workspace
-//     (`combine_kernel`), in the rotated output space; the caller rotates back.
-// The legacy tensor-core path is deliberate here: M = 16 rows do not fill a tcgen05 tile, and what has to
-// be fast is the decode around the MMA, not the MMA.
+//     coordinate) and a byte permute per A register turns two keys' pairs into the pairs along the key that
+//     the fragment wants;
+//   * the four warps of a CTA merge through shared memory, the splits through a small fp32 workspace.
+// The legacy tensor-core path is deliberate here: eight or sixteen query rows do not fill a tcgen05 tile, and
+// what has to be fast is the decode around the MMA, not the MMA.
 #include <math.h>
 #include <stdlib.h>
 
@@ -35,7 +44,7 @@
 namespace tq {
 namespace {
 
-constexpr int kRows = 16;        // query rows per KV head (M of the MMA)
+constexpr int kRows = 16;        // most query rows per KV head (two N tiles of the MMA)
 constexpr int kWarps = 4;
 constexpr int kBlockKeys = 16;   // keys per warp iteration
 constexpr int kMaxExtraUnits = 640;  // bound on the CTAs the splits are sized for (resident CTAs of the device)
