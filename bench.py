@@ -305,8 +305,8 @@ def run_quality(args):
 def run_decode(args):
     """Decode step against a resident compressed KV cache: one query token per sequence (32 query / 8 KV heads,
     d = 128) attends to Sk = 32768 cached keys, batch 8 — the per-GPU share of the scaling shape K,V
-    [64, 8, 32768, 128] over 8 GPUs.  The cache is compressed once outside the timed region; a step is the
-    fused attention call.  The work is bound by the packed bytes: per key (16 (b-1) + 16 + 4) + (16 b + 2)."""
+    [64, 8, 32768, 128] over 8 GPUs.  The cache (`CompressedKVCache`, capacity above the keys in use) is filled
+    outside the timed region; a step is `cache.attend(q)`.  The work is bound by the packed bytes: per key (16 (b-1) + 16 + 4) + (16 b + 2)."""
     import turboquant_b200 as tq
     from turboquant_b200 import _lib
     dev = torch.device("cuda", 0)
@@ -318,20 +318,36 @@ def run_decode(args):
     q = torch.randn(batch, HQ, 1, D, generator=g, device=dev).to(torch.bfloat16)
     kc = tq.TurboQuantCompressorV2(D, bits, 42, device=str(dev))
     vc = tq.TurboQuantCompressorMSE(D, bits, 10042, device=str(dev))
-    ck, cv = kc.compress(k), vc.compress(v)
+    # a persistent cache with room to grow: the kernel reads rows with the capacity as their stride
+    cache = tq.CompressedKVCache(kc, vc, batch, HKV, sk + 256, device=dev)
+    cache.append(k, v)
+    k_new, v_new = k[:, :, -1:].clone(), v[:, :, -1:].clone()
     del k, v
 
     def timed(steps):
         for _ in range(max(args.warmup, 3)):
-            tq.fused_attention(q, ck, cv, kc, vc, causal=True)
+            cache.attend(q, causal=True)
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(steps):
-            out = tq.fused_attention(q, ck, cv, kc, vc, causal=True)
+            out = cache.attend(q, causal=True)
         e1.record()
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / steps, out
+
+    def generation_steps(steps):
+        """Append the new token's key and value (two compression launches + six small copies), then attend."""
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            cache.append(k_new, v_new)
+            cache.attend(q, causal=True)
+        e1.record()
+        torch.cuda.synchronize()
+        cache.length = sk
+        return e0.elapsed_time(e1) / steps
 
     sampler = ClockSampler(0)
     sampler.start()
@@ -340,6 +356,8 @@ def run_decode(args):
     ms_sum, launches = (ctypes.c_float * 5)(), (ctypes.c_int * 5)()
     _lib.check(_lib.lib.tq_profile_end(ms_sum, launches))
     clocks = sampler.finish()
+    generation_steps(3)
+    gen_ms = generation_steps(min(max(args.steps, 1), 200))
     kern_ms = ms_sum[3] / max(launches[3], 1)
     keys = batch * HKV * sk
     bytes_per_key = (16 * (bits - 1) + 16 + 4) + (16 * bits + 2)
@@ -358,6 +376,7 @@ def run_decode(args):
                          "peak_source": peaks["source"]},
             "kernel_ms": {"prepare_queries": ms_sum[2] / max(launches[2], 1), "decode": kern_ms,
                           "merge_and_back_rotation": ms_sum[4] / max(launches[4], 1)},
+            "generation_step_ms": gen_ms,  # append one token per sequence to the cache, then attend
             "device_wait_faults": tq.device_fault_count(dev), "output_norm": float(out.float().norm())}
     print(json.dumps(line), flush=True)
 

@@ -225,6 +225,26 @@ int tq_attention_fwd_static(const void* q, int dtype, int64_t B, int64_t Hq, int
                             void* out, int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s,
                             int mode, void* stream);
 
+/* tq_attention_fwd against a persistent packed KV cache (no counterpart in the reference, which
+ * disables the cache and recompresses the whole prefix for every generated token: patch.py:80-81;
+ * the concept is turboquant.py:199-286).  Every packed array has room for `kv_capacity` keys per
+ * (batch, KV head) -- key k of pair (b, h) is row (b*Hkv + h)*kv_capacity + k -- of which the
+ * first Sk are in use; new tokens are compressed by tq_compress_keys / tq_compress_values and
+ * copied behind them.  Served by the split-KV kernel: head_dim 128, (Hq/Hkv)*Sq <= 16 query rows
+ * per KV head, TQ_MODE_BF16, no additive mask, any Sk >= 1; other shapes return TQ_ERR_INVALID_ARG.
+ * Workspace as for tq_attention_fwd in TQ_MODE_BF16. */
+int tq_attention_fwd_cached(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq, int d,
+                            int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                            int64_t Hkv, int64_t Sk, int64_t kv_capacity,
+                            const uint8_t* key_idx, const uint8_t* key_signs,
+                            const uint16_t* key_vec_norms, const uint16_t* key_residual_norms,
+                            const uint8_t* val_idx, const uint16_t* val_vec_norms,
+                            const float* Pi_k, const float* S_eff, const float* centroids_k,
+                            const float* Pi_v, const float* centroids_v, int bits,
+                            float sm_scale, int causal,
+                            void* out, int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s,
+                            void* workspace, size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

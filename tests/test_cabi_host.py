@@ -84,3 +84,22 @@ def test_attention_argument_checks():
     need = _lib.lib.tq_attention_workspace_bytes(1, 8, 4, 128, 1)
     assert need >= 8 * 4 * 128 * 2 * 3 and need % 256 == 0
     assert _lib.lib.tq_attention_workspace_bytes(0, 8, 4, 128, 1) == 0
+
+
+def test_cached_attention_argument_checks():
+    """tq_attention_fwd_cached refuses a capacity below the keys in use and shapes the split-KV kernel does not
+    serve, before anything is launched."""
+    from turboquant_b200 import _lib
+
+    buf = ctypes.create_string_buffer(1 << 16)
+    p = (ctypes.addressof(buf) + 255) & ~255
+
+    def call(Hq=8, Hkv=2, Sq=1, Sk=64, cap=128, d=128):
+        return _lib.lib.tq_attention_fwd_cached(p, 1, 1, Hq, Sq, d, Hq * Sq * d, Sq * d, d, Hkv, Sk, cap,
+                                                p, p, p, p, p, p, p, p, p, p, p, 3, 0.1, 1,
+                                                p, Hq * Sq * d, Sq * d, d, p, 0, None)
+
+    assert call(cap=32) == 1 and "capacity" in _lib.last_error()
+    assert call(Sq=8) == 1 and "query rows" in _lib.last_error()        # 4 heads per KV head x 8 positions > 16
+    assert call(d=64) == 1
+    assert call() == 4 and "workspace" in _lib.last_error()             # passes the shape checks

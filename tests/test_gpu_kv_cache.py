@@ -1,0 +1,74 @@
+"""Persistent compressed KV cache: tokens appended step by step and attended in place by the split-KV kernel
+give what the reference's cache-less flow gives (compress the whole prefix again, attend over it:
+src/transformers_turboquant/patch.py:80-81, families/llama.py:100-114)."""
+
+import pytest
+import torch
+
+from helpers import (device_compressors, oracle_attention_from_packed, oracle_key_dict_to_device, oracle_params,
+                     oracle_value_dict_to_device, rel_err)
+from oracle import tq_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def _tokens(B, H, S, d, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(B, H, S, d, generator=g)
+    x[..., :4] *= 8.0  # outlier channels, as in LLM keys
+    return x.to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4])
+def test_generation_loop_matches_recompression(bits):
+    from turboquant_b200 import CompressedKVCache, fused_attention
+    d, B, Hq, Hkv, prefill, steps, cap = 128, 2, 8, 2, 300, 6, 333
+    kc, vc = device_compressors(d, bits, mode="bf16")
+    k, v = _tokens(B, Hkv, prefill + steps, d, 1).cuda(), _tokens(B, Hkv, prefill + steps, d, 2).cuda()
+    q = _tokens(B, Hq, prefill + steps, d, 3).cuda()
+    cache = CompressedKVCache(kc, vc, B, Hkv, cap)
+    cache.append(k[:, :, :prefill], v[:, :, :prefill])
+    # prefill-sized queries over the cache take the gather path
+    want = fused_attention(q[:, :, :prefill], kc.compress(k[:, :, :prefill]), vc.compress(v[:, :, :prefill]), kc, vc)
+    assert torch.equal(cache.attend(q[:, :, :prefill]), want)
+    for t in range(prefill, prefill + steps):
+        cache.append(k[:, :, t:t + 1], v[:, :, t:t + 1])
+        assert len(cache) == t + 1
+        got = cache.attend(q[:, :, t:t + 1])
+        # the reference's flow: everything compressed again, one query row over t + 1 keys
+        ck, cv = kc.compress(k[:, :, :t + 1]), vc.compress(v[:, :, :t + 1])
+        assert torch.equal(cache.key_indices[:, :, :t + 1].reshape(-1, ck["packed_key_indices"].shape[1]),
+                           ck["packed_key_indices"])
+        assert torch.equal(cache.value_norms[:, :, :t + 1].reshape(-1), cv["vec_norms"])
+        want = fused_attention(q[:, :, t:t + 1], ck, cv, kc, vc, causal=True)
+        assert got.shape == want.shape and got.dtype == torch.bfloat16
+        assert torch.equal(got, want)  # same kernel, same split of the same bytes; only the row stride differs
+    with pytest.raises(ValueError):
+        cache.append(k[:, :, :cap], v[:, :, :cap])
+
+
+@pytest.mark.parametrize("n_keys,Sq", [(1, 1), (5, 1), (63, 2), (130, 4), (1000, 3)])
+def test_cached_attention_against_oracle_any_length(n_keys, Sq):
+    """Short and ragged caches (the split-KV kernel serves every length when the rows are strided), several new
+    positions at once (causal among themselves), against the oracle on the oracle's own packed bytes."""
+    from turboquant_b200 import CompressedKVCache
+    d, bits, B, Hq, Hkv, cap = 128, 3, 2, 8, 2, 1024
+    kp, vp = oracle_params(d, bits)
+    kc, vc = device_compressors(d, bits, mode="bf16")
+    k, v = _tokens(B, Hkv, n_keys, d, 10 + n_keys), _tokens(B, Hkv, n_keys, d, 20 + n_keys)
+    q = _tokens(B, Hq, Sq, d, 30 + n_keys)
+    ok, ov = orc.key_compress(k, kp), orc.value_compress(v, vp)
+    want = oracle_attention_from_packed(q, ok, ov, kp, vp, causal=True)
+    cache = CompressedKVCache(kc, vc, B, Hkv, cap)
+    # store the oracle's bytes so that both sides attend over identical packed data
+    n = n_keys
+    dk, dv = oracle_key_dict_to_device(ok), oracle_value_dict_to_device(ov)
+    cache.key_indices[:, :, :n] = dk["packed_key_indices"].view(B, Hkv, n, -1)
+    cache.key_signs[:, :, :n] = dk["packed_qjl_signs"].view(B, Hkv, n, -1)
+    cache.key_norms[:, :, :n] = dk["vec_norms"].view(B, Hkv, n)
+    cache.key_residual_norms[:, :, :n] = dk["residual_norm"].view(B, Hkv, n)
+    cache.value_indices[:, :, :n] = dv["packed_indices"].view(B, Hkv, n, -1)
+    cache.value_norms[:, :, :n] = dv["vec_norms"].view(B, Hkv, n)
+    cache.length = n
+    got = cache.attend(q.cuda(), causal=True)
+    assert rel_err(got, want) < 1.5e-2, rel_err(got, want)

@@ -26,6 +26,9 @@ struct AttnArgs {
   void* out;
   int out_dtype;
   int64_t o_stride_b, o_stride_h, o_stride_s;
+  // keys between the packed rows of consecutive (batch, KV head) pairs in every packed array: Sk for the
+  // contiguous [B, Hkv, Sk] layout, the capacity of a persistent cache otherwise (split-KV kernel only)
+  int64_t kv_stride;
 };
 
 int check_attention_args(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq, int d, int64_t sb, int64_t sh,
@@ -46,7 +49,7 @@ size_t workspace_bytes_bf16(int64_t BHq, int64_t Sq, int d);
 // Decode-sized calls (few query rows per KV head, long keys; tq_attention_decode.cu), three launches: query
 // preparation into `q_cat` (bf16 [n_q, 2d]), the split-KV kernel, then merge + back-rotation into a.out.
 // `part_ws` holds decode_workspace_bytes(B * Hq).
-bool decode_applies(const AttnArgs& a, int d);
+bool decode_applies(const AttnArgs& a, int d);  // a.kv_stride != a.Sk: any key count
 size_t decode_workspace_bytes(int64_t BHq);
 int attention_decode(const AttnArgs& a, int64_t B, int bits, const void* q, int q_dtype, int64_t sb, int64_t sh,
                      int64_t ss, const float* Pi_k, const float* S_eff, void* q_cat, void* part_ws, cudaStream_t stream);

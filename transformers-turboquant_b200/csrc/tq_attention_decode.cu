@@ -54,7 +54,7 @@ constexpr int kQPitch = 2 * 128 + 16;  // bf16 elements per staged query row: ro
 
 struct DecodeArgs {
   const __nv_bfloat16* q_cat;  // [B*Hq*Sq, 2d]
-  int64_t Hq, Hkv, Sq, Sk;
+  int64_t Hq, Hkv, Sq, Sk, kv_stride;
   const uint8_t* key_idx;
   const uint8_t* key_sgn;
   const uint16_t* key_vn;
@@ -208,7 +208,7 @@ __global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a)
   const int split = blockIdx.x;
   const int64_t kvh = blockIdx.y, b = blockIdx.z;
   const int G = (int)(a.Hq / a.Hkv), R = G * (int)a.Sq;
-  const int64_t kv_base = (b * a.Hkv + kvh) * a.Sk;
+  const int64_t kv_base = (b * a.Hkv + kvh) * a.kv_stride;
   const int shift = (int)(a.Sk - a.Sq);
 
   // ---- stage the query rows (row r = g * Sq + s of query head kvh * G + g), build the tables ----
@@ -681,7 +681,9 @@ static bool decode_enabled() {
 }
 
 bool decode_applies(const AttnArgs& a, int d) {
-  return decode_enabled() && d == 128 && a.mask == nullptr && a.Hkv > 0 && (a.Hq / a.Hkv) * a.Sq <= kRows && a.Sk >= 4 * kBlockKeys * kWarps;
+  const bool shape_ok = d == 128 && a.mask == nullptr && a.Hkv > 0 && (a.Hq / a.Hkv) * a.Sq <= kRows;
+  if (a.kv_stride != a.Sk) return shape_ok;  // a persistent cache: the only kernel that reads strided rows
+  return decode_enabled() && shape_ok && a.Sk >= 4 * kBlockKeys * kWarps;
 }
 
 
@@ -743,7 +745,7 @@ int attention_decode(const AttnArgs& a, int64_t B, int bits, const void* q, int 
   nsplit = (int)((a.Sk + per - 1) / per);
   float* part_o = static_cast<float*>(part_ws);
   float* part_ml = part_o + (size_t)units * nsplit * kRows * 128;
-  DecodeArgs da{static_cast<const __nv_bfloat16*>(q_cat), a.Hq, a.Hkv, a.Sq, a.Sk, a.key_idx, a.key_sgn, a.key_vn,
+  DecodeArgs da{static_cast<const __nv_bfloat16*>(q_cat), a.Hq, a.Hkv, a.Sq, a.Sk, a.kv_stride, a.key_idx, a.key_sgn, a.key_vn,
                 a.key_rn, a.val_idx, a.val_vn, a.cen_k, a.cen_v, a.sm_scale, a.causal, part_o, part_ml, nsplit, per};
   dim3 grid((unsigned)nsplit, (unsigned)a.Hkv, (unsigned)B);
   {

@@ -636,8 +636,8 @@ extern "C" int tq_prepare_queries(const void* q, int dtype, int64_t B, int64_t H
                               q_cat, s);
 }
 
-extern "C" int tq_attention_fwd(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq, int d, int64_t q_stride_b,
-                                int64_t q_stride_h, int64_t q_stride_s, int64_t Hkv, int64_t Sk,
+static int attention_entry(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq, int d, int64_t q_stride_b,
+                                int64_t q_stride_h, int64_t q_stride_s, int64_t Hkv, int64_t Sk, int64_t kv_stride,
                                 const uint8_t* key_idx, const uint8_t* key_signs, const uint16_t* key_vec_norms,
                                 const uint16_t* key_residual_norms, const uint8_t* val_idx,
                                 const uint16_t* val_vec_norms, const float* Pi_k, const float* S_eff,
@@ -666,13 +666,51 @@ extern "C" int tq_attention_fwd(const void* q, int dtype, int64_t B, int64_t Hq,
                 workspace_bytes);
   AttnArgs a{nullptr, Hq, Sq, Hkv, Sk, key_idx, key_signs, key_vec_norms, key_residual_norms, val_idx,
              val_vec_norms, centroids_k, centroids_v, Pi_v, sm_scale, causal, mask, mask_stride_b, mask_stride_q,
-             out, dtype, o_stride_b, o_stride_h, o_stride_s};
+             out, dtype, o_stride_b, o_stride_h, o_stride_s, kv_stride};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (mode == TQ_MODE_FP32)
+  if (mode == TQ_MODE_FP32) {
+    TQ_REQUIRE(kv_stride == Sk, "a cache with capacity > Sk needs TQ_MODE_BF16");
     return attention_fwd_fp32(q, dtype, B, Hq, Sq, d, q_stride_b, q_stride_h, q_stride_s, Pi_k, S_eff, a, bits,
                               workspace, s);
+  }
   return attention_fwd_bf16(q, dtype, B, Hq, Sq, d, q_stride_b, q_stride_h, q_stride_s, Pi_k, S_eff, a, bits,
                             workspace, s);
+}
+
+extern "C" int tq_attention_fwd(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq, int d, int64_t q_stride_b,
+                                int64_t q_stride_h, int64_t q_stride_s, int64_t Hkv, int64_t Sk,
+                                const uint8_t* key_idx, const uint8_t* key_signs, const uint16_t* key_vec_norms,
+                                const uint16_t* key_residual_norms, const uint8_t* val_idx,
+                                const uint16_t* val_vec_norms, const float* Pi_k, const float* S_eff,
+                                const float* centroids_k, const float* Pi_v, const float* centroids_v, int bits,
+                                float sm_scale, int causal, const float* mask, int64_t mask_stride_b,
+                                int64_t mask_stride_q, void* out, int64_t o_stride_b, int64_t o_stride_h,
+                                int64_t o_stride_s, void* workspace, size_t workspace_bytes, int mode, void* stream) {
+  return attention_entry(q, dtype, B, Hq, Sq, d, q_stride_b, q_stride_h, q_stride_s, Hkv, Sk, Sk, key_idx, key_signs,
+                         key_vec_norms, key_residual_norms, val_idx, val_vec_norms, Pi_k, S_eff, centroids_k, Pi_v,
+                         centroids_v, bits, sm_scale, causal, mask, mask_stride_b, mask_stride_q, out, o_stride_b,
+                         o_stride_h, o_stride_s, workspace, workspace_bytes, mode, stream);
+}
+
+extern "C" int tq_attention_fwd_cached(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq, int d,
+                                       int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s, int64_t Hkv,
+                                       int64_t Sk, int64_t kv_capacity, const uint8_t* key_idx,
+                                       const uint8_t* key_signs, const uint16_t* key_vec_norms,
+                                       const uint16_t* key_residual_norms, const uint8_t* val_idx,
+                                       const uint16_t* val_vec_norms, const float* Pi_k, const float* S_eff,
+                                       const float* centroids_k, const float* Pi_v, const float* centroids_v, int bits,
+                                       float sm_scale, int causal, void* out, int64_t o_stride_b, int64_t o_stride_h,
+                                       int64_t o_stride_s, void* workspace, size_t workspace_bytes, void* stream) {
+  TQ_REQUIRE(kv_capacity >= Sk, "cache capacity %lld is smaller than the %lld keys in use", (long long)kv_capacity,
+             (long long)Sk);
+  // (a full cache, capacity == Sk, is the contiguous layout and may be served by any of the kernels)
+  TQ_REQUIRE(d == 128 && Hkv > 0 && Hq % Hkv == 0 && (Hq / Hkv) * Sq <= 16,
+             "tq_attention_fwd_cached serves head_dim 128 and (Hq / Hkv) * Sq <= 16 query rows per KV head");
+  return attention_entry(q, dtype, B, Hq, Sq, d, q_stride_b, q_stride_h, q_stride_s, Hkv, Sk,
+                         kv_capacity, key_idx, key_signs, key_vec_norms, key_residual_norms,
+                         val_idx, val_vec_norms, Pi_k, S_eff, centroids_k, Pi_v, centroids_v, bits, sm_scale, causal,
+                         nullptr, 0, 0, out, o_stride_b, o_stride_h, o_stride_s, workspace, workspace_bytes,
+                         TQ_MODE_BF16, stream);
 }
 
 // ---- attention without caller-supplied scratch ---------------------------------------------
