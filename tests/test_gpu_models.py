@@ -128,3 +128,53 @@ def test_single_training_step_completes(kind):
     opt.step()
     assert not torch.equal(before, getattr(attn, out_w).weight.detach())
     assert model.config.use_cache is False
+
+
+def test_generation_with_the_compressed_cache_matches_recomputation():
+    """`apply_turboquant(..., kv_cache_capacity=n)` (an extension: the reference's adapters always run with
+    use_cache = False, patch.py:80-81) keeps a CompressedKVCache per layer.  Token-by-token decoding through the
+    HF cache protocol must give the logits of the reference flow, which recompresses and re-attends the whole
+    prefix for every new token."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+    from turboquant_b200 import apply_turboquant
+    torch.manual_seed(0)
+    cfg = LlamaConfig(hidden_size=512, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+                      intermediate_size=512, num_hidden_layers=2, vocab_size=512, max_position_embeddings=512)
+    base = LlamaForCausalLM(cfg).eval().cuda().to(torch.bfloat16)
+    plain = apply_turboquant(copy.deepcopy(base), bits=3, seed=42)
+    cached = apply_turboquant(copy.deepcopy(base), bits=3, seed=42, kv_cache_capacity=400)
+    assert plain.config.use_cache is False and cached.config.use_cache is True
+    ids = torch.randint(0, 512, (2, 300), generator=torch.Generator().manual_seed(4)).cuda()
+    steps = 5
+    with torch.no_grad():
+        out = cached(input_ids=ids[:, :300 - steps], use_cache=True)
+        pkv = out.past_key_values
+        assert rel_err(out.logits[:, -1].float(), plain(input_ids=ids[:, :300 - steps]).logits[:, -1].float()) < 1e-6
+        for t in range(300 - steps, 300):
+            out = cached(input_ids=ids[:, t:t + 1], past_key_values=pkv, use_cache=True)
+            want = plain(input_ids=ids[:, :t + 1]).logits[:, -1].float()
+            got = out.logits[:, -1].float()
+            # one query row per head through the split-KV kernel instead of the last row of a prefill tile
+            assert rel_err(got, want) < 3e-2, (t, rel_err(got, want))
+        # a second generation starts over: a new HF cache object resets the compressed caches
+        again = cached(input_ids=ids[:, :64], use_cache=True).logits[:, -1].float()
+        assert rel_err(again, plain(input_ids=ids[:, :64]).logits[:, -1].float()) < 1e-6
+        # and generate() runs end to end on it
+        gen = cached.generate(ids[:1, :32], max_new_tokens=4, do_sample=False)
+        assert gen.shape == (1, 36)
+
+
+def test_generate_without_cache_recomputes_the_whole_sequence():
+    """The reference switches `config.use_cache` off (patch.py:80-81); current transformers read the flag from
+    `generation_config`, which has to follow, or generate() would hand the adapters single tokens."""
+    from turboquant_b200 import apply_turboquant
+    model, _ = _build("llama")
+    model = apply_turboquant(copy.deepcopy(model).cuda().to(torch.bfloat16), bits=3, seed=42)
+    assert model.config.use_cache is False and model.generation_config.use_cache is False
+    ids = torch.randint(0, 512, (1, 40), generator=torch.Generator().manual_seed(5)).cuda()
+    with torch.no_grad():
+        gen = model.generate(ids, max_new_tokens=3, do_sample=False)
+        want = ids
+        for _ in range(3):
+            want = torch.cat([want, model(input_ids=want).logits[:, -1:].argmax(-1)], dim=1)
+    assert torch.equal(gen, want)

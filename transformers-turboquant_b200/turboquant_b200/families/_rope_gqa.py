@@ -20,6 +20,8 @@ from ..plugin import TurboQuantAttentionBase
 
 class RopeGQAAttention(TurboQuantAttentionBase):
     ATTENTION_CLASS_NAMES = ()
+    SUPPORTS_KV_CACHE = True
+    kv_cache_capacity: int | None = None  # set by apply_turboquant(..., kv_cache_capacity=n)
 
     @staticmethod
     def _rotary(q, k, cos, sin):
@@ -52,9 +54,35 @@ class RopeGQAAttention(TurboQuantAttentionBase):
         v = self.v_proj(hidden_states).view(shape).transpose(1, 2)
         cos, sin = position_embeddings
         q, k = self._rotary(q, k, cos, sin)
+        if self.kv_cache_capacity is not None and past_key_values is not None:
+            out = self._attend_cached(q, k, v, past_key_values, attention_mask)
+            return self.o_proj(out.transpose(1, 2).reshape(B, T, self.num_heads * self.head_dim)), None
         ck = self.key_compressor.compress(k)
         cv = self.val_compressor.compress(v)
         out = fused_attention(q, ck, cv, self.key_compressor, self.val_compressor, causal=True,
                               attention_mask=attention_mask)
         out = out.transpose(1, 2).reshape(B, T, self.num_heads * self.head_dim)
         return self.o_proj(out), None
+
+    def _attend_cached(self, q, k, v, past_key_values, attention_mask):
+        """Generation with a persistent compressed cache (no counterpart in the reference, whose adapters run
+        with `use_cache = False`).  The HF cache object only keeps count of the positions (it is fed
+        one channel of each key and value, 1/128 of them, so that `cache_position` and the rotary positions
+        advance as usual) and tells one
+        generation from the next: a cache object this layer has not seen starts a new sequence."""
+        import weakref
+
+        from ..kv_cache import CompressedKVCache
+        B, Hkv, T, D = k.shape
+        owner = getattr(self, "_tq_owner", None)
+        cache = getattr(self, "_tq_cache", None)
+        if owner is None or owner() is not past_key_values:
+            if cache is None or (cache.batch, cache.kv_heads) != (B, Hkv) or cache.key_indices.device != k.device:
+                cache = CompressedKVCache(self.key_compressor, self.val_compressor, B, Hkv, self.kv_cache_capacity,
+                                          device=k.device)
+                self._tq_cache = cache
+            cache.reset()
+            self._tq_owner = weakref.ref(past_key_values)
+        cache.append(k, v)
+        past_key_values.update(k[..., :1], v[..., :1], self.layer_idx)
+        return cache.attend(q, causal=True, attention_mask=attention_mask)

@@ -91,12 +91,13 @@ class CompressedKVCache:
         return ck, cv
 
     @torch.no_grad()
-    def attend(self, q: torch.Tensor, causal: bool = True, sm_scale: float | None = None) -> torch.Tensor:
+    def attend(self, q: torch.Tensor, causal: bool = True, sm_scale: float | None = None,
+               attention_mask: torch.Tensor | None = None) -> torch.Tensor:
         """softmax(scores * sm_scale) @ V_hat of q [B, Hq, Sq, D] over the tokens in use; with `causal` the
         queries are the last Sq positions (append their keys first).  Returns [B, Hq, Sq, D] in q.dtype.
 
-        Decode-sized calls (head_dim 128, (Hq / Hkv) * Sq <= 16, 16-bit queries) read the cache in place;
-        anything else gathers the prefix once and takes the prefill kernels."""
+        Decode-sized calls (head_dim 128, (Hq / Hkv) * Sq <= 16, 16-bit queries, no additive mask) read the
+        cache in place; anything else gathers the prefix once and takes the prefill kernels."""
         _require_cuda(q, "q")
         B, Hq, Sq, D = q.shape
         if (B, D) != (self.batch, self.head_dim) or Hq % self.kv_heads != 0:
@@ -104,11 +105,11 @@ class CompressedKVCache:
         if self.length == 0:
             raise ValueError("attention over an empty cache is undefined")
         in_place = (D == 128 and (Hq // self.kv_heads) * Sq <= 16 and q.dtype in (torch.bfloat16, torch.float16)
-                    and self.key_compressor.mode in (None, "bf16"))
+                    and self.key_compressor.mode in (None, "bf16") and attention_mask is None)
         if not in_place:
             ck, cv = self._contiguous_prefix()
             return fused_attention(q, ck, cv, self.key_compressor, self.val_compressor, causal=causal,
-                                   sm_scale=sm_scale)
+                                   attention_mask=attention_mask, sm_scale=sm_scale)
         kc, vc = self.key_compressor, self.val_compressor
         kc._check_device(q)
         vc._check_device(q)

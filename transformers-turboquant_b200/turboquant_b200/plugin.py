@@ -83,12 +83,18 @@ def _head_dim_of(module: nn.Module, config) -> int:
     return int(hd)
 
 
-def apply_turboquant(model, bits: int = 3, seed: int = 42, use_triton: bool = True):
+def apply_turboquant(model, bits: int = 3, seed: int = 42, use_triton: bool = True,
+                     kv_cache_capacity: int | None = None):
     """Replace every attention layer of a HF `PreTrainedModel` by its TurboQuant adapter,
     in place, and return the model.  Layer i (module traversal order) compresses keys with
     seed `seed + i` and values with `seed + i + 10000`; `config.use_cache` is switched off
     because the adapters recompute full-sequence attention (patch.py:13-82).
-    `use_triton` is accepted for call compatibility and ignored."""
+    `use_triton` is accepted for call compatibility and ignored.
+
+    `kv_cache_capacity` (an extension; the reference has no such mode) keeps `use_cache` on
+    instead: adapters that support it hold a `CompressedKVCache` of that many tokens per
+    sequence, so that `generate()` compresses every token once and a decode step reads the
+    packed cache in place."""
     adapter = get_attention_class(model.config.model_type)
     device = str(next(model.parameters()).device)
     layer = 0
@@ -99,7 +105,17 @@ def apply_turboquant(model, bits: int = 3, seed: int = 42, use_triton: bool = Tr
             hd = _head_dim_of(child, model.config)
             kc = TurboQuantCompressorV2(hd, bits, seed=seed + layer, device=device, use_triton=use_triton)
             vc = TurboQuantCompressorMSE(hd, bits, seed=seed + layer + 10000, device=device, use_triton=use_triton)
-            setattr(parent, name, adapter.from_original(child, kc, vc))
+            new = adapter.from_original(child, kc, vc)
+            if kv_cache_capacity is not None:
+                if not getattr(new, "SUPPORTS_KV_CACHE", False):
+                    raise UnsupportedModelError(f"{type(new).__name__} has no compressed-cache mode")
+                new.kv_cache_capacity = int(kv_cache_capacity)
+            setattr(parent, name, new)
             layer += 1
-    model.config.use_cache = False
+    model.config.use_cache = kv_cache_capacity is not None
+    # generate() reads its own copy of the flag: left on, it would feed the cache-less adapters one token
+    # at a time and every step would attend over that token alone
+    gen_cfg = getattr(model, "generation_config", None)
+    if gen_cfg is not None:
+        gen_cfg.use_cache = model.config.use_cache
     return model
