@@ -153,11 +153,13 @@ template <int BITS>
 struct Tables {
   static constexpr int KB = BITS - 1, VB = BITS;
   // keys: two adjacent indices -> one operand register (a bf16 pair along the coordinate), one copy per lane.
-  // (A wider entry, four indices -> two registers by one 64-bit load, costs more than it saves: with the few
-  // copies that fit its loads collide, and its register pair has to be moved apart for the MMA.)
-  static constexpr int kIdxBitsK = 2 * KB;
-  static constexpr int kEntryK = 4;
-  static constexpr int kCopiesK = 32;
+  // A wider entry, four indices -> two registers by one 64-bit load, saves instructions but needs a copy per
+  // lane of a half warp to stay free of bank conflicts: that fits for 1-bit indices (16 entries) and is used
+  // there; for 2-bit indices (256 entries) only 8 copies fit, its loads collide and it measured slower.
+  static constexpr bool kQuad = KB == 1;
+  static constexpr int kIdxBitsK = kQuad ? 4 * KB : 2 * KB;
+  static constexpr int kEntryK = kQuad ? 8 : 4;
+  static constexpr int kCopiesK = kQuad ? 16 : 32;
   static constexpr int kShiftK = 7;  // log2(kEntryK * kCopiesK)
   static constexpr int kBytesK = (1 << kIdxBitsK) * kEntryK * kCopiesK;
   // signs: four adjacent sign bits -> two registers of +-1 pairs by one 64-bit load; the 16 entries cover the
@@ -231,7 +233,9 @@ __global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a)
     constexpr uint32_t km = (1u << KB) - 1, vm = (1u << VB) - 1;
     for (int e = tid; e < (1 << T::kIdxBitsK) * T::kCopiesK; e += kWarps * 32) {
       const uint32_t i = e / T::kCopiesK;
-      reinterpret_cast<uint32_t*>(lutK)[e] = bf16x2(__ldg(a.cen_k + (i & km)), __ldg(a.cen_k + (i >> KB)));
+      uint32_t* dst = reinterpret_cast<uint32_t*>(lutK + e * T::kEntryK);
+      dst[0] = bf16x2(__ldg(a.cen_k + (i & km)), __ldg(a.cen_k + ((i >> KB) & km)));
+      if constexpr (T::kQuad) dst[1] = bf16x2(__ldg(a.cen_k + ((i >> (2 * KB)) & km)), __ldg(a.cen_k + ((i >> (3 * KB)) & km)));
     }
     for (int e = tid; e < (1 << (2 * VB)) * T::kCopiesV; e += kWarps * 32) {
       const uint32_t i = e / T::kCopiesV;
@@ -248,6 +252,7 @@ __global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a)
   // load takes as its immediate, the second one three-input logic operation on the shifted packed word
   const uint32_t lutK_base = smem_u32(lutK), lutV_base = smem_u32(lutV), lutS_base = smem_u32(lutS);
   const uint32_t lane4 = (uint32_t)(lane * 4), laneV = (uint32_t)((lane % T::kCopiesV) * 4);
+  const uint32_t laneK = (uint32_t)((lane % T::kCopiesK) * T::kEntryK);
 
   // Query rows are the N dimension of every MMA (tiles of 8): NT = 1 serves up to 8 rows, NT = 2 up to 16.  Rows
   // past R hold zero queries; their results are never read, so they are not masked.  Masking is needed only in
@@ -384,6 +389,9 @@ __global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a)
         for (int h = 0; h < 2; ++h) {
           if constexpr (ks >= 8) {
             const uint2 e = lds64(lutS_base + scaled_field<4 * j, 4, 3>(sg[h]));
+            ka[h] = e.x; ka[2 + h] = e.y;
+          } else if constexpr (T::kQuad) {
+            const uint2 e = lds64(lutK_base + (laneK | scaled_field<4 * KB * j, 4 * KB, T::kShiftK>(kw[h])));
             ka[h] = e.x; ka[2 + h] = e.y;
           } else {
             ka[h] = lds32(lutK_base + (lane4 | scaled_field<4 * KB * j, 2 * KB, T::kShiftK>(kw[h])));
