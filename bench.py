@@ -351,11 +351,14 @@ def run_decode(args):
 
     sampler = ClockSampler(0)
     sampler.start()
-    _lib.check(_lib.lib.tq_profile_begin(max(args.steps, 1) + max(args.warmup, 3)))
     ms, out = timed(args.steps)
+    clocks = sampler.finish()
+    # per-kernel times from a second pass: the profiling events sit between the three launches of a call and
+    # keep them from overlapping (programmatic dependent launch), so the timed pass above runs without them
+    _lib.check(_lib.lib.tq_profile_begin(max(args.steps, 1) + max(args.warmup, 3)))
+    timed(args.steps)
     ms_sum, launches = (ctypes.c_float * 5)(), (ctypes.c_int * 5)()
     _lib.check(_lib.lib.tq_profile_end(ms_sum, launches))
-    clocks = sampler.finish()
     generation_steps(3)
     gen_ms = generation_steps(min(max(args.steps, 1), 200))
     kern_ms = ms_sum[3] / max(launches[3], 1)
@@ -369,7 +372,7 @@ def run_decode(args):
             "config": {"workload": "decode_b8_h32_kv8_sk32768", "batch_per_gpu": batch, "q_heads": HQ, "kv_heads": HKV,
                        "new_tokens": 1, "cached_keys": sk, "head_dim": D, "bits": bits,
                        "l2": f"packed cache ({keys * bytes_per_key / 1e6:.0f} MB) exceeds the 126 MB L2; no flush"},
-            "clocks": clocks, "gpu_launches": int(sum(launches)),
+            "clocks": clocks, "gpu_launches": 3 * args.steps,  # per call: query preparation, split-KV kernel, merge + back-rotation
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "traffic": None,
                          "kernel": "decode_kernel", "ms_per_launch": kern_ms,

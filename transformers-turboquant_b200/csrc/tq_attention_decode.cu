@@ -80,6 +80,11 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Programmatic dependent launch: `wait` returns when the grid this one depends on has completed and its writes
+// are visible (at once when the kernel was launched without the attribute); `launch_dependents` lets the next
+// kernel of the stream start early, up to its own `wait`.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 // 8x8 transpose of 16-bit elements across the warp: lane (g, t) gives row g, columns 2 t, 2 t + 1 and receives
 // column g, rows 2 t, 2 t + 1
 __device__ __forceinline__ uint32_t transpose8x8(uint32_t v) {
@@ -173,7 +178,7 @@ struct Tables {
 };
 
 template <int BITS, int NT>
-__global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a) {
+__global__ void __launch_bounds__(kWarps * 32, 4) decode_kernel(const DecodeArgs a) {
   using T = Tables<BITS>;
   constexpr bool kQInRegs = NT == 1;
   constexpr int D = 128, KB = BITS - 1, VB = BITS;
@@ -213,22 +218,7 @@ __global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a)
   const int64_t kv_base = (b * a.Hkv + kvh) * a.kv_stride;
   const int shift = (int)(a.Sk - a.Sq);
 
-  // ---- stage the query rows (row r = g * Sq + s of query head kvh * G + g), build the tables ----
-  // Within each half of a row (rotated coordinates, sketch coordinates) coordinate 32 t + 4 j + e is stored at
-  // 16 j + 4 t + e: lane t of a quad owns coordinates 32 t .. 32 t + 31 (contiguous bits of a packed row), and
-  // its four coordinates of k-step j are one 64-bit load.
-  for (int e = tid; e < kRows * (2 * D / 8); e += kWarps * 32) {
-    const int r = e / (2 * D / 8), m = e % (2 * D / 8);
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < R) {
-      const int64_t h = kvh * G + r / a.Sq, s = r % a.Sq;
-      v = reinterpret_cast<const uint4*>(a.q_cat + ((b * a.Hq + h) * a.Sq + s) * (2 * D))[m];
-    }
-    const int half = m / 16, mm = m % 16;  // coordinates 8 mm .. 8 mm + 7 of the half: t = mm / 4, j = 2 (mm % 4), + 1
-    __nv_bfloat16* dst = &q_s[r * kQPitch + 128 * half + 32 * (mm % 4) + 4 * (mm / 4)];
-    *reinterpret_cast<uint2*>(dst) = make_uint2(v.x, v.y);
-    *reinterpret_cast<uint2*>(dst + 16) = make_uint2(v.z, v.w);
-  }
+  // ---- build the tables (nothing here depends on the kernel launched before this one) ----
   {
     constexpr uint32_t km = (1u << KB) - 1, vm = (1u << VB) - 1;
     for (int e = tid; e < (1 << T::kIdxBitsK) * T::kCopiesK; e += kWarps * 32) {
@@ -247,7 +237,6 @@ __global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a)
                                                        ((tid & 4) ? pos : neg) | (((tid & 8) ? pos : neg) << 16));
     }
   }
-  __syncthreads();
   // a look-up address is (table address) + (lane's copy | entry): the first is a constant of the build that the
   // load takes as its immediate, the second one three-input logic operation on the shifted packed word
   const uint32_t lutK_base = smem_u32(lutK), lutV_base = smem_u32(lutV), lutS_base = smem_u32(lutS);
@@ -284,13 +273,6 @@ __global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a)
       m_run[t][e] = -INFINITY;
       l_run[t][e] = 0.f;
     }
-  // B fragments of Q^T (k-slots of k-step ks x query row gq of tile t): kept in registers when one tile is all
-  uint2 qr[kQInRegs ? 16 : 1];
-  if constexpr (kQInRegs) {
-#pragma unroll
-    for (int ks = 0; ks < 16; ++ks) qr[ks] = *reinterpret_cast<const uint2*>(&q_s[gq * kQPitch + 16 * ks + 4 * tq]);
-  }
-
   const int k_lo = split * a.keys_per_split;
   const int k_hi = min((int)a.Sk, k_lo + a.keys_per_split);
   const uint8_t* kidx_base = a.key_idx + kv_base * (16 * KB);
@@ -343,6 +325,33 @@ __global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a)
     const int pb = blk0 + s * kBlockKeys * kWarps;
     if (pb < k_hi) stage(pb, s);
     cp_async_commit();
+  }
+  // The query rows come from the kernel launched just before this one.  With programmatic dependent launch this
+  // kernel may have started while that one was still running: everything above (tables, the first copies of
+  // packed rows) overlapped with it, and this is where its results are waited for.
+  grid_dependency_wait();
+  // ---- stage the query rows (row r = g * Sq + s of query head kvh * G + g) ----
+  // Within each half of a row (rotated coordinates, sketch coordinates) coordinate 32 t + 4 j + e is stored at
+  // 16 j + 4 t + e: lane t of a quad owns coordinates 32 t .. 32 t + 31 (contiguous bits of a packed row), and
+  // its four coordinates of k-step j are one 64-bit load.
+  for (int e = tid; e < kRows * (2 * D / 8); e += kWarps * 32) {
+    const int r = e / (2 * D / 8), m = e % (2 * D / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < R) {
+      const int64_t h = kvh * G + r / a.Sq, s = r % a.Sq;
+      v = reinterpret_cast<const uint4*>(a.q_cat + ((b * a.Hq + h) * a.Sq + s) * (2 * D))[m];
+    }
+    const int half = m / 16, mm = m % 16;  // coordinates 8 mm .. 8 mm + 7 of the half: t = mm / 4, j = 2 (mm % 4), + 1
+    __nv_bfloat16* dst = &q_s[r * kQPitch + 128 * half + 32 * (mm % 4) + 4 * (mm / 4)];
+    *reinterpret_cast<uint2*>(dst) = make_uint2(v.x, v.y);
+    *reinterpret_cast<uint2*>(dst + 16) = make_uint2(v.z, v.w);
+  }
+  __syncthreads();  // tables and query rows are complete
+  // B fragments of Q^T (k-slots of k-step ks x query row gq of tile t): kept in registers when one tile is all
+  uint2 qr[kQInRegs ? 16 : 1];
+  if constexpr (kQInRegs) {
+#pragma unroll
+    for (int ks = 0; ks < 16; ++ks) qr[ks] = *reinterpret_cast<const uint2*>(&q_s[gq * kQPitch + 16 * ks + 4 * tq]);
   }
   int st = 0;
   for (int blk = blk0; blk < k_hi; blk += kBlockKeys * kWarps, st = (st + 1 == kStages ? 0 : st + 1)) {
@@ -523,6 +532,7 @@ __global__ void __launch_bounds__(kWarps * 32) decode_kernel(const DecodeArgs a)
   }
 
   // ---- merge: lane groups (row sums), the four warps, then this split's partial result ----
+  grid_launch_dependents();  // the finishing kernel may start its own set-up; it waits for this grid to end
   asm volatile("cp.async.wait_group 0;" ::: "memory");
 #pragma unroll
   for (int t = 0; t < NT; ++t)
@@ -593,6 +603,7 @@ __global__ void __launch_bounds__(1024) decode_prepare_kernel(const void* __rest
                                                               float coeff, __nv_bfloat16* __restrict__ q_cat) {
   constexpr int D = 128;
   __shared__ __align__(16) float buf[3][kRows][D];  // raw queries, rotated queries, sketch projections
+  grid_launch_dependents();  // the split-KV kernel builds its tables and starts copying packed rows meanwhile
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int64_t b = blockIdx.x / Hkv, kvh = blockIdx.x % Hkv;
   const int G = (int)(Hq / Hkv), R = G * (int)Sq;
@@ -642,6 +653,10 @@ __global__ void __launch_bounds__(512) decode_finish_kernel(const float* __restr
   const int r = blockIdx.x;
   const int64_t unit = blockIdx.y, b = unit / Hkv, kvh = unit % Hkv;
   const int G = (int)(Hq / Hkv);
+  float pv[D / 4];  // this thread's part of column j of Pi_v: independent of the kernel before, loaded while it ends
+#pragma unroll
+  for (int c = 0; c < D / 4; ++c) pv[c] = __ldg(Pi_v + (32 * p + c) * D + j);
+  grid_dependency_wait();
   const float* ml = part_ml + (unit * nsplit * kRows + r) * 2;  // split s: ml[s * kRows * 2], + 1
   // every warp finds the maximum and the total weight by itself; warp 0 also publishes the factors
   float m = -INFINITY;
@@ -667,7 +682,7 @@ __global__ void __launch_bounds__(512) decode_finish_kernel(const float* __restr
   __syncthreads();
   float y = 0.f;
 #pragma unroll
-  for (int c = 0; c < D / 4; ++c) y = fmaf(o_s[32 * p + c], __ldg(Pi_v + (32 * p + c) * D + j), y);
+  for (int c = 0; c < D / 4; ++c) y = fmaf(o_s[32 * p + c], pv[c], y);
   part[p][j] = y;
   __syncthreads();
   if (tid < D) {
@@ -716,6 +731,23 @@ static int resident_ctas(int bits, int nt) {
   return cached[bits][nt];
 }
 
+// Launch a kernel that may start before the previous kernel of the stream has finished (programmatic dependent
+// launch); the kernel itself waits (grid_dependency_wait) before it touches that kernel's results.
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 block, cudaStream_t stream, Args... args) {
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 int attention_decode(const AttnArgs& a, int64_t B, int bits, const void* q, int q_dtype, int64_t sb, int64_t sh,
                      int64_t ss, const float* Pi_k, const float* S_eff, void* q_cat, void* part_ws, cudaStream_t stream) {
   const int64_t units = B * a.Hkv;
@@ -758,22 +790,15 @@ int attention_decode(const AttnArgs& a, int64_t B, int bits, const void* q, int 
   dim3 grid((unsigned)nsplit, (unsigned)a.Hkv, (unsigned)B);
   {
     ProfScope prof(kProfAttention, stream);
-    const unsigned threads = kWarps * 32;
-    if (nt == 1) {
-      if (bits == 2) decode_kernel<2, 1><<<grid, threads, 0, stream>>>(da);
-      else if (bits == 3) decode_kernel<3, 1><<<grid, threads, 0, stream>>>(da);
-      else decode_kernel<4, 1><<<grid, threads, 0, stream>>>(da);
-    } else {
-      if (bits == 2) decode_kernel<2, 2><<<grid, threads, 0, stream>>>(da);
-      else if (bits == 3) decode_kernel<3, 2><<<grid, threads, 0, stream>>>(da);
-      else decode_kernel<4, 2><<<grid, threads, 0, stream>>>(da);
-    }
-    TQ_CUDA_OK(cudaGetLastError());
+    void (*kern)(DecodeArgs) =
+        nt == 1 ? (bits == 2 ? decode_kernel<2, 1> : bits == 3 ? decode_kernel<3, 1> : decode_kernel<4, 1>)
+                : (bits == 2 ? decode_kernel<2, 2> : bits == 3 ? decode_kernel<3, 2> : decode_kernel<4, 2>);
+    TQ_CUDA_OK(launch_dependent(kern, grid, dim3(kWarps * 32), stream, da));
   }
   ProfScope prof(kProfBackRotation, stream);
-  decode_finish_kernel<<<dim3((unsigned)R, (unsigned)units), 512, 0, stream>>>(
-      part_o, part_ml, nsplit, a.Hq, a.Hkv, a.Sq, a.Pi_v, a.out, a.out_dtype, a.o_stride_b, a.o_stride_h, a.o_stride_s);
-  TQ_CUDA_OK(cudaGetLastError());
+  TQ_CUDA_OK(launch_dependent(decode_finish_kernel, dim3((unsigned)R, (unsigned)units), dim3(512), stream, part_o,
+                              part_ml, nsplit, a.Hq, a.Hkv, a.Sq, a.Pi_v, a.out, a.out_dtype, a.o_stride_b,
+                              a.o_stride_h, a.o_stride_s));
   return TQ_OK;
 }
 
