@@ -245,6 +245,23 @@ int tq_attention_fwd_cached(const void* q, int dtype, int64_t B, int64_t Hq, int
                             void* out, int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s,
                             void* workspace, size_t workspace_bytes, void* stream);
 
+/* tq_compress_keys / tq_compress_values writing straight into a persistent cache (see
+ * tq_attention_fwd_cached): input vector (b, h, s) goes to row (b*H + h)*kv_capacity + kv_offset + s
+ * of every output array, i.e. behind the kv_offset tokens already stored.  Same arithmetic and the
+ * same bytes as the contiguous calls; kv_offset + S must not exceed kv_capacity. */
+int tq_append_keys(const void* keys, int dtype, int64_t B, int64_t H, int64_t S, int d,
+                   int64_t stride_b, int64_t stride_h, int64_t stride_s,
+                   const float* Pi, const float* S_eff, const float* centroids,
+                   const float* boundaries, int bits,
+                   uint8_t* packed_idx, uint8_t* packed_signs,
+                   uint16_t* vec_norms, uint16_t* residual_norms,
+                   int64_t kv_capacity, int64_t kv_offset, int mode, void* stream);
+int tq_append_values(const void* values, int dtype, int64_t B, int64_t H, int64_t S, int d,
+                     int64_t stride_b, int64_t stride_h, int64_t stride_s,
+                     const float* Pi, const float* boundaries, int bits,
+                     uint8_t* packed_idx, uint16_t* vec_norms,
+                     int64_t kv_capacity, int64_t kv_offset, int mode, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -103,3 +103,16 @@ def test_cached_attention_argument_checks():
     assert call(Sq=8) == 1 and "query rows" in _lib.last_error()        # 4 heads per KV head x 8 positions > 16
     assert call(d=64) == 1
     assert call() == 4 and "workspace" in _lib.last_error()             # passes the shape checks
+
+
+def test_append_argument_checks():
+    """tq_append_keys / tq_append_values refuse tokens that do not fit behind the ones stored."""
+    from turboquant_b200 import _lib
+
+    buf = ctypes.create_string_buffer(1 << 16)
+    p = (ctypes.addressof(buf) + 255) & ~255
+    st = _lib.lib.tq_append_keys(p, 1, 1, 2, 8, 128, 2048, 1024, 128, p, p, p, p, 3, p, p, p, p, 64, 60, 1, None)
+    assert st == 1 and "do not fit" in _lib.last_error()
+    st = _lib.lib.tq_append_values(p, 1, 1, 2, 8, 128, 2048, 1024, 128, p, p, 3, p, p, 64, -1, 1, None)
+    assert st == 1 and "do not fit" in _lib.last_error()
+    assert _lib.lib.tq_append_values(None, 1, 1, 2, 0, 128, 0, 0, 128, None, None, 3, None, None, 64, 64, 1, None) == 0

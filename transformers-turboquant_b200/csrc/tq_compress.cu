@@ -86,10 +86,11 @@ __global__ void __launch_bounds__(16 * (D / 8)) compress_simt_kernel(const Compr
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
       const int64_t n = base + row0 + r;
+      const int64_t no = compress_out_row(a, n);
       int f[8];
 #pragma unroll
       for (int c = 0; c < 8; ++c) f[c] = count_below<NB>(y[r][c], bnd);
-      if (n < a.n_vec) store_fields8<IB>(a.packed_idx + n * (D * IB / 8) + tx * IB, f);
+      if (n < a.n_vec) store_fields8<IB>(a.packed_idx + no * (D * IB / 8) + tx * IB, f);
       const float nv = nrm[row0 + r];
       if (IS_KEY) {
         const float np = nv + 1e-8f;
@@ -107,11 +108,11 @@ __global__ void __launch_bounds__(16 * (D / 8)) compress_simt_kernel(const Compr
 #pragma unroll
         for (int off = TX / 2; off > 0; off >>= 1) rr += __shfl_xor_sync(0xffffffffu, rr, off);
         if (tx == 0 && n < a.n_vec) {
-          a.vec_norms[n] = fp16_bits(nv);
-          a.residual_norms[n] = fp16_bits(sqrtf(rr));
+          a.vec_norms[no] = fp16_bits(nv);
+          a.residual_norms[no] = fp16_bits(sqrtf(rr));
         }
       } else if (tx == 0 && n < a.n_vec) {
-        a.vec_norms[n] = fp16_bits(nv);
+        a.vec_norms[no] = fp16_bits(nv);
       }
     }
     if (IS_KEY) {
@@ -124,7 +125,7 @@ __global__ void __launch_bounds__(16 * (D / 8)) compress_simt_kernel(const Compr
         unsigned bits = 0;
 #pragma unroll
         for (int c = 0; c < 8; ++c) bits |= (p[r][c] >= 0.f ? 1u : 0u) << c;
-        if (n < a.n_vec) a.packed_signs[n * (D / 8) + tx] = static_cast<uint8_t>(bits);
+        if (n < a.n_vec) a.packed_signs[compress_out_row(a, n) * (D / 8) + tx] = static_cast<uint8_t>(bits);
       }
     }
   }
@@ -200,11 +201,11 @@ using namespace tq;
 
 extern "C" {
 
-int tq_compress_keys(const void* keys, int dtype, int64_t B, int64_t H, int64_t S, int d,
+static int compress_keys_entry(const void* keys, int dtype, int64_t B, int64_t H, int64_t S, int d,
                      int64_t stride_b, int64_t stride_h, int64_t stride_s, const float* Pi,
                      const float* S_eff, const float* centroids, const float* boundaries, int bits,
                      uint8_t* packed_idx, uint8_t* packed_signs, uint16_t* vec_norms,
-                     uint16_t* residual_norms, int mode, void* stream) {
+                     uint16_t* residual_norms, int64_t out_stride, int64_t out_offset, int mode, void* stream) {
   if (int st = check_states(keys, dtype, B, H, S, d, stride_b, stride_h, stride_s, bits)) return st;
   TQ_REQUIRE(mode == TQ_MODE_FP32 || mode == TQ_MODE_BF16, "unknown mode %d", mode);
   const int64_t n = B * H * S;
@@ -213,14 +214,14 @@ int tq_compress_keys(const void* keys, int dtype, int64_t B, int64_t H, int64_t 
   TQ_REQUIRE(packed_idx && packed_signs && vec_norms && residual_norms, "NULL output pointer");
   CompressArgs a{keys, n, H, S, stride_b, stride_h, stride_s, Pi, S_eff, centroids, boundaries,
                  packed_idx, packed_signs, vec_norms, residual_norms,
-                 (int)((n + kTileRows - 1) / kTileRows)};
+                 (int)((n + kTileRows - 1) / kTileRows), out_stride, out_offset};
   return dispatch_compress<true>(dtype, d, bits - 1, a, mode, static_cast<cudaStream_t>(stream));
 }
 
-int tq_compress_values(const void* values, int dtype, int64_t B, int64_t H, int64_t S, int d,
+static int compress_values_entry(const void* values, int dtype, int64_t B, int64_t H, int64_t S, int d,
                        int64_t stride_b, int64_t stride_h, int64_t stride_s, const float* Pi,
                        const float* boundaries, int bits, uint8_t* packed_idx, uint16_t* vec_norms,
-                       int mode, void* stream) {
+                       int64_t out_stride, int64_t out_offset, int mode, void* stream) {
   if (int st = check_states(values, dtype, B, H, S, d, stride_b, stride_h, stride_s, bits)) return st;
   TQ_REQUIRE(mode == TQ_MODE_FP32 || mode == TQ_MODE_BF16, "unknown mode %d", mode);
   const int64_t n = B * H * S;
@@ -228,8 +229,49 @@ int tq_compress_values(const void* values, int dtype, int64_t B, int64_t H, int6
   TQ_REQUIRE(Pi && boundaries, "NULL constant pointer");
   TQ_REQUIRE(packed_idx && vec_norms, "NULL output pointer");
   CompressArgs a{values, n, H, S, stride_b, stride_h, stride_s, Pi, nullptr, nullptr, boundaries,
-                 packed_idx, nullptr, vec_norms, nullptr, (int)((n + kTileRows - 1) / kTileRows)};
+                 packed_idx, nullptr, vec_norms, nullptr, (int)((n + kTileRows - 1) / kTileRows), out_stride, out_offset};
   return dispatch_compress<false>(dtype, d, bits, a, mode, static_cast<cudaStream_t>(stream));
+}
+
+int tq_compress_keys(const void* keys, int dtype, int64_t B, int64_t H, int64_t S, int d,
+                     int64_t stride_b, int64_t stride_h, int64_t stride_s, const float* Pi,
+                     const float* S_eff, const float* centroids, const float* boundaries, int bits,
+                     uint8_t* packed_idx, uint8_t* packed_signs, uint16_t* vec_norms,
+                     uint16_t* residual_norms, int mode, void* stream) {
+  return compress_keys_entry(keys, dtype, B, H, S, d, stride_b, stride_h, stride_s, Pi, S_eff, centroids, boundaries,
+                             bits, packed_idx, packed_signs, vec_norms, residual_norms, S, 0, mode, stream);
+}
+
+int tq_compress_values(const void* values, int dtype, int64_t B, int64_t H, int64_t S, int d,
+                       int64_t stride_b, int64_t stride_h, int64_t stride_s, const float* Pi,
+                       const float* boundaries, int bits, uint8_t* packed_idx, uint16_t* vec_norms,
+                       int mode, void* stream) {
+  return compress_values_entry(values, dtype, B, H, S, d, stride_b, stride_h, stride_s, Pi, boundaries, bits,
+                               packed_idx, vec_norms, S, 0, mode, stream);
+}
+
+int tq_append_keys(const void* keys, int dtype, int64_t B, int64_t H, int64_t S, int d,
+                   int64_t stride_b, int64_t stride_h, int64_t stride_s, const float* Pi,
+                   const float* S_eff, const float* centroids, const float* boundaries, int bits,
+                   uint8_t* packed_idx, uint8_t* packed_signs, uint16_t* vec_norms,
+                   uint16_t* residual_norms, int64_t kv_capacity, int64_t kv_offset, int mode, void* stream) {
+  TQ_REQUIRE(kv_offset >= 0 && S >= 0 && kv_offset + S <= kv_capacity,
+             "%lld new tokens behind %lld do not fit a cache of %lld", (long long)S, (long long)kv_offset,
+             (long long)kv_capacity);
+  return compress_keys_entry(keys, dtype, B, H, S, d, stride_b, stride_h, stride_s, Pi, S_eff, centroids, boundaries,
+                             bits, packed_idx, packed_signs, vec_norms, residual_norms, kv_capacity, kv_offset, mode,
+                             stream);
+}
+
+int tq_append_values(const void* values, int dtype, int64_t B, int64_t H, int64_t S, int d,
+                     int64_t stride_b, int64_t stride_h, int64_t stride_s, const float* Pi,
+                     const float* boundaries, int bits, uint8_t* packed_idx, uint16_t* vec_norms,
+                     int64_t kv_capacity, int64_t kv_offset, int mode, void* stream) {
+  TQ_REQUIRE(kv_offset >= 0 && S >= 0 && kv_offset + S <= kv_capacity,
+             "%lld new tokens behind %lld do not fit a cache of %lld", (long long)S, (long long)kv_offset,
+             (long long)kv_capacity);
+  return compress_values_entry(values, dtype, B, H, S, d, stride_b, stride_h, stride_s, Pi, boundaries, bits,
+                               packed_idx, vec_norms, kv_capacity, kv_offset, mode, stream);
 }
 
 }  // extern "C"

@@ -19,7 +19,14 @@ struct CompressArgs {
   uint16_t* vec_norms;
   uint16_t* residual_norms;
   int num_tiles;
+  // Output row of input vector n = (b * H + h) * S + s: (b * H + h) * out_stride + out_offset + s.  out_stride = S
+  // and out_offset = 0 give the contiguous layout; a persistent cache passes its capacity and its fill level.
+  int64_t out_stride, out_offset;
 };
+
+__device__ __forceinline__ int64_t compress_out_row(const CompressArgs& a, int64_t n) {
+  return a.out_stride == a.S ? n + a.out_offset : (n / a.S) * a.out_stride + a.out_offset + n % a.S;
+}
 
 // bf16 inputs, rotation and sketch projection on tcgen05 (tq_compress_tc.cu).
 int compress_tc(bool is_key, int d, int index_bits, const CompressArgs& a, cudaStream_t stream);

@@ -136,6 +136,7 @@ __global__ void __launch_bounds__(4 * D, 1) compress_tc_kernel(const CompressArg
   for (int tile = blockIdx.x; tile < a.num_tiles; tile += gridDim.x) {
     const int64_t n = static_cast<int64_t>(tile) * 128 + row;
     const bool live = n < a.n_vec;
+    const int64_t no = compress_out_row(a, n);  // where this vector's packed row goes
     // ---- 1. norm + A tile ------------------------------------------------------------------
     {
       float ss = 0.f;
@@ -220,14 +221,14 @@ __global__ void __launch_bounds__(4 * D, 1) compress_tc_kernel(const CompressArg
       }
     }
     if (live) {
-      uint32_t* dst = reinterpret_cast<uint32_t*>(a.packed_idx + n * ROWB + 4 * IB * part);
+      uint32_t* dst = reinterpret_cast<uint32_t*>(a.packed_idx + no * ROWB + 4 * IB * part);
       if constexpr (IB == 4) *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
       else if constexpr (IB == 2) *reinterpret_cast<uint2*>(dst) = make_uint2(packed[0], packed[1]);
       else {
 #pragma unroll
         for (int i = 0; i < IB; ++i) dst[i] = packed[i];
       }
-      if (part == 0) a.vec_norms[n] = fp16_bits(nv);
+      if (part == 0) a.vec_norms[no] = fp16_bits(nv);
     }
     if (IS_KEY) {
       // ---- QJL sketch of the residual --------------------------------------------------------
@@ -252,7 +253,7 @@ __global__ void __launch_bounds__(4 * D, 1) compress_tc_kernel(const CompressArg
         float rs = 0.f;
 #pragma unroll
         for (int q = 0; q < NP; ++q) rs += rr_part[q][row];
-        a.residual_norms[n] = fp16_bits(sqrtf(rs));
+        a.residual_norms[no] = fp16_bits(sqrtf(rs));
       }
       if (!tc::mbar_wait_or_abort(bar_addr, phase, abort_flag)) break;
       phase ^= 1;
@@ -263,7 +264,7 @@ __global__ void __launch_bounds__(4 * D, 1) compress_tc_kernel(const CompressArg
       uint32_t bits = 0;
 #pragma unroll
       for (int e = 0; e < 32; ++e) bits |= (__uint_as_float(raw[e]) >= 0.f ? 1u : 0u) << e;
-      if (live) *reinterpret_cast<uint32_t*>(a.packed_signs + n * (D / 8) + 4 * part) = bits;
+      if (live) *reinterpret_cast<uint32_t*>(a.packed_signs + no * (D / 8) + 4 * part) = bits;
     }
     tc::fence_before_sync();
     __syncthreads();  // the next tile overwrites the A tiles, the partial sums and the accumulators

@@ -49,6 +49,8 @@ SIGNATURES = {
     "tq_dequantize": (_i, [_p, _l, _i, _p, _i, _p, _p]),
     "tq_compress_keys": (_i, [_p, _i, _l, _l, _l, _i, _l, _l, _l, _p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _p]),
     "tq_compress_values": (_i, [_p, _i, _l, _l, _l, _i, _l, _l, _l, _p, _p, _i, _p, _p, _i, _p]),
+    "tq_append_keys": (_i, [_p, _i, _l, _l, _l, _i, _l, _l, _l, _p, _p, _p, _p, _i, _p, _p, _p, _p, _l, _l, _i, _p]),
+    "tq_append_values": (_i, [_p, _i, _l, _l, _l, _i, _l, _l, _l, _p, _p, _i, _p, _p, _l, _l, _i, _p]),
     "tq_decompress_values": (_i, [_p, _p, _l, _i, _p, _p, _i, _p, _p]),
     "tq_attention_scores": (_i, [_p, _i, _l, _l, _l, _i, _l, _l, _l, _l, _l, _p, _p, _p, _p, _p, _p, _p, _i,
                                  _p, _p, _z, _i, _p]),

@@ -17,7 +17,7 @@ import torch
 
 from . import _lib
 from .compressors import (_DTYPES, _require_cuda, _rows_view, _stream_ptr, TurboQuantCompressorMSE,
-                          TurboQuantCompressorV2, fused_attention)
+                          TurboQuantCompressorV2, fused_attention, resolve_mode)
 
 
 class CompressedKVCache:
@@ -69,15 +69,22 @@ class CompressedKVCache:
                              f"{tuple(keys.shape)} and {tuple(values.shape)}")
         if self.length + S > self.capacity:
             raise ValueError(f"cache holds {self.length} of {self.capacity} tokens; cannot append {S}")
-        ck = self.key_compressor.compress(keys)
-        cv = self.val_compressor.compress(values)
-        t = slice(self.length, self.length + S)
-        self.key_indices[:, :, t] = ck["packed_key_indices"].view(B, H, S, -1)
-        self.key_signs[:, :, t] = ck["packed_qjl_signs"].view(B, H, S, -1)
-        self.key_norms[:, :, t] = ck["vec_norms"].view(B, H, S)
-        self.key_residual_norms[:, :, t] = ck["residual_norm"].view(B, H, S)
-        self.value_indices[:, :, t] = cv["packed_indices"].view(B, H, S, -1)
-        self.value_norms[:, :, t] = cv["vec_norms"].view(B, H, S)
+        _require_cuda(keys, "keys")
+        kc, vc = self.key_compressor, self.val_compressor
+        kc._check_device(keys)
+        vc._check_device(keys)
+        k, v = _rows_view(keys), _rows_view(values)
+        stream = _stream_ptr(k.device)
+        # the compression kernels write their rows straight behind the tokens in use: no scratch, no copies
+        _lib.check(_lib.lib.tq_append_keys(
+            k.data_ptr(), _DTYPES[k.dtype], B, H, S, D, k.stride(0), k.stride(1), k.stride(2),
+            kc.Pi.data_ptr(), kc.S_eff.data_ptr(), kc.centroids.data_ptr(), kc.boundaries.data_ptr(), kc.bits,
+            self.key_indices.data_ptr(), self.key_signs.data_ptr(), self.key_norms.data_ptr(),
+            self.key_residual_norms.data_ptr(), self.capacity, self.length, resolve_mode(k.dtype, kc.mode), stream))
+        _lib.check(_lib.lib.tq_append_values(
+            v.data_ptr(), _DTYPES[v.dtype], B, H, S, D, v.stride(0), v.stride(1), v.stride(2),
+            vc.Pi.data_ptr(), vc.boundaries.data_ptr(), vc.bits, self.value_indices.data_ptr(),
+            self.value_norms.data_ptr(), self.capacity, self.length, resolve_mode(v.dtype, vc.mode), stream))
         self.length += S
 
     def _contiguous_prefix(self) -> tuple[dict, dict]:
