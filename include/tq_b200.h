@@ -171,7 +171,7 @@ int tq_prepare_queries(const void* q, int dtype, int64_t B, int64_t Hq, int64_t 
 /* Scratch bytes tq_attention_scores / tq_attention_fwd need for the given problem. */
 size_t tq_attention_workspace_bytes(int64_t B, int64_t Hq, int64_t Sq, int d, int mode);
 
-/* Decode-sized calls (query rows per KV head (Hq/Hkv)*Sq <= 16, Sk >= 256, d = 128, no mask, TQ_MODE_BF16)
+/* Decode-sized calls (query rows per KV head (Hq/Hkv)*Sq <= 16, Sk >= 256, d = 128, TQ_MODE_BF16)
  * are served by a split-KV kernel that streams the packed bytes once; same arguments, same result.
  * The reference has no counterpart: it disables the KV cache (patch.py:80-81). */
 /* Fused compressed attention: out = softmax(scores*sm_scale + mask) @ V_hat, computed
@@ -231,7 +231,8 @@ int tq_attention_fwd_static(const void* q, int dtype, int64_t B, int64_t Hq, int
  * (batch, KV head) -- key k of pair (b, h) is row (b*Hkv + h)*kv_capacity + k -- of which the
  * first Sk are in use; new tokens are compressed by tq_compress_keys / tq_compress_values and
  * copied behind them.  Served by the split-KV kernel: head_dim 128, (Hq/Hkv)*Sq <= 16 query rows
- * per KV head, TQ_MODE_BF16, no additive mask, any Sk >= 1; other shapes return TQ_ERR_INVALID_ARG.
+ * per KV head, TQ_MODE_BF16, any Sk >= 1 (mask as in tq_attention_fwd); other shapes return
+ * TQ_ERR_INVALID_ARG.
  * Workspace as for tq_attention_fwd in TQ_MODE_BF16. */
 int tq_attention_fwd_cached(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq, int d,
                             int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
@@ -242,6 +243,7 @@ int tq_attention_fwd_cached(const void* q, int dtype, int64_t B, int64_t Hq, int
                             const float* Pi_k, const float* S_eff, const float* centroids_k,
                             const float* Pi_v, const float* centroids_v, int bits,
                             float sm_scale, int causal,
+                            const float* mask, int64_t mask_stride_b, int64_t mask_stride_q,
                             void* out, int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s,
                             void* workspace, size_t workspace_bytes, void* stream);
 

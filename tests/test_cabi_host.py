@@ -96,7 +96,7 @@ def test_cached_attention_argument_checks():
 
     def call(Hq=8, Hkv=2, Sq=1, Sk=64, cap=128, d=128):
         return _lib.lib.tq_attention_fwd_cached(p, 1, 1, Hq, Sq, d, Hq * Sq * d, Sq * d, d, Hkv, Sk, cap,
-                                                p, p, p, p, p, p, p, p, p, p, p, 3, 0.1, 1,
+                                                p, p, p, p, p, p, p, p, p, p, p, 3, 0.1, 1, None, 0, 0,
                                                 p, Hq * Sq * d, Sq * d, d, p, 0, None)
 
     assert call(cap=32) == 1 and "capacity" in _lib.last_error()

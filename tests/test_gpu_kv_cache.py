@@ -72,3 +72,31 @@ def test_cached_attention_against_oracle_any_length(n_keys, Sq):
     cache.length = n
     got = cache.attend(q.cuda(), causal=True)
     assert rel_err(got, want) < 1.5e-2, rel_err(got, want)
+
+
+@pytest.mark.parametrize("Sq", [1, 3])
+def test_cached_attention_with_padding_mask(Sq):
+    """Left-padded batch: an additive mask (the large negative HF builds) over the cache, in place, against the
+    oracle with the same mask."""
+    from turboquant_b200 import CompressedKVCache
+    d, bits, B, Hq, Hkv, n, cap = 128, 3, 2, 8, 2, 500, 640
+    kp, vp = oracle_params(d, bits)
+    kc, vc = device_compressors(d, bits, mode="bf16")
+    k, v, q = _tokens(B, Hkv, n, d, 41), _tokens(B, Hkv, n, d, 42), _tokens(B, Hq, Sq, d, 43)
+    ok, ov = orc.key_compress(k, kp), orc.value_compress(v, vp)
+    mask = torch.zeros(B, 1, Sq, n)
+    mask[1, :, :, :37] = torch.finfo(torch.float32).min   # sequence 1 starts with 37 padding tokens
+    want = oracle_attention_from_packed(q, ok, ov, kp, vp, causal=True, mask=mask)
+    cache = CompressedKVCache(kc, vc, B, Hkv, cap)
+    dk, dv = oracle_key_dict_to_device(ok), oracle_value_dict_to_device(ov)
+    cache.key_indices[:, :, :n] = dk["packed_key_indices"].view(B, Hkv, n, -1)
+    cache.key_signs[:, :, :n] = dk["packed_qjl_signs"].view(B, Hkv, n, -1)
+    cache.key_norms[:, :, :n] = dk["vec_norms"].view(B, Hkv, n)
+    cache.key_residual_norms[:, :, :n] = dk["residual_norm"].view(B, Hkv, n)
+    cache.value_indices[:, :, :n] = dv["packed_indices"].view(B, Hkv, n, -1)
+    cache.value_norms[:, :, :n] = dv["vec_norms"].view(B, Hkv, n)
+    cache.length = n
+    got = cache.attend(q.cuda(), causal=True, attention_mask=mask.cuda())
+    assert rel_err(got, want) < 1.5e-2, rel_err(got, want)
+    unmasked = cache.attend(q.cuda(), causal=True)
+    assert rel_err(got[1], unmasked[1]) > 1e-3  # the mask does something

@@ -65,6 +65,8 @@ struct DecodeArgs {
   const float* cen_v;
   float sm_scale;
   int causal;
+  const float* mask;  // optional additive mask, element (b, s, k) at mask[b * mask_stride_b + s * mask_stride_q + k]
+  int64_t mask_stride_b, mask_stride_q;
   float* part_o;   // [B*Hkv, nsplit, 16, d]
   float* part_ml;  // [B*Hkv, nsplit, 16, 2]  (running maximum, row sum)
   int nsplit, keys_per_split;
@@ -177,7 +179,7 @@ struct Tables {
   static_assert((1 << kShiftK) == kEntryK * kCopiesK && (1 << kShiftV) == 4 * kCopiesV, "table strides");
 };
 
-template <int BITS, int NT>
+template <int BITS, int NT, bool MASK>
 __global__ void __launch_bounds__(kWarps * 32, 4) decode_kernel(const DecodeArgs a) {
   using T = Tables<BITS>;
   constexpr bool kQInRegs = NT == 1;
@@ -363,6 +365,20 @@ __global__ void __launch_bounds__(kWarps * 32, 4) decode_kernel(const DecodeArgs
       __syncwarp();
     }
     const uint8_t* stg = stage_ptr(warp, st);
+    // additive mask of this lane's score elements (query row 8 t + 2 tq + e, keys blk + gq, + 8), loaded ahead of
+    // the decode work that hides its latency
+    float mk[MASK ? NT : 1][4];
+    if constexpr (MASK) {
+#pragma unroll
+      for (int t = 0; t < NT; ++t)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int r = 8 * t + 2 * tq + (i & 1), key = blk + gq + 8 * (i >> 1);
+          mk[t][i] = (r < R && key < (int)a.Sk)
+                         ? __ldg(a.mask + b * a.mask_stride_b + (r % (int)a.Sq) * a.mask_stride_q + key) * kLog2e
+                         : 0.f;
+        }
+    }
     // ============ scores, transposed: S^T (16 keys x 8 query rows per tile); centroid half s1, sign half s2 ============
     float s1[NT][4], s2[NT][4];
 #pragma unroll
@@ -438,6 +454,7 @@ __global__ void __launch_bounds__(kWarps * 32, 4) decode_kernel(const DecodeArgs
         for (int i = 0; i < 4; ++i) {
           const int h = i >> 1, e = i & 1;
           float x = fmaf(s2[t][i], rn[h], s1[t][i] * kn[h]);
+          if constexpr (MASK) x += mk[t][i];
           if (need_mask && blk + gq + 8 * h > row_lim[t][e]) x = -INFINITY;
           s1[t][i] = x;
           mx[t][e] = fmaxf(mx[t][e], x);
@@ -704,7 +721,7 @@ static bool decode_enabled() {
 }
 
 bool decode_applies(const AttnArgs& a, int d) {
-  const bool shape_ok = d == 128 && a.mask == nullptr && a.Hkv > 0 && (a.Hq / a.Hkv) * a.Sq <= kRows;
+  const bool shape_ok = d == 128 && a.Hkv > 0 && (a.Hq / a.Hkv) * a.Sq <= kRows;
   if (a.kv_stride != a.Sk) return shape_ok;  // a persistent cache: the only kernel that reads strided rows
   return decode_enabled() && shape_ok && a.Sk >= 4 * kBlockKeys * kWarps;
 }
@@ -719,7 +736,7 @@ size_t decode_workspace_bytes(int64_t BHq) {
 template <int BITS, int NT>
 static int occupancy_of() {
   int n = 0;
-  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, decode_kernel<BITS, NT>, kWarps * 32, 0);
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, decode_kernel<BITS, NT, false>, kWarps * 32, 0);
   return n > 0 ? n : 1;
 }
 static int resident_ctas(int bits, int nt) {
@@ -786,13 +803,18 @@ int attention_decode(const AttnArgs& a, int64_t B, int bits, const void* q, int 
   float* part_o = static_cast<float*>(part_ws);
   float* part_ml = part_o + (size_t)units * nsplit * kRows * 128;
   DecodeArgs da{static_cast<const __nv_bfloat16*>(q_cat), a.Hq, a.Hkv, a.Sq, a.Sk, a.kv_stride, a.key_idx, a.key_sgn, a.key_vn,
-                a.key_rn, a.val_idx, a.val_vn, a.cen_k, a.cen_v, a.sm_scale, a.causal, part_o, part_ml, nsplit, per};
+                a.key_rn, a.val_idx, a.val_vn, a.cen_k, a.cen_v, a.sm_scale, a.causal, a.mask, a.mask_stride_b,
+                a.mask_stride_q, part_o, part_ml, nsplit, per};
   dim3 grid((unsigned)nsplit, (unsigned)a.Hkv, (unsigned)B);
   {
     ProfScope prof(kProfAttention, stream);
-    void (*kern)(DecodeArgs) =
-        nt == 1 ? (bits == 2 ? decode_kernel<2, 1> : bits == 3 ? decode_kernel<3, 1> : decode_kernel<4, 1>)
-                : (bits == 2 ? decode_kernel<2, 2> : bits == 3 ? decode_kernel<3, 2> : decode_kernel<4, 2>);
+    void (*kern)(DecodeArgs);
+    if (a.mask == nullptr)
+      kern = nt == 1 ? (bits == 2 ? decode_kernel<2, 1, false> : bits == 3 ? decode_kernel<3, 1, false> : decode_kernel<4, 1, false>)
+                     : (bits == 2 ? decode_kernel<2, 2, false> : bits == 3 ? decode_kernel<3, 2, false> : decode_kernel<4, 2, false>);
+    else
+      kern = nt == 1 ? (bits == 2 ? decode_kernel<2, 1, true> : bits == 3 ? decode_kernel<3, 1, true> : decode_kernel<4, 1, true>)
+                     : (bits == 2 ? decode_kernel<2, 2, true> : bits == 3 ? decode_kernel<3, 2, true> : decode_kernel<4, 2, true>);
     TQ_CUDA_OK(launch_dependent(kern, grid, dim3(kWarps * 32), stream, da));
   }
   ProfScope prof(kProfBackRotation, stream);

@@ -699,7 +699,8 @@ extern "C" int tq_attention_fwd_cached(const void* q, int dtype, int64_t B, int6
                                        const uint16_t* key_residual_norms, const uint8_t* val_idx,
                                        const uint16_t* val_vec_norms, const float* Pi_k, const float* S_eff,
                                        const float* centroids_k, const float* Pi_v, const float* centroids_v, int bits,
-                                       float sm_scale, int causal, void* out, int64_t o_stride_b, int64_t o_stride_h,
+                                       float sm_scale, int causal, const float* mask, int64_t mask_stride_b,
+                                       int64_t mask_stride_q, void* out, int64_t o_stride_b, int64_t o_stride_h,
                                        int64_t o_stride_s, void* workspace, size_t workspace_bytes, void* stream) {
   TQ_REQUIRE(kv_capacity >= Sk, "cache capacity %lld is smaller than the %lld keys in use", (long long)kv_capacity,
              (long long)Sk);
@@ -709,8 +710,8 @@ extern "C" int tq_attention_fwd_cached(const void* q, int dtype, int64_t B, int6
   return attention_entry(q, dtype, B, Hq, Sq, d, q_stride_b, q_stride_h, q_stride_s, Hkv, Sk,
                          kv_capacity, key_idx, key_signs, key_vec_norms, key_residual_norms,
                          val_idx, val_vec_norms, Pi_k, S_eff, centroids_k, Pi_v, centroids_v, bits, sm_scale, causal,
-                         nullptr, 0, 0, out, o_stride_b, o_stride_h, o_stride_s, workspace, workspace_bytes,
-                         TQ_MODE_BF16, stream);
+                         mask, mask_stride_b, mask_stride_q, out, o_stride_b, o_stride_h, o_stride_s, workspace,
+                         workspace_bytes, TQ_MODE_BF16, stream);
 }
 
 // ---- attention without caller-supplied scratch ---------------------------------------------

@@ -840,7 +840,7 @@ int attention_fwd_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_t 
 
   const bool decode = decode_applies(a, d) && Sq <= 16;
   TQ_REQUIRE(decode || a.kv_stride == a.Sk,
-             "a cache with capacity %lld > Sk is served by the split-KV kernel only: head_dim 128, no mask, "
+             "a cache with capacity %lld > Sk is served by the split-KV kernel only: head_dim 128, "
              "(Hq / Hkv) * Sq <= 16", (long long)a.kv_stride);
   const bool pairs = d == 128 && use_sm_pairs() && !decode;
   if (decode)  // its own small kernels on both sides of the split-KV kernel; none of the bf16 operand images

@@ -206,6 +206,26 @@ class TurboQuantCompressorMSE(_Constants):
         return out
 
 
+def _mask_args(attention_mask, B: int, Sq: int, Sk: int, dev):
+    """An additive mask broadcastable to [B, 1, Sq, Sk] as (tensor, pointer, batch stride, row stride) of an
+    fp32 tensor with unit inner stride; (None, None, 0, 0) for no mask."""
+    if attention_mask is None:
+        return None, None, 0, 0
+    mk = attention_mask
+    if mk.dim() == 4:
+        if mk.shape[1] != 1:
+            raise ValueError("per-head masks are not supported; expected [B, 1, Sq, Sk]")
+        mk = mk[:, 0]
+    elif mk.dim() == 2:
+        mk = mk.unsqueeze(0)
+    mk = mk.to(device=dev, dtype=torch.float32)
+    if mk.shape[-2:] != (Sq, Sk) or mk.shape[0] not in (1, B):
+        raise ValueError(f"mask shape {tuple(attention_mask.shape)} does not broadcast to [B,1,{Sq},{Sk}]")
+    if mk.stride(-1) != 1:
+        mk = mk.contiguous()
+    return mk, mk.data_ptr(), (mk.stride(0) if mk.shape[0] == B and B > 1 else 0), mk.stride(1)
+
+
 @torch.no_grad()
 def fused_attention(q: torch.Tensor, compressed_k: dict, compressed_v: dict,
                     key_compressor: TurboQuantCompressorV2, val_compressor: TurboQuantCompressorMSE,
@@ -233,21 +253,7 @@ def fused_attention(q: torch.Tensor, compressed_k: dict, compressed_v: dict,
     out = torch.empty((B, Hq, Sq, D), dtype=qv.dtype, device=dev)
     ws_bytes = _lib.lib.tq_attention_workspace_bytes(B, Hq, Sq, D, m)
     ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
-    mask_ptr, msb, msq = None, 0, 0
-    if attention_mask is not None:
-        mk = attention_mask
-        if mk.dim() == 4:
-            if mk.shape[1] != 1:
-                raise ValueError("per-head masks are not supported; expected [B, 1, Sq, Sk]")
-            mk = mk[:, 0]
-        elif mk.dim() == 2:
-            mk = mk.unsqueeze(0)
-        mk = mk.to(device=dev, dtype=torch.float32)
-        if mk.shape[-2:] != (Sq, Sk) or mk.shape[0] not in (1, B):
-            raise ValueError(f"mask shape {tuple(attention_mask.shape)} does not broadcast to [B,1,{Sq},{Sk}]")
-        if mk.stride(-1) != 1:
-            mk = mk.contiguous()
-        mask_ptr, msb, msq = mk.data_ptr(), (mk.stride(0) if mk.shape[0] == B and B > 1 else 0), mk.stride(1)
+    mk, mask_ptr, msb, msq = _mask_args(attention_mask, B, Sq, Sk, dev)  # mk keeps the converted mask alive
     scale = float(sm_scale) if sm_scale is not None else 1.0 / math.sqrt(D)
     _lib.check(_lib.lib.tq_attention_fwd(
         qv.data_ptr(), _DTYPES[qv.dtype], B, Hq, Sq, D, qv.stride(0), qv.stride(1), qv.stride(2), Hkv, Sk,

@@ -16,7 +16,7 @@ import math
 import torch
 
 from . import _lib
-from .compressors import (_DTYPES, _require_cuda, _rows_view, _stream_ptr, TurboQuantCompressorMSE,
+from .compressors import (_DTYPES, _mask_args, _require_cuda, _rows_view, _stream_ptr, TurboQuantCompressorMSE,
                           TurboQuantCompressorV2, fused_attention, resolve_mode)
 
 
@@ -103,8 +103,9 @@ class CompressedKVCache:
         """softmax(scores * sm_scale) @ V_hat of q [B, Hq, Sq, D] over the tokens in use; with `causal` the
         queries are the last Sq positions (append their keys first).  Returns [B, Hq, Sq, D] in q.dtype.
 
-        Decode-sized calls (head_dim 128, (Hq / Hkv) * Sq <= 16, 16-bit queries, no additive mask) read the
-        cache in place; anything else gathers the prefix once and takes the prefill kernels."""
+        `attention_mask` is an optional additive mask broadcastable to [B, 1, Sq, tokens in use] (padding).
+        Decode-sized calls (head_dim 128, (Hq / Hkv) * Sq <= 16, 16-bit queries) read the cache in place;
+        anything else gathers the prefix once and takes the prefill kernels."""
         _require_cuda(q, "q")
         B, Hq, Sq, D = q.shape
         if (B, D) != (self.batch, self.head_dim) or Hq % self.kv_heads != 0:
@@ -112,7 +113,7 @@ class CompressedKVCache:
         if self.length == 0:
             raise ValueError("attention over an empty cache is undefined")
         in_place = (D == 128 and (Hq // self.kv_heads) * Sq <= 16 and q.dtype in (torch.bfloat16, torch.float16)
-                    and self.key_compressor.mode in (None, "bf16") and attention_mask is None)
+                    and self.key_compressor.mode in (None, "bf16"))
         if not in_place:
             ck, cv = self._contiguous_prefix()
             return fused_attention(q, ck, cv, self.key_compressor, self.val_compressor, causal=causal,
@@ -126,12 +127,14 @@ class CompressedKVCache:
         ws_bytes = _lib.lib.tq_attention_workspace_bytes(B, Hq, Sq, D, _lib.TQ_MODE_BF16)
         ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
         scale = float(sm_scale) if sm_scale is not None else 1.0 / math.sqrt(D)
+        mk, mask_ptr, msb, msq = _mask_args(attention_mask, B, Sq, self.length, dev)  # mk keeps the mask alive
         _lib.check(_lib.lib.tq_attention_fwd_cached(
             qv.data_ptr(), _DTYPES[qv.dtype], B, Hq, Sq, D, qv.stride(0), qv.stride(1), qv.stride(2),
             self.kv_heads, self.length, self.capacity,
             self.key_indices.data_ptr(), self.key_signs.data_ptr(), self.key_norms.data_ptr(),
             self.key_residual_norms.data_ptr(), self.value_indices.data_ptr(), self.value_norms.data_ptr(),
             kc.Pi.data_ptr(), kc.S_eff.data_ptr(), kc.centroids.data_ptr(), vc.Pi.data_ptr(), vc.centroids.data_ptr(),
-            kc.bits, scale, 1 if causal else 0, out.data_ptr(), out.stride(0), out.stride(1), out.stride(2),
+            kc.bits, scale, 1 if causal else 0, mask_ptr, msb, msq,
+            out.data_ptr(), out.stride(0), out.stride(1), out.stride(2),
             ws.data_ptr(), ws.numel(), _stream_ptr(dev)))
         return out
