@@ -249,3 +249,22 @@ def test_compress_and_attention_replay_from_a_cuda_graph(Sq):
     torch.cuda.synchronize()
     assert torch.equal(out_g, run())
 
+
+
+@pytest.mark.parametrize("Hq,Hkv,Sq", [(2, 2, 1), (4, 2, 8), (16, 1, 1), (8, 1, 2), (3, 3, 5)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_decode_kernel_group_sizes_and_dtypes(Hq, Hkv, Sq, dtype):
+    """The split-KV kernel over the group sizes and row counts it accepts (1 to 16 query rows per KV head, one or
+    two tiles of eight), fp16 and bf16 queries, a key count that is odd and not a multiple of the block."""
+    d, bits, B, Sk = 128, 3, 2, 1531
+    q, k, v = _case(B, Hq, Hkv, Sq, Sk, d, seed=7 * Hq + Sq, dtype=torch.float32)
+    kp, vp = oracle_params(d, bits)
+    ok, ov = orc.key_compress(k, kp), orc.value_compress(v, vp)
+    q = q.to(dtype)
+    want = oracle_attention_from_packed(q, ok, ov, kp, vp, causal=True)
+    from turboquant_b200 import fused_attention
+    kc, vc = device_compressors(d, bits, mode="bf16")
+    out = fused_attention(q.cuda(), oracle_key_dict_to_device(ok), oracle_value_dict_to_device(ov), kc, vc,
+                          causal=True, mode="bf16")
+    assert out.dtype == dtype
+    assert rel_err(out, want) < 1.5e-2, rel_err(out, want)
