@@ -100,3 +100,20 @@ def test_cached_attention_with_padding_mask(Sq):
     assert rel_err(got, want) < 1.5e-2, rel_err(got, want)
     unmasked = cache.attend(q.cuda(), causal=True)
     assert rel_err(got[1], unmasked[1]) > 1e-3  # the mask does something
+
+
+def test_fully_masked_row_averages_uniformly():
+    """A query row that sees only masked keys (a padding position) gets the uniform average of the values, as
+    with the prefill kernels and a softmax over equal finite scores -- not NaN and not zero."""
+    from turboquant_b200 import CompressedKVCache, fused_attention
+    d, bits, B, Hq, Hkv, n = 128, 3, 1, 4, 2, 320
+    kc, vc = device_compressors(d, bits, mode="bf16")
+    k, v, q = _tokens(B, Hkv, n, d, 51).cuda(), _tokens(B, Hkv, n, d, 52).cuda(), _tokens(B, Hq, 1, d, 53).cuda()
+    cache = CompressedKVCache(kc, vc, B, Hkv, 400)
+    cache.append(k, v)
+    mask = torch.full((B, 1, 1, n), torch.finfo(torch.float32).min, device="cuda")
+    got = cache.attend(q, causal=True, attention_mask=mask)
+    assert torch.isfinite(got).all()
+    # uniform weights: every query head of a KV head gets the same mean of the decompressed values
+    want = vc.decompress(vc.compress(v)).mean(dim=2, keepdim=True).repeat_interleave(Hq // Hkv, dim=1)
+    assert rel_err(got, want) < 2e-2, rel_err(got, want)

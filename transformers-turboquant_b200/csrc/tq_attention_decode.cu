@@ -374,8 +374,11 @@ __global__ void __launch_bounds__(kWarps * 32, 4) decode_kernel(const DecodeArgs
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int r = 8 * t + 2 * tq + (i & 1), key = blk + gq + 8 * (i >> 1);
+          // kept finite, as the large negative value HF masks with is: a row whose keys are all masked then
+          // averages them uniformly, as it does in the prefill kernels and in the reference's softmax
           mk[t][i] = (r < R && key < (int)a.Sk)
-                         ? __ldg(a.mask + b * a.mask_stride_b + (r % (int)a.Sq) * a.mask_stride_q + key) * kLog2e
+                         ? fmaxf(__ldg(a.mask + b * a.mask_stride_b + (r % (int)a.Sq) * a.mask_stride_q + key) * kLog2e,
+                                 -3.0e38f)
                          : 0.f;
         }
     }
