@@ -122,19 +122,6 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait_all_but() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-// table look-ups by 32-bit shared address (the tables are written once, before the barrier that ends set-up,
-// and every address depends on packed data loaded after it)
-__device__ __forceinline__ uint2 lds64(uint32_t addr) {
-  uint2 v;
-  asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
-  uint32_t v;
-  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-  return v;
-}
 // (field << SH) for the NBITS-bit field at compile-time bit BIT of a little-endian word array: the byte offset of
 // entry `field` in a table whose entries are 2^SH bytes apart.  One shift and one mask; a funnel shift first
 // when the field straddles two words.
@@ -239,9 +226,9 @@ __global__ void __launch_bounds__(kWarps * 32, 4) decode_kernel(const DecodeArgs
                                                        ((tid & 4) ? pos : neg) | (((tid & 8) ? pos : neg) << 16));
     }
   }
-  // a look-up address is (table address) + (lane's copy | entry): the first is a constant of the build that the
-  // load takes as its immediate, the second one three-input logic operation on the shifted packed word
-  const uint32_t lutK_base = smem_u32(lutK), lutV_base = smem_u32(lutV), lutS_base = smem_u32(lutS);
+  // a look-up address is (table address) + (lane's copy | entry): the tables are indexed as plain static shared
+  // arrays, so the first term is the load's immediate; the second is one three-input logic operation on the
+  // shifted packed word.  (Loads through an explicit 32-bit shared address cost one more add per look-up.)
   const uint32_t lane4 = (uint32_t)(lane * 4), laneV = (uint32_t)((lane % T::kCopiesV) * 4);
   const uint32_t laneK = (uint32_t)((lane % T::kCopiesK) * T::kEntryK);
 
@@ -416,14 +403,14 @@ __global__ void __launch_bounds__(kWarps * 32, 4) decode_kernel(const DecodeArgs
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           if constexpr (ks >= 8) {
-            const uint2 e = lds64(lutS_base + scaled_field<4 * j, 4, 3>(sg[h]));
+            const uint2 e = *reinterpret_cast<const uint2*>(lutS + scaled_field<4 * j, 4, 3>(sg[h]));
             ka[h] = e.x; ka[2 + h] = e.y;
           } else if constexpr (T::kQuad) {
-            const uint2 e = lds64(lutK_base + (laneK | scaled_field<4 * KB * j, 4 * KB, T::kShiftK>(kw[h])));
+            const uint2 e = *reinterpret_cast<const uint2*>(lutK + (laneK | scaled_field<4 * KB * j, 4 * KB, T::kShiftK>(kw[h])));
             ka[h] = e.x; ka[2 + h] = e.y;
           } else {
-            ka[h] = lds32(lutK_base + (lane4 | scaled_field<4 * KB * j, 2 * KB, T::kShiftK>(kw[h])));
-            ka[2 + h] = lds32(lutK_base + (lane4 | scaled_field<4 * KB * j + 2 * KB, 2 * KB, T::kShiftK>(kw[h])));
+            ka[h] = *reinterpret_cast<const uint32_t*>(lutK + (lane4 | scaled_field<4 * KB * j, 2 * KB, T::kShiftK>(kw[h])));
+            ka[2 + h] = *reinterpret_cast<const uint32_t*>(lutK + (lane4 | scaled_field<4 * KB * j + 2 * KB, 2 * KB, T::kShiftK>(kw[h])));
           }
         }
 #pragma unroll
@@ -541,7 +528,7 @@ __global__ void __launch_bounds__(kWarps * 32, 4) decode_kernel(const DecodeArgs
         uint32_t e[4];
 #pragma unroll
         for (int kq = 0; kq < 4; ++kq)
-          e[kq] = lds32(lutV_base + (laneV | scaled_field<2 * VB * ct, 2 * VB, T::kShiftV>(vw[kq])));
+          e[kq] = *reinterpret_cast<const uint32_t*>(lutV + (laneV | scaled_field<2 * VB * ct, 2 * VB, T::kShiftV>(vw[kq])));
         const uint32_t va[4] = {__byte_perm(e[0], e[1], 0x5410), __byte_perm(e[0], e[1], 0x7632),
                                 __byte_perm(e[2], e[3], 0x5410), __byte_perm(e[2], e[3], 0x7632)};
 #pragma unroll
