@@ -2,9 +2,12 @@
  * tq_b200.h -- C ABI of the B200 (sm_100a) TurboQuant KV-compression and
  * compressed-attention library (libtq_b200.so).
  *
- * Everything here takes plain pointers and sizes.  All data pointers are DEVICE
- * pointers on the current CUDA device unless a parameter says "host".  `stream`
- * is a cudaStream_t passed as void* (NULL = the legacy default stream).  Every
+ * Everything here takes plain pointers and sizes.  All data pointers of a call are DEVICE
+ * pointers on ONE CUDA device unless a parameter says "host"; that device need not be the
+ * thread's current one: an entry point finds the owner of its first data pointer, makes it
+ * current for the duration of the call and restores the previous device (`stream` must
+ * belong to the same device).  `stream` is a cudaStream_t passed as void* (NULL = the legacy
+ * default stream).  Every
  * entry point validates its arguments on the host and returns a tq_status; on
  * anything but TQ_OK no kernel was launched and tq_last_error() describes the
  * problem.  No entry point allocates or frees device memory; scratch space is
@@ -54,9 +57,26 @@ int tq_version(void);
 /* Message of the last failing call made by this host thread ("" if none). */
 const char* tq_last_error(void);
 
-/* Number of bounded device-side waits that have expired since the library was
- * loaded (0 in a healthy process).  Reads a device counter; synchronises `stream`. */
+/* Number of bounded device-side waits that have expired on the current device since the library was
+ * loaded (0 in a healthy process).  Reads a device counter; synchronises `stream`.
+ *
+ * Status contract: a kernel whose bounded wait expires unwinds cleanly and raises a flag in a page of host
+ * memory (static storage of the library, pinned and mapped by the first call made on a device outside stream
+ * capture; nothing is allocated).  From then on every launching entry point called for that device returns
+ * TQ_ERR_DEVICE_WAIT without launching anything -- the check is one read of host memory, so it costs no
+ * synchronisation and is legal during stream capture.  The call whose own kernel gave up has already returned
+ * TQ_OK (launches are asynchronous); its output, and that of calls queued before the flag was seen, is invalid. */
 int tq_device_fault_count(void* stream, int64_t* count_host);
+
+/* Self-test of the expiry path of the bounded device-side waits (no counterpart in the reference).  Launches one
+ * tiny CTA on the current device that waits, with the same bounded wait the attention and compression kernels
+ * use, for an mbarrier nobody arrives on, with a limit of `limit_cycles` SM clocks (1e3 .. 2e9).  The wait gives
+ * up, the kernel returns normally and reports the expiry to the host through the library's status page; the call
+ * synchronises `stream` and then returns TQ_ERR_DEVICE_WAIT with a tq_last_error() text -- the same status every
+ * launching entry point returns once a production kernel has given up a wait.  The self-test uses a flag of its
+ * own: tq_device_fault_count stays 0 and later calls are not refused.  `waited_cycles_host` (optional) receives
+ * the SM clocks the wait lasted.  TQ_ERR_UNSUPPORTED when the status page could not be pinned. */
+int tq_selftest_wait_expiry(void* stream, int64_t limit_cycles, int64_t* waited_cycles_host);
 
 /* Per-kernel device timing for benchmarks (no counterpart in the reference).  Between
  * tq_profile_begin and tq_profile_end every launch of the kernel kinds below is bracketed
@@ -81,6 +101,8 @@ int tq_profile_end(float* ms_sum_host, int* launches_host);
  * roles: tag = role << 32 | event << 16 | key tile.  tq_trace_read synchronises the device
  * and copies the first max_records slots of the 4096-slot buffer (2 int64 each; each role owns
  * one third of the slots, unused slots carry tag -1) to the host. */
+/* The tracing instantiations are compiled only by `build.py --trace`; in the default build tq_trace_enable(1)
+ * returns TQ_ERR_UNSUPPORTED. */
 int tq_trace_enable(int on);
 int tq_trace_read(int64_t* records_host, int max_records, int* n_host);
 

@@ -136,8 +136,15 @@ def test_fused_attention_additive_mask_and_noncausal(mode):
     dk, dv = oracle_key_dict_to_device(ok), oracle_value_dict_to_device(ov)
     want = oracle_attention_from_packed(q, ok, ov, kp, vp, causal=True, mask=mask)
     out = fused_attention(q.cuda(), dk, dv, kc, vc, causal=True, attention_mask=mask.cuda(), mode=mode)
-    # rows of batch 1 that only see padding are a uniform average in both implementations
     assert rel_err(out[:, :, 17:], want[:, :, 17:]) < TOL[mode]
+    # Rows 0..16 of batch 1 see only masked keys.  Their softmax runs over equal finite scores, so the row is a
+    # uniform average: of the keys the causal rule leaves visible here, of all keys in the reference (whose
+    # causal mask is the same finite value).  Such rows are padding positions; what matters is that they are
+    # finite and that both kernels (prefill and split-KV) treat them the same way.
+    vals = orc.values_from_packed(ov["packed_indices"], ov["vec_norms"], vp, ov["shape"])  # [B, Hkv, S, d]
+    for row in (0, 5, 16):
+        uniform = vals[1, :, :row + 1].mean(dim=1)                                         # [Hkv, d]
+        assert rel_err(out[1, :, row], uniform) < 2e-2, (row, rel_err(out[1, :, row], uniform))
     want_nc = oracle_attention_from_packed(q, ok, ov, kp, vp, causal=False)
     out_nc = fused_attention(q.cuda(), dk, dv, kc, vc, causal=False, mode=mode)
     assert rel_err(out_nc, want_nc) < TOL[mode]
@@ -268,3 +275,129 @@ def test_decode_kernel_group_sizes_and_dtypes(Hq, Hkv, Sq, dtype):
                           causal=True, mode="bf16")
     assert out.dtype == dtype
     assert rel_err(out, want) < 1.5e-2, rel_err(out, want)
+
+
+def _oracle_rows(q, ck, cv, kp, vp, b, h, hk, rows, S, d):
+    """Oracle attention output of query rows `rows` (a slice) of head h of batch b, from the product's own packed
+    bytes of KV head hk: scores over all S keys, causal mask, softmax, P @ V_hat."""
+    Hkv = ck["shape"][1]
+    sel = slice((b * Hkv + hk) * S, (b * Hkv + hk + 1) * S)
+    sc = orc.scores_from_packed(q[b:b + 1, h:h + 1, rows].float().cpu(), ck["packed_key_indices"][sel].cpu().numpy(),
+                                ck["packed_qjl_signs"][sel].cpu().numpy(), ck["vec_norms"][b, hk].cpu(),
+                                ck["residual_norm"][b, hk].cpu(), kp, (1, 1, S, d))
+    vals = orc.values_from_packed(cv["packed_indices"][sel].cpu().numpy(), cv["vec_norms"][sel].cpu(), vp, (1, 1, S, d))
+    return torch.softmax(sc / d ** 0.5 + orc.causal_mask(S, S)[rows], -1) @ vals
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4])
+def test_benchmark_shape_s8192_slices_against_oracle(bits):
+    """The benchmarked configuration itself (32 query / 8 KV heads, S = 8192, bf16, four key channels per head
+    scaled x8 -- the generator of bench.py), one batch element: rows from the end, the middle and the first tile
+    of three heads against the oracle, all bit widths."""
+    import bench
+    from turboquant_b200 import fused_attention
+    d, S = 128, 8192
+    q, k, v = bench.make_inputs(1, S, torch.device("cuda"), seed=0)
+    kc, vc = device_compressors(d, bits)
+    ck, cv = kc.compress(k), vc.compress(v)
+    out = fused_attention(q, ck, cv, kc, vc, causal=True, mode="bf16")
+    kp, vp = oracle_params(d, bits)
+    for h, rows in ((31, slice(S - 32, S)), (13, slice(4100, 4132)), (0, slice(0, 32)), (6, slice(127, 130))):
+        want = _oracle_rows(q, ck, cv, kp, vp, 0, h, h // 4, rows, S, d)
+        err = rel_err(out[0:1, h:h + 1, rows], want)
+        assert err < TOL["bf16"], (bits, h, rows, err)
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4])
+def test_scaling_shape_s32768_slices_against_oracle(bits):
+    """S = 32768, the sequence length of the multi-GPU scaling configuration: 256 key tiles per query tile, so the
+    staging rings and barrier phases wrap four times as often as at S = 8192.  One batch element with two KV
+    heads and their eight query heads; rows near the end (all tiles), in the middle and at a ring wrap-around."""
+    from turboquant_b200 import fused_attention
+    d, S, Hq, Hkv = 128, 32768, 8, 2
+    g = torch.Generator(device="cuda").manual_seed(11)
+    q = torch.randn(1, Hq, S, d, generator=g, device="cuda").to(torch.bfloat16)
+    k = torch.randn(1, Hkv, S, d, generator=g, device="cuda").to(torch.bfloat16)
+    v = torch.randn(1, Hkv, S, d, generator=g, device="cuda").to(torch.bfloat16)
+    kc, vc = device_compressors(d, bits)
+    ck, cv = kc.compress(k), vc.compress(v)
+    out = fused_attention(q, ck, cv, kc, vc, causal=True, mode="bf16")
+    assert torch.isfinite(out.float()).all()
+    kp, vp = oracle_params(d, bits)
+    for h, rows in ((7, slice(S - 32, S)), (2, slice(20000, 20016)), (5, slice(128 * 3 * 17, 128 * 3 * 17 + 8))):
+        want = _oracle_rows(q, ck, cv, kp, vp, 0, h, h // 4, rows, S, d)
+        err = rel_err(out[0:1, h:h + 1, rows], want)
+        assert err < TOL["bf16"], (bits, h, rows, err)
+
+
+def test_boolean_mask_means_visible():
+    """HF's sdpa path hands over a boolean mask (True = visible) for padded batches; it must act as the additive
+    mask with the large negative value at the False entries, in the prefill and in the split-KV kernel."""
+    from turboquant_b200 import fused_attention
+    d, bits, B, S = 128, 3, 2, 300
+    q, k, v = _case(B, 4, 2, S, S, d, seed=21, dtype=torch.bfloat16)
+    kc, vc = device_compressors(d, bits, mode="bf16")
+    ck, cv = kc.compress(k.cuda()), vc.compress(v.cuda())
+    keep = torch.ones(B, 1, S, S, dtype=torch.bool)
+    keep[1, :, :, :23] = False
+    additive = torch.zeros(B, 1, S, S).masked_fill_(~keep, torch.finfo(torch.float32).min)
+    a = fused_attention(q.cuda(), ck, cv, kc, vc, causal=True, attention_mask=keep.cuda())
+    b2 = fused_attention(q.cuda(), ck, cv, kc, vc, causal=True, attention_mask=additive.cuda())
+    assert torch.equal(a, b2)
+    assert rel_err(a[1, :, 23:], fused_attention(q.cuda(), ck, cv, kc, vc, causal=True)[1, :, 23:]) > 1e-3
+    # decode-sized: the last query row against all keys
+    a1 = fused_attention(q[:, :, -1:].cuda(), ck, cv, kc, vc, causal=True, attention_mask=keep[:, :, -1:].cuda())
+    b1 = fused_attention(q[:, :, -1:].cuda(), ck, cv, kc, vc, causal=True, attention_mask=additive[:, :, -1:].cuda())
+    assert torch.equal(a1, b1)
+    with pytest.raises(TypeError):
+        fused_attention(q.cuda(), ck, cv, kc, vc, causal=True, attention_mask=keep.long().cuda())
+
+
+def test_expired_device_wait_is_reported_as_a_status():
+    """The expiry path of the bounded waits, exercised safely: a one-CTA self-test kernel waits (with the wait the
+    production kernels use and a short limit) for a barrier nobody arrives on, gives up, returns normally and
+    raises the host-visible flag; the host turns that into TQ_ERR_DEVICE_WAIT and an error text.  The self-test
+    has a flag of its own: the production fault counter stays 0 and later calls run."""
+    import ctypes
+    import time
+    from turboquant_b200 import _lib, device_fault_count, fused_attention
+    kc, vc = device_compressors(128, 3, mode="bf16")
+    q, k, v = (t.cuda() for t in _case(1, 2, 1, 64, 64, 128, seed=1, dtype=torch.bfloat16))
+    fused_attention(q, kc.compress(k), vc.compress(v), kc, vc)   # the first call on the device installs the status page
+    torch.cuda.synchronize()
+    waited = ctypes.c_int64(0)
+    t0 = time.perf_counter()
+    st = _lib.lib.tq_selftest_wait_expiry(torch.cuda.current_stream().cuda_stream, 200_000, ctypes.byref(waited))
+    elapsed = time.perf_counter() - t0
+    assert st == 5, (st, _lib.last_error())                       # TQ_ERR_DEVICE_WAIT
+    assert "gave up" in _lib.last_error() and "self-test" in _lib.last_error()
+    assert 200_000 <= waited.value < 50_000_000, waited.value     # it did wait for the limit, and not much longer
+    assert elapsed < 1.0, elapsed
+    with pytest.raises(_lib.TurboQuantError) as exc:
+        _lib.check(st)
+    assert exc.value.status == 5
+    assert device_fault_count() == 0                              # the production counter is untouched
+    out = fused_attention(q, kc.compress(k), vc.compress(v), kc, vc)   # and later calls are served
+    assert torch.isfinite(out.float()).all()
+
+
+def test_tensors_on_a_device_that_is_not_current():
+    """A model on cuda:1 while the thread's current device is cuda:0 (device_map splits, a second replica in one
+    process): every entry point runs on the device that owns its tensors and leaves the current device alone."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from turboquant_b200 import TurboQuantCompressorMSE, TurboQuantCompressorV2, device_fault_count, fused_attention
+    d, bits = 128, 3
+    q, k, v = _case(1, 4, 2, 200, 200, d, seed=9, dtype=torch.bfloat16)
+    outs = []
+    for dev in ("cuda:0", "cuda:1"):
+        torch.cuda.set_device(0)
+        kc = TurboQuantCompressorV2(d, bits, 42, device=dev)
+        vc = TurboQuantCompressorMSE(d, bits, 10042, device=dev)
+        qd, kd, vd = (t.to(dev) for t in (q, k, v))
+        out = fused_attention(qd, kc.compress(kd), vc.compress(vd), kc, vc, causal=True)
+        dec = fused_attention(qd[:, :, -1:], kc.compress(kd), vc.compress(vd), kc, vc, causal=True)
+        assert out.device == torch.device(dev) and torch.cuda.current_device() == 0
+        outs.append((out.cpu(), dec.cpu()))
+        assert device_fault_count(dev) == 0
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])

@@ -6,54 +6,15 @@ import copy
 
 import pytest
 import torch
-import torch.nn as nn
 
 from helpers import rel_err
-from oracle import tq_oracle as orc
+from oracle.model_oracle import oracle_model
 
 pytestmark = pytest.mark.gpu
 
 
-class OracleCore(nn.Module):
-    """Replaces an HF attention module on the CPU; projections are the original module's, the
-    attention core is oracle.attention_core (families/llama.py:100-114, gpt2.py:90-110)."""
-
-    def __init__(self, original, kind, layer, bits, seed):
-        super().__init__()
-        self.o, self.kind = original, kind
-        ks, vs = orc.layer_seeds(seed, layer)
-        d = original.head_dim
-        self.kp, self.vp = orc.make_key_params(d, bits, ks), orc.make_value_params(d, bits, vs)
-
-    def forward(self, hidden_states, position_embeddings=None, attention_mask=None, **kw):
-        o = self.o
-        B, T, _ = hidden_states.shape
-        if self.kind == "gpt2":
-            q, k, v = o.c_attn(hidden_states).split(o.embed_dim, dim=2)
-            shp = (B, T, -1, o.head_dim)
-            q, k, v = (t.view(shp).transpose(1, 2) for t in (q, k, v))
-        else:
-            from transformers.models.llama.modeling_llama import apply_rotary_pos_emb
-            shp = (B, T, -1, o.head_dim)
-            q = o.q_proj(hidden_states).view(shp).transpose(1, 2)
-            k = o.k_proj(hidden_states).view(shp).transpose(1, 2)
-            v = o.v_proj(hidden_states).view(shp).transpose(1, 2)
-            q, k = apply_rotary_pos_emb(q, k, *position_embeddings)
-        out, _ = orc.attention_core(q, k, v, self.kp, self.vp, mask=orc.causal_mask(T, T), literal=True)
-        out = out.transpose(1, 2).reshape(B, T, -1)
-        return (o.c_proj(out) if self.kind == "gpt2" else o.o_proj(out)), None
-
-
 def _oracle_model(model, cls_name, kind, bits, seed):
-    ref = copy.deepcopy(model)
-    layer = 0
-    for _, parent in list(ref.named_modules()):
-        for name, child in list(parent.named_children()):
-            if type(child).__name__ == cls_name:
-                setattr(parent, name, OracleCore(child, kind, layer, bits, seed))
-                layer += 1
-    assert layer > 0
-    return ref
+    return oracle_model(model, cls_name, kind, bits, seed)
 
 
 def _build(kind):

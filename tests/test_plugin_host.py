@@ -114,3 +114,24 @@ def test_unsupported_model_type_raises():
     with pytest.raises(UnsupportedModelError):
         apply_turboquant(BertModel(BertConfig(hidden_size=32, num_attention_heads=2, num_hidden_layers=1,
                                               intermediate_size=32, vocab_size=32)))
+
+
+def test_mask_forms_accepted_by_the_attention_wrapper():
+    """Boolean masks mean True = visible (HF's sdpa path), floating-point masks are additive (its eager path),
+    integer masks are refused because their meaning would be a guess."""
+    import pytest
+    import torch
+    from turboquant_b200.compressors import _mask_args
+    keep = torch.ones(2, 1, 3, 5, dtype=torch.bool)
+    keep[1, 0, :, :2] = False
+    mk, ptr, sb, sq = _mask_args(keep, 2, 3, 5, "cpu")
+    assert mk.dtype == torch.float32 and mk.shape == (2, 3, 5) and (sb, sq) == (15, 5) and ptr == mk.data_ptr()
+    assert torch.equal(mk == 0, keep[:, 0]) and float(mk[1, 0, 0]) == torch.finfo(torch.float32).min
+    add = torch.zeros(1, 1, 3, 5, dtype=torch.float16)
+    mk, _, sb, _ = _mask_args(add, 2, 3, 5, "cpu")
+    assert mk.dtype == torch.float32 and sb == 0            # broadcast over the batch
+    with pytest.raises(TypeError):
+        _mask_args(keep.long(), 2, 3, 5, "cpu")
+    with pytest.raises(ValueError):
+        _mask_args(torch.zeros(2, 4, 3, 5), 2, 3, 5, "cpu")  # per-head masks
+    assert _mask_args(None, 2, 3, 5, "cpu") == (None, None, 0, 0)

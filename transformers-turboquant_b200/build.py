@@ -1,11 +1,13 @@
 """Build libtq_b200.so (CUDA kernels + C ABI) for sm_100a with nvcc, in-tree.
 
-    python transformers-turboquant_b200/build.py [--force] [--verbose]
+    python transformers-turboquant_b200/build.py [--force] [--verbose] [--trace]
 
 Each csrc/*.cu is compiled to an object in build/ (only when its sources changed) and
 the objects are linked into turboquant_b200/libtq_b200.so.  nvcc cross-compiles, so no
 GPU is needed.  `-Xptxas -v` output (registers, spills, shared memory per kernel) is
-kept in build/ptxas_<file>.log.
+kept in build/ptxas_<file>.log.  `--trace` (implies a full rebuild) adds the diagnostic
+instantiations of the attention kernels that tq_trace_enable / tq_trace_read need; the
+default product build leaves them out.
 """
 
 from __future__ import annotations
@@ -29,8 +31,18 @@ def _newest(paths):
     return max(os.path.getmtime(p) for p in paths)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, trace: bool = False) -> str:
     os.makedirs(BUILD, exist_ok=True)
+    flags = FLAGS + (["-DTQ_B200_TRACE=1"] if trace else [])
+    # a library built with tracing is a different product: switching the option rebuilds everything
+    stamp = os.path.join(BUILD, "trace.flag")
+    had_trace = os.path.exists(stamp)
+    if trace != had_trace:
+        force = True
+        if trace:
+            open(stamp, "w").close()
+        else:
+            os.remove(stamp)
     sources = sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cuh")]
     headers.append(os.path.join(INCLUDE, "tq_b200.h"))
@@ -41,7 +53,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         path = os.path.join(CSRC, src)
         if not force and os.path.exists(obj) and os.path.getmtime(obj) > max(os.path.getmtime(path), hdr_time):
             return obj, False
-        res = subprocess.run([NVCC, *FLAGS, "-c", path, "-o", obj], capture_output=True, text=True)
+        res = subprocess.run([NVCC, *flags, "-c", path, "-o", obj], capture_output=True, text=True)
         with open(os.path.join(BUILD, f"ptxas_{src[:-3]}.log"), "w") as fh:
             fh.write(res.stderr)
         if res.returncode != 0:
@@ -62,4 +74,4 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, trace="--trace" in sys.argv))

@@ -44,6 +44,12 @@
 namespace tq {
 
 __device__ unsigned long long g_c2_faults = 0ull;
+// this device's slot of the host-visible status page (NULL until the first call on the device installs it)
+__device__ unsigned long long* g_fault_mailbox_c2 = nullptr;
+int set_fault_mailbox_c2(unsigned long long* slot) {
+  TQ_CUDA_OK(cudaMemcpyToSymbol(g_fault_mailbox_c2, &slot, sizeof(slot)));
+  return TQ_OK;
+}
 
 int read_c2_faults(unsigned long long* out) {
   TQ_CUDA_OK(cudaMemcpyFromSymbol(out, g_c2_faults, sizeof(*out)));
@@ -392,7 +398,11 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
         for (int c = 0; c < HC; ++c) {
           const int k = kc0 + c;
           float v = t[c] * cexp;
-          if (mrow != nullptr && k < a.Sk) v = fmaf(mrow[c], kLog2e, v);
+          // The large negative value HF masks with is clamped to -60000 (log2 units: exp2 of it is still exactly 0
+          // beside any real score) so that it stays finite and small enough for the raw-unit round trip below to be
+          // accurate: a row whose visible keys are all masked then averages them uniformly, as a softmax over equal
+          // finite scores does in the reference, instead of coming out as zeros.
+          if (mrow != nullptr && k < a.Sk) v = fmaxf(fmaf(mrow[c], kLog2e, v), -60000.f);
           if (k >= a.Sk || (a.causal && k > qi + shift)) v = -INFINITY;
           t[c] = v * rcexp;
           mx = fmaxf(mx, v);
@@ -797,7 +807,10 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
       tc::mma_commit2(e_done, 3);
     }
   }
-  if (!ok && atomicExch(&s_abort, 2) != 2) atomicAdd(&g_c2_faults, 1ull);  // one fault per CTA
+  if (!ok && atomicExch(&s_abort, 2) != 2) {  // one fault per CTA
+    atomicAdd(&g_c2_faults, 1ull);
+    notify_host_of_fault(g_fault_mailbox_c2);
+  }
   tc::fence_before_sync();
   __syncthreads();
   tc::cluster_sync_relaxed();  // neither CTA leaves (or frees tensor memory) while the pair's MMAs or signals may touch it
@@ -807,7 +820,11 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
 template <int D, int BITS>
 int launch_c2(const AttnArgs& a, const PairArgs& x, int64_t B, cudaStream_t stream) {
   constexpr size_t smem = C2Smem<D, BITS>::kTotal > 120 * 1024 ? C2Smem<D, BITS>::kTotal : 120 * 1024;
+#ifdef TQ_B200_TRACE  // diagnostics build only: the product library carries one instantiation per (d, bits)
   auto kern = g_trace2_host_on ? attention_c2_kernel<D, BITS, true> : attention_c2_kernel<D, BITS, false>;
+#else
+  auto kern = attention_c2_kernel<D, BITS, false>;
+#endif
   TQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int pair_heads = ((a.Hq / a.Hkv) % 2 == 0) ? 1 : 0;
   const int64_t blocks = (a.Sq + kBM - 1) / kBM;

@@ -560,6 +560,8 @@ int tq_decompress_values(const uint8_t* packed_idx, const uint16_t* vec_norms, i
   if (n == 0) return TQ_OK;
   TQ_REQUIRE(packed_idx && vec_norms && Pi && centroids && out, "NULL pointer");
   TQ_REQUIRE(aligned16(out), "out must be 16-byte aligned");
+  CallScope scope(packed_idx, "packed_idx", static_cast<cudaStream_t>(stream));
+  if (scope.status()) return scope.status();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (d == 128) {
     if (bits == 2) return launch_decompress<128, 2>(packed_idx, vec_norms, n, Pi, centroids, out, s);
@@ -587,6 +589,8 @@ int tq_attention_scores(const void* q, int dtype, int64_t B, int64_t Hq, int64_t
   if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u))
     return fail(TQ_ERR_WORKSPACE, "workspace of %zu bytes needed (256-byte aligned), got %zu", need, workspace_bytes);
   // The score matrix is a parity/inspection product: always evaluated in fp32.
+  CallScope scope(q, "q", static_cast<cudaStream_t>(stream));
+  if (scope.status()) return scope.status();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   float* q_cat = static_cast<float*>(workspace);
   if (int st = qprep_fp32(q, dtype, B, Hq, Sq, d, q_stride_b, q_stride_h, q_stride_s, Pi_k, S_eff, q_cat, s))
@@ -624,6 +628,8 @@ extern "C" int tq_prepare_queries(const void* q, int dtype, int64_t B, int64_t H
     return st;
   if (B * Hq * Sq == 0) return TQ_OK;
   TQ_REQUIRE(Pi_k && S_eff && q_cat && aligned16(q_cat), "NULL or misaligned pointer");
+  CallScope scope(q, "q", static_cast<cudaStream_t>(stream));
+  if (scope.status()) return scope.status();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (mode == TQ_MODE_FP32)
     return qprep_fp32(q, dtype, B, Hq, Sq, d, q_stride_b, q_stride_h, q_stride_s, Pi_k, S_eff,
@@ -664,6 +670,8 @@ static int attention_entry(const void* q, int dtype, int64_t B, int64_t Hq, int6
   if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u))
     return fail(TQ_ERR_WORKSPACE, "workspace of %zu bytes needed (256-byte aligned), got %zu", need,
                 workspace_bytes);
+  CallScope scope(q, "q", static_cast<cudaStream_t>(stream));
+  if (scope.status()) return scope.status();
   AttnArgs a{nullptr, Hq, Sq, Hkv, Sk, key_idx, key_signs, key_vec_norms, key_residual_norms, val_idx,
              val_vec_norms, centroids_k, centroids_v, Pi_v, sm_scale, causal, mask, mask_stride_b, mask_stride_q,
              out, dtype, o_stride_b, o_stride_h, o_stride_s, kv_stride};
@@ -725,7 +733,6 @@ extern "C" int tq_attention_fwd_cached(const void* q, int dtype, int64_t B, int6
 namespace {
 constexpr size_t kStaticScratchBytes = 32u << 20;  // 32 MiB
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
-constexpr int kMaxDevices = 64;
 void* g_static_scratch_addr[kMaxDevices] = {nullptr};  // device address of the array, per device
 }  // namespace
 
@@ -750,9 +757,11 @@ extern "C" int tq_attention_fwd_static(const void* q, int dtype, int64_t B, int6
                 "problem needs %zu bytes of scratch but the built-in array holds %zu; use tq_attention_fwd with "
                 "a caller-supplied workspace",
                 need, kStaticScratchBytes);
-  int dev = 0;
-  TQ_CUDA_OK(cudaGetDevice(&dev));
-  TQ_REQUIRE(dev >= 0 && dev < kMaxDevices, "device ordinal %d outside 0..%d", dev, kMaxDevices - 1);
+  if (B * Hq * Sq == 0) return TQ_OK;
+  // the array of the device that owns the queries, whatever the thread's current device is
+  CallScope scope(q, "q", static_cast<cudaStream_t>(stream));
+  if (scope.status()) return scope.status();
+  const int dev = scope.device();
   if (g_static_scratch_addr[dev] == nullptr) {
     // In host code the array's name is only a handle; the address kernels may use comes from the
     // runtime, once per device, with that device current.

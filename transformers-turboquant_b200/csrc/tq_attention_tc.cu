@@ -27,6 +27,12 @@
 namespace tq {
 
 __device__ unsigned long long g_wait_faults = 0ull;
+// this device's slot of the host-visible status page (NULL until the first call on the device installs it)
+__device__ unsigned long long* g_fault_mailbox_tc = nullptr;
+int set_fault_mailbox_tc(unsigned long long* slot) {
+  TQ_CUDA_OK(cudaMemcpyToSymbol(g_fault_mailbox_tc, &slot, sizeof(slot)));
+  return TQ_OK;
+}
 
 int read_wait_faults(unsigned long long* out) {
   TQ_CUDA_OK(cudaMemcpyFromSymbol(out, g_wait_faults, sizeof(*out)));
@@ -57,7 +63,10 @@ struct Tracer {
 __device__ __forceinline__ bool poisoned() {
   return *reinterpret_cast<volatile unsigned long long*>(&g_wait_faults) != 0ull;
 }
-__device__ __forceinline__ void record_fault() { atomicAdd(&g_wait_faults, 1ull); }
+__device__ __forceinline__ void record_fault() {
+  atomicAdd(&g_wait_faults, 1ull);
+  notify_host_of_fault(g_fault_mailbox_tc);
+}
 
 // ---- constant operand builder ------------------------------------------------------------
 // w_cat [2d, d] bf16 = [ Pi ; coeff * S ] with S = S_eff * Pi, so that q * w_cat^T = [q_rot | coeff q_s];
@@ -424,7 +433,11 @@ attention_ws_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
         for (int c = 0; c < kBN; ++c) {
           const int k = k0 + c;
           float v = t[c] * cexp;
-          if (mrow != nullptr && k < a.Sk) v = fmaf(mrow[c], kLog2e, v);
+          // The large negative value HF masks with is clamped to -60000 (log2 units: exp2 of it is still exactly 0
+          // beside any real score) so that it stays finite and small enough for the raw-unit round trip below to be
+          // accurate: a row whose visible keys are all masked then averages them uniformly, as a softmax over equal
+          // finite scores does in the reference, instead of coming out as zeros.
+          if (mrow != nullptr && k < a.Sk) v = fmaxf(fmaf(mrow[c], kLog2e, v), -60000.f);
           if (k >= a.Sk || (a.causal && k > qi + shift)) v = -INFINITY;
           t[c] = v * rcexp;  // back to raw units: the exp2 below rescales (-inf stays -inf)
           mx = fmaxf(mx, v);
@@ -769,7 +782,11 @@ static int launch_attention_tc(const AttnArgs& a, int64_t B, __nv_bfloat16* o_ro
   // every CTA takes all 512 tensor-memory columns, so keep it alone on its SM: ask for more than
   // half of the shared memory even when the tiles (d = 64) would need less
   constexpr size_t smem = WsSmem<D, BITS>::kTotal > 120 * 1024 ? WsSmem<D, BITS>::kTotal : 120 * 1024;
+#ifdef TQ_B200_TRACE  // diagnostics build only: the product library carries one instantiation per (d, bits)
   auto kern = g_trace_host_on ? attention_ws_kernel<D, BITS, true> : attention_ws_kernel<D, BITS, false>;
+#else
+  auto kern = attention_ws_kernel<D, BITS, false>;
+#endif
   TQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   // two query tiles per CTA: two heads of one GQA group when the group size is even, otherwise
   // two consecutive position blocks of one head

@@ -33,6 +33,44 @@ inline bool valid_head_dim(int d) { return d == 64 || d == 128; }
 inline bool valid_bits(int bits) { return bits >= 2 && bits <= 4; }
 inline int elem_size(int dtype) { return dtype == TQ_F32 ? 4 : 2; }
 
+// ---- host: which device a call runs on, and what earlier launches reported ----------------
+//
+// An entry point runs on the device that owns its first data pointer, whatever the thread's current device is:
+// CallScope looks the owner up (cudaPointerGetAttributes), makes it current for the duration of the call and
+// restores the previous device on the way out.  A pointer that is not device (or managed) memory is refused.
+//
+// It is also where a call learns that an EARLIER launch on that device gave up a bounded wait: the kernels raise a
+// flag in a page of host memory that the library pins and maps once per process (static storage, 4 KB, no
+// allocation), so the check is one read of host memory -- no synchronisation, legal during stream capture.  The
+// page is installed on a device by the first call made there outside stream capture; until then, and if pinning
+// is refused, only tq_device_fault_count() (which reads the device counters) reports expired waits.
+class CallScope {
+ public:
+  CallScope(const void* data_ptr, const char* what, cudaStream_t stream);
+  ~CallScope();
+  CallScope(const CallScope&) = delete;
+  CallScope& operator=(const CallScope&) = delete;
+  int status() const { return status_; }  // TQ_OK, or the status the entry point must return at once
+  int device() const { return device_; }
+
+ private:
+  int status_ = TQ_OK, device_ = -1, previous_ = -1;
+};
+constexpr int kMaxDevices = 64;
+// installed by CallScope, one per translation unit that has bounded waits
+int set_fault_mailbox_c2(unsigned long long* slot);
+int set_fault_mailbox_tc(unsigned long long* slot);
+int set_fault_mailbox_compress(unsigned long long* slot);
+int set_fault_mailbox_selftest(unsigned long long* slot);
+
+// Device side of the mailbox: `slot` is the translation unit's copy of the pointer (NULL until installed).
+__device__ __forceinline__ void notify_host_of_fault(unsigned long long* slot) {
+  if (slot != nullptr) {
+    *reinterpret_cast<volatile unsigned long long*>(slot) = 1ull;
+    __threadfence_system();
+  }
+}
+
 // Copies the device counter of expired bounded waits (kept by the tensor-core
 // translation unit) to the host.
 int read_wait_faults(unsigned long long* out);

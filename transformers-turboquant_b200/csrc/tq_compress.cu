@@ -212,6 +212,8 @@ static int compress_keys_entry(const void* keys, int dtype, int64_t B, int64_t H
   if (n == 0) return TQ_OK;
   TQ_REQUIRE(Pi && S_eff && centroids && boundaries, "NULL constant pointer");
   TQ_REQUIRE(packed_idx && packed_signs && vec_norms && residual_norms, "NULL output pointer");
+  CallScope scope(keys, "keys", static_cast<cudaStream_t>(stream));
+  if (scope.status()) return scope.status();
   CompressArgs a{keys, n, H, S, stride_b, stride_h, stride_s, Pi, S_eff, centroids, boundaries,
                  packed_idx, packed_signs, vec_norms, residual_norms,
                  (int)((n + kTileRows - 1) / kTileRows), out_stride, out_offset};
@@ -228,6 +230,8 @@ static int compress_values_entry(const void* values, int dtype, int64_t B, int64
   if (n == 0) return TQ_OK;
   TQ_REQUIRE(Pi && boundaries, "NULL constant pointer");
   TQ_REQUIRE(packed_idx && vec_norms, "NULL output pointer");
+  CallScope scope(values, "values", static_cast<cudaStream_t>(stream));
+  if (scope.status()) return scope.status();
   CompressArgs a{values, n, H, S, stride_b, stride_h, stride_s, Pi, nullptr, nullptr, boundaries,
                  packed_idx, nullptr, vec_norms, nullptr, (int)((n + kTileRows - 1) / kTileRows), out_stride, out_offset};
   return dispatch_compress<false>(dtype, d, bits, a, mode, static_cast<cudaStream_t>(stream));

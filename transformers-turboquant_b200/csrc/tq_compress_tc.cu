@@ -23,6 +23,12 @@
 namespace tq {
 
 __device__ unsigned long long g_compress_faults = 0ull;  // expired bounded waits in this file's kernels
+// this device's slot of the host-visible status page (NULL until the first call on the device installs it)
+__device__ unsigned long long* g_fault_mailbox_compress = nullptr;
+int set_fault_mailbox_compress(unsigned long long* slot) {
+  TQ_CUDA_OK(cudaMemcpyToSymbol(g_fault_mailbox_compress, &slot, sizeof(slot)));
+  return TQ_OK;
+}
 
 int read_compress_faults(unsigned long long* out) {
   TQ_CUDA_OK(cudaMemcpyFromSymbol(out, g_compress_faults, sizeof(*out)));
@@ -270,7 +276,10 @@ __global__ void __launch_bounds__(4 * D, 1) compress_tc_kernel(const CompressArg
     __syncthreads();  // the next tile overwrites the A tiles, the partial sums and the accumulators
   }
   if (s_abort) {
-    if (tid == 0) atomicAdd(&g_compress_faults, 1ull);
+    if (tid == 0) {
+      atomicAdd(&g_compress_faults, 1ull);
+      notify_host_of_fault(g_fault_mailbox_compress);
+    }
   }
   tc::fence_before_sync();
   __syncthreads();

@@ -6,8 +6,11 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <mutex>
+
 #include "tq_common.cuh"
 #include "tq_attention.cuh"
+#include "tq_tcgen05.cuh"
 
 namespace tq {
 
@@ -26,6 +29,125 @@ int fail(tq_status st, const char* fmt, ...) {
   vsnprintf(t_error, sizeof(t_error), fmt, ap);
   va_end(ap);
   return st;
+}
+
+// ---- device selection and the host-visible status page -------------------------------------
+namespace {
+// One page of the library's own static storage, pinned and mapped into the devices' address space at first use.
+// Slot d: an expired bounded wait on device d.  Slot kMaxDevices + d: the self-test's flag on device d.
+struct alignas(4096) StatusPage {
+  volatile unsigned long long slot[4096 / sizeof(unsigned long long)];
+};
+StatusPage g_status_page;
+std::mutex g_setup_mutex;
+int g_page_state = 0;                    // 0 = not tried yet, 1 = pinned and mapped, -1 = pinning was refused
+bool g_device_ready[kMaxDevices] = {};   // mailbox pointers installed on this device
+bool g_sticky_fault[kMaxDevices] = {};   // tq_device_fault_count has seen a non-zero device counter
+
+__device__ unsigned long long* g_mailbox_selftest = nullptr;
+
+// The first call on a device outside stream capture installs the mailbox pointers (four small synchronous
+// copies to device symbols).  Nothing is allocated: the page is static storage, cudaHostRegister only pins it.
+void install_status_page(int dev, cudaStream_t stream) {
+  std::lock_guard<std::mutex> lock(g_setup_mutex);
+  if (g_device_ready[dev] || g_page_state < 0) return;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+    cudaGetLastError();
+    return;  // not now: synchronous set-up is illegal inside a capture; a later call installs it
+  }
+  if (g_page_state == 0) {
+    const cudaError_t e = cudaHostRegister(&g_status_page, sizeof(g_status_page),
+                                           cudaHostRegisterMapped | cudaHostRegisterPortable);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      g_page_state = -1;
+      return;
+    }
+    g_page_state = 1;
+  }
+  void* dptr = nullptr;
+  if (cudaHostGetDevicePointer(&dptr, const_cast<unsigned long long*>(&g_status_page.slot[0]), 0) != cudaSuccess) {
+    cudaGetLastError();
+    return;
+  }
+  unsigned long long* base = static_cast<unsigned long long*>(dptr);
+  unsigned long long* self = base + kMaxDevices + dev;
+  if (set_fault_mailbox_c2(base + dev) || set_fault_mailbox_tc(base + dev) || set_fault_mailbox_compress(base + dev) ||
+      cudaMemcpyToSymbol(g_mailbox_selftest, &self, sizeof(self)) != cudaSuccess) {
+    cudaGetLastError();
+    return;
+  }
+  g_device_ready[dev] = true;
+}
+}  // namespace
+
+CallScope::CallScope(const void* data_ptr, const char* what, cudaStream_t stream) {
+  cudaPointerAttributes attr;
+  cudaError_t e = cudaPointerGetAttributes(&attr, data_ptr);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    status_ = fail(TQ_ERR_CUDA, "cudaPointerGetAttributes(%s) failed: %s", what, cudaGetErrorString(e));
+    return;
+  }
+  if (attr.type != cudaMemoryTypeDevice && attr.type != cudaMemoryTypeManaged) {
+    status_ = fail(TQ_ERR_INVALID_ARG, "%s is not a device pointer (the library has no host path)", what);
+    return;
+  }
+  device_ = attr.device;
+  if (device_ < 0 || device_ >= kMaxDevices) {
+    status_ = fail(TQ_ERR_INVALID_ARG, "device ordinal %d outside 0..%d", device_, kMaxDevices - 1);
+    return;
+  }
+  int current = -1;
+  if ((e = cudaGetDevice(&current)) != cudaSuccess) {
+    status_ = fail(TQ_ERR_CUDA, "cudaGetDevice failed: %s", cudaGetErrorString(e));
+    return;
+  }
+  if (current != device_) {
+    if ((e = cudaSetDevice(device_)) != cudaSuccess) {
+      status_ = fail(TQ_ERR_CUDA, "cudaSetDevice(%d) failed: %s", device_, cudaGetErrorString(e));
+      return;
+    }
+    previous_ = current;
+  }
+  if (!g_device_ready[device_]) install_status_page(device_, stream);
+  if (g_status_page.slot[device_] != 0ull || g_sticky_fault[device_])
+    status_ = fail(TQ_ERR_DEVICE_WAIT,
+                   "a bounded device-side wait expired in an earlier launch on device %d: results computed since "
+                   "then are not valid and nothing further is launched (tq_device_fault_count reads the counter; "
+                   "the condition lasts until the process exits)", device_);
+}
+
+CallScope::~CallScope() {
+  if (previous_ >= 0) cudaSetDevice(previous_);
+}
+
+int set_fault_mailbox_selftest(unsigned long long* slot) {
+  TQ_CUDA_OK(cudaMemcpyToSymbol(g_mailbox_selftest, &slot, sizeof(slot)));
+  return TQ_OK;
+}
+
+// Self-test of the expiry path (tq_selftest_wait_expiry): one CTA initialises an mbarrier that nobody arrives on
+// and waits for it with the bounded wait the production kernels use, with a short limit.  The wait gives up,
+// raises the CTA's abort flag, and thread 0 reports through the mailbox -- into the self-test's own slot, not
+// the one that poisons later calls.  Nothing traps, faults or spins without bound.
+__global__ void selftest_wait_kernel(long long limit_cycles, long long* waited_cycles) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    tc::mbar_init(tc::smem_u32(&bar), 1);
+    tc::fence_mbar_init();
+  }
+  __syncthreads();
+  const long long t0 = clock64();
+  const bool ok = tc::mbar_wait_or_abort(tc::smem_u32(&bar), 0, &s_abort, limit_cycles);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    *waited_cycles = clock64() - t0;
+    if (!ok && s_abort) notify_host_of_fault(g_mailbox_selftest);
+  }
 }
 
 // ---- per-kernel timing ------------------------------------------------------------------
@@ -183,7 +305,35 @@ int tq_device_fault_count(void* stream, int64_t* count_host) {
   unsigned long long x = 0;
   if (int st = read_c2_faults(&x)) return st;
   *count_host = static_cast<int64_t>(v + w + x);
+  int dev = -1;
+  if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices && v + w + x != 0) g_sticky_fault[dev] = true;
   return TQ_OK;
+}
+
+int tq_selftest_wait_expiry(void* stream, int64_t limit_cycles, int64_t* waited_cycles_host) {
+  TQ_REQUIRE(limit_cycles >= 1000 && limit_cycles <= 2000000000ll, "limit_cycles %lld outside 1e3..2e9",
+             (long long)limit_cycles);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int dev = -1;
+  TQ_CUDA_OK(cudaGetDevice(&dev));
+  TQ_REQUIRE(dev >= 0 && dev < kMaxDevices, "device ordinal %d outside 0..%d", dev, kMaxDevices - 1);
+  if (!g_device_ready[dev]) install_status_page(dev, s);
+  if (!g_device_ready[dev])
+    return fail(TQ_ERR_UNSUPPORTED, "the host-visible status page could not be installed on device %d", dev);
+  volatile unsigned long long* flag = &g_status_page.slot[kMaxDevices + dev];
+  long long* waited = const_cast<long long*>(reinterpret_cast<volatile long long*>(&g_status_page.slot[2 * kMaxDevices + dev]));
+  void* waited_dev = nullptr;
+  TQ_CUDA_OK(cudaHostGetDevicePointer(&waited_dev, waited, 0));
+  *flag = 0ull;
+  *waited = 0;
+  selftest_wait_kernel<<<1, 64, 0, s>>>((long long)limit_cycles, static_cast<long long*>(waited_dev));
+  TQ_CUDA_OK(cudaGetLastError());
+  TQ_CUDA_OK(cudaStreamSynchronize(s));
+  if (waited_cycles_host != nullptr) *waited_cycles_host = *waited;
+  if (*flag == 0ull) return TQ_OK;  // the wait did not expire (it cannot succeed either: nobody arrives)
+  *flag = 0ull;
+  return fail(TQ_ERR_DEVICE_WAIT, "self-test: a bounded device-side wait gave up after %lld cycles (limit %lld) and "
+              "reported it to the host", (long long)*waited, (long long)limit_cycles);
 }
 
 static bool trace_sm_pairs() {
@@ -192,6 +342,9 @@ static bool trace_sm_pairs() {
 }
 
 int tq_trace_enable(int on) {
+#ifndef TQ_B200_TRACE
+  if (on) return fail(TQ_ERR_UNSUPPORTED, "this build carries no tracing kernels: rebuild with `build.py --trace`");
+#endif
   if (int st = trace_enable(on)) return st;
   return trace_enable_c2(on);
 }
@@ -242,6 +395,8 @@ int tq_pack_bits(const int32_t* indices, int64_t n, int d, int b, uint8_t* packe
   if (n == 0) return TQ_OK;
   TQ_REQUIRE(indices && packed, "NULL pointer");
   TQ_REQUIRE(aligned16(indices), "indices must be 16-byte aligned");
+  CallScope scope(indices, "indices", static_cast<cudaStream_t>(stream));
+  if (scope.status()) return scope.status();
   int st = dispatch_bits<PackL>(b, indices, n * (d / 8), d / 8, packed, static_cast<cudaStream_t>(stream));
   if (st) return st;
   TQ_CUDA_OK(cudaGetLastError());
@@ -253,6 +408,8 @@ int tq_unpack_bits(const uint8_t* packed, int64_t n, int d, int b, int32_t* indi
   if (n == 0) return TQ_OK;
   TQ_REQUIRE(indices && packed, "NULL pointer");
   TQ_REQUIRE(aligned16(indices), "indices must be 16-byte aligned");
+  CallScope scope(packed, "packed", static_cast<cudaStream_t>(stream));
+  if (scope.status()) return scope.status();
   int st = dispatch_bits<UnpackL>(b, packed, n * (d / 8), indices, static_cast<cudaStream_t>(stream));
   if (st) return st;
   TQ_CUDA_OK(cudaGetLastError());
@@ -265,6 +422,8 @@ int tq_quantize_rotated(const float* rotated, int64_t n, int d, const float* bou
   if (n == 0) return TQ_OK;
   TQ_REQUIRE(rotated && boundaries && packed, "NULL pointer");
   TQ_REQUIRE(aligned16(rotated), "rotated must be 16-byte aligned");
+  CallScope scope(rotated, "rotated", static_cast<cudaStream_t>(stream));
+  if (scope.status()) return scope.status();
   const int64_t ng = n * (d / 8);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (b_eff) {  // boundaries live in registers, so only the widths the codebooks use
@@ -283,6 +442,8 @@ int tq_dequantize(const uint8_t* packed, int64_t n, int d, const float* centroid
   if (n == 0) return TQ_OK;
   TQ_REQUIRE(packed && centroids && out, "NULL pointer");
   TQ_REQUIRE(aligned16(out), "out must be 16-byte aligned");
+  CallScope scope(packed, "packed", static_cast<cudaStream_t>(stream));
+  if (scope.status()) return scope.status();
   int st = dispatch_bits<DequantL>(b, packed, n * (d / 8), centroids, out, static_cast<cudaStream_t>(stream));
   if (st) return st;
   TQ_CUDA_OK(cudaGetLastError());

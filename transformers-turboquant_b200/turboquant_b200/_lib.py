@@ -39,6 +39,7 @@ SIGNATURES = {
     "tq_version": (_i, []),
     "tq_last_error": (C.c_char_p, []),
     "tq_device_fault_count": (_i, [_p, C.POINTER(C.c_int64)]),
+    "tq_selftest_wait_expiry": (_i, [_p, _l, C.POINTER(C.c_int64)]),
     "tq_trace_enable": (_i, [_i]),
     "tq_trace_read": (_i, [C.POINTER(C.c_int64), _i, C.POINTER(C.c_int)]),
     "tq_profile_begin": (_i, [_i]),

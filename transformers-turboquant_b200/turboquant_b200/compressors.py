@@ -207,8 +207,12 @@ class TurboQuantCompressorMSE(_Constants):
 
 
 def _mask_args(attention_mask, B: int, Sq: int, Sk: int, dev):
-    """An additive mask broadcastable to [B, 1, Sq, Sk] as (tensor, pointer, batch stride, row stride) of an
-    fp32 tensor with unit inner stride; (None, None, 0, 0) for no mask."""
+    """A mask broadcastable to [B, 1, Sq, Sk] as (tensor, pointer, batch stride, row stride) of an additive
+    fp32 tensor with unit inner stride; (None, None, 0, 0) for no mask.
+
+    Floating-point masks are additive (0 = visible, large negative = hidden), as HF's eager path builds them.
+    Boolean masks mean True = visible, which is what HF's sdpa path hands over for padded batches; they are
+    turned into the additive form here.  Integer masks are refused: their meaning would be a guess."""
     if attention_mask is None:
         return None, None, 0, 0
     mk = attention_mask
@@ -218,7 +222,14 @@ def _mask_args(attention_mask, B: int, Sq: int, Sk: int, dev):
         mk = mk[:, 0]
     elif mk.dim() == 2:
         mk = mk.unsqueeze(0)
-    mk = mk.to(device=dev, dtype=torch.float32)
+    if mk.dtype == torch.bool:
+        keep = mk.to(device=dev)
+        mk = torch.zeros(keep.shape, dtype=torch.float32, device=dev).masked_fill_(~keep, torch.finfo(torch.float32).min)
+    elif mk.dtype.is_floating_point:
+        mk = mk.to(device=dev, dtype=torch.float32)
+    else:
+        raise TypeError(f"attention mask of dtype {mk.dtype} is ambiguous: pass a bool mask (True = visible) or an "
+                        "additive floating-point mask")
     if mk.shape[-2:] != (Sq, Sk) or mk.shape[0] not in (1, B):
         raise ValueError(f"mask shape {tuple(attention_mask.shape)} does not broadcast to [B,1,{Sq},{Sk}]")
     if mk.stride(-1) != 1:
@@ -274,5 +285,6 @@ def device_fault_count(device=None) -> int:
 
     n = ctypes.c_int64(0)
     dev = torch.device(device if device is not None else "cuda")
-    _lib.check(_lib.lib.tq_device_fault_count(_stream_ptr(dev), ctypes.byref(n)))
+    with torch.cuda.device(dev):  # the counter read is the one call that goes by the current device
+        _lib.check(_lib.lib.tq_device_fault_count(_stream_ptr(dev), ctypes.byref(n)))
     return int(n.value)

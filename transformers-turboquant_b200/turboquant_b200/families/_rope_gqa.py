@@ -76,13 +76,26 @@ class RopeGQAAttention(TurboQuantAttentionBase):
         B, Hkv, T, D = k.shape
         owner = getattr(self, "_tq_owner", None)
         cache = getattr(self, "_tq_cache", None)
+        seen = int(past_key_values.get_seq_length(self.layer_idx))
         if owner is None or owner() is not past_key_values:
+            # A cache object this layer has not met starts a new sequence -- but only an EMPTY one can: the
+            # compressed tokens of a pre-filled HF cache (a resumed generation, a second generation interleaved
+            # with the first, assisted decoding) live nowhere, and attending over the new tokens alone would be
+            # silently wrong.
+            if seen != 0:
+                raise RuntimeError(
+                    f"layer {self.layer_idx}: the HF cache handed over already holds {seen} positions that this "
+                    "layer's compressed cache never saw (the compressed cache follows one generation at a time; "
+                    "start each generation from an empty cache object and do not interleave generations)")
             if cache is None or (cache.batch, cache.kv_heads) != (B, Hkv) or cache.key_indices.device != k.device:
                 cache = CompressedKVCache(self.key_compressor, self.val_compressor, B, Hkv, self.kv_cache_capacity,
                                           device=k.device)
                 self._tq_cache = cache
             cache.reset()
             self._tq_owner = weakref.ref(past_key_values)
+        elif seen != cache.length:
+            raise RuntimeError(f"layer {self.layer_idx}: the HF cache holds {seen} positions but the compressed cache "
+                               f"{cache.length}; cache reordering or cropping (beam search, rollback) is not supported")
         cache.append(k, v)
         past_key_values.update(k[..., :1], v[..., :1], self.layer_idx)
         return cache.attend(q, causal=True, attention_mask=attention_mask)

@@ -27,13 +27,22 @@ class TurboQuantGPT2Attention(TurboQuantAttentionBase):
     def forward(self, hidden_states, past_key_values=None, cache_position=None, attention_mask=None,
                 head_mask=None, encoder_hidden_states=None, encoder_attention_mask=None,
                 output_attentions=False, **kwargs):
+        if output_attentions:
+            raise NotImplementedError("the fused kernel never materialises attention probabilities; "
+                                      "output_attentions is not available on the compressed path")
+        if self.training and self.attn_dropout.p > 0 and not getattr(self, "_warned_dropout", False):
+            import warnings
+            warnings.warn(f"attention-probability dropout (attn_pdrop={self.attn_dropout.p}) is not applied on the "
+                          "compressed path: fine-tuning differs from the reference's adapter, which drops "
+                          "probabilities (families/gpt2.py:104); set attn_pdrop=0 to make them agree")
+            self._warned_dropout = True
         B, T, _ = hidden_states.shape
         q, k, v = self.c_attn(hidden_states).split(self.embed_dim, dim=2)
         q, k, v = (t.view(B, T, self.num_heads, self.head_dim).transpose(1, 2) for t in (q, k, v))
         ck = self.key_compressor.compress(k)
         cv = self.val_compressor.compress(v)
-        # attention-probability dropout (attn_pdrop) has no counterpart in the fused kernel;
-        # it is inactive in eval mode, which is the only mode the compressed path serves
+        # attention-probability dropout (attn_pdrop) has no counterpart in the fused kernel; it is
+        # inactive in eval mode and warned about above in train mode
         out = fused_attention(q, ck, cv, self.key_compressor, self.val_compressor, causal=True,
                               attention_mask=attention_mask)
         out = out.transpose(1, 2).reshape(B, T, self.embed_dim)
