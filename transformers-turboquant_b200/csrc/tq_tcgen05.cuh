@@ -35,6 +35,13 @@ __host__ __device__ constexpr uint32_t idesc_bf16(int M, int N, bool a_mn_major,
 }
 
 
+// fp16 x fp16 -> fp32 (format fields at bits 7 and 10: 0 = fp16, 1 = bf16).  Both operands of an MMA must have
+// the same format: bf16 A with fp16 B raises an illegal-instruction fault on B200.
+__host__ __device__ constexpr uint32_t idesc_f16(int M, int N, bool a_mn_major, bool b_mn_major) {
+  return (1u << 4) /*D=f32*/ | ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
+         (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
+}
+
 // ---- mbarrier ------------------------------------------------------------------------
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -290,6 +297,21 @@ __device__ __forceinline__ void mma_commit2(uint32_t bar, uint16_t cta_mask) {
       : "memory");
 }
 
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+// fp16 pair of values clamped to the largest finite fp16 magnitude (an operand must never carry an infinity)
+__device__ __forceinline__ uint32_t pack_f16x2_sat(float lo, float hi) {
+  return pack_f16x2(fminf(fmaxf(lo, -65504.f), 65504.f), fminf(fmaxf(hi, -65504.f), 65504.f));
+}
+// two fp16 products of packed pairs
+__device__ __forceinline__ uint32_t mul_f16x2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
