@@ -4,15 +4,23 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         --master-port P bench.py --gpus N --steps K --warmup W
 
-Workload ("op_level_gqa4_s8192"): bf16 Q [4,32,8192,128], K,V [4,8,8192,128] drawn N(0,1)
+Headline workload ("op_level_gqa4_s8192"): bf16 Q [4,32,8192,128], K,V [4,8,8192,128] drawn N(0,1)
 with 4 key channels per head scaled x8, rotation/QJL matrices from seed 42, causal, 3-bit by
-default.  One step = compress K, compress V, fused attention over the whole batch.  With N
-ranks every rank runs this workload on its own (batch x KV-head) shard, no data-path
-collective (weak scaling).  Inputs (402 MB) exceed the 126 MB L2, so no flush between
-steps.  Prints ONE JSON line on rank 0.
+default.  One step = compress K and V, fused attention over the whole batch.  With N ranks every
+rank runs this workload on its own (batch x KV-head) shard, no data-path collective (weak scaling).
+Inputs (402 MB) exceed the 126 MB L2, so no flush between steps.  Rank 0 prints ONE JSON line.
 
-`--impl reference` times the CPU restatement of the reference's PyTorch path (oracle/) on the
-host cores, on a bounded sample of the same workload.
+The same line carries, as extra objects, the other halves of the metric (`--sections` selects them):
+  decode          one new token per sequence against a 32768-key compressed cache (split-KV kernel, HBM roofline)
+  models.llama8b  prefill tokens/s of a LLaMA-3.1-8B-shaped random-init model, global batch 8 x 4096 split over
+                  the ranks, 3-bit TurboQuant attention, logits all_gather inside the timed region, with the same
+                  model on HF sdpa attention beside it
+  scaling_config5 STRONG scaling of the fused path on K,V [64,8,32768,128] / Q [64,32,32768,128], the 512
+                  (batch, KV head) units split over the ranks
+
+`--impl reference` times the CPU restatement of the reference's PyTorch path (oracle/) on the host cores: every
+step is one whole (batch, query head) unit of the workload (the reference expands K/V to one copy per query
+head and materialises the full score rows); the line reports the measured step and the unit count it scales by.
 """
 
 from __future__ import annotations
@@ -41,6 +49,7 @@ import torch  # noqa: E402
 B, HQ, HKV, S, D = 4, 32, 8, 8192, 128
 METRIC = "fused_tq_attention_keys_per_s"
 UNIT = "keys/s"
+ALL_SECTIONS = ("e2e", "cpu", "gpuref", "sustained", "decode", "llama8b", "config5")
 
 
 def parse():
@@ -52,14 +61,30 @@ def parse():
     ap.add_argument("--bits", type=int, default=3)
     ap.add_argument("--seq", type=int, default=S, help="sequence length (default: the named workload)")
     ap.add_argument("--batch", type=int, default=B)
-    ap.add_argument("--workload", default="op", choices=["op", "llama8b", "deepseek7b", "quality", "decode"],
-                    help="op: the op-level headline workload (default); llama8b / deepseek7b: end-to-end prefill of a "
-                         "random-init model of that shape through apply_turboquant; quality: estimator quality "
-                         "metrics on a Qwen2.5-3B-shaped attention layer; decode: one new token per sequence against a long "
-                         "compressed KV cache (split-KV kernel)")
+    ap.add_argument("--workload", default="op",
+                    choices=["op", "llama8b", "deepseek7b", "gpt2small", "config5", "quality", "decode"],
+                    help="op: the headline line with all its sections (default).  The others print one line of "
+                         "their own: llama8b / deepseek7b: end-to-end prefill of a random-init model of that shape "
+                         "through apply_turboquant; gpt2small: the GPT-2-small configuration, logits and per-layer "
+                         "score cosines against the CPU oracle model; config5: the strong-scaling sweep shape; "
+                         "quality: estimator quality on the Qwen2.5-3B shape; decode: one new token per sequence "
+                         "against a long compressed KV cache")
+    ap.add_argument("--sections", default="all",
+                    help="comma-separated extra sections of the headline line: " + ",".join(ALL_SECTIONS) +
+                         " (default all; 'none' for the bare op-level line)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    return ap.parse_args()
+    args = ap.parse_args()
+    want = set(ALL_SECTIONS) if args.sections == "all" else set(x for x in args.sections.split(",") if x and x != "none")
+    unknown = want - set(ALL_SECTIONS)
+    if unknown:
+        ap.error(f"unknown sections {sorted(unknown)}")
+    if args.no_cpu_baseline:
+        want.discard("cpu")
+    if args.no_e2e:
+        want.discard("e2e")
+    args.want = want
+    return args
 
 
 def make_inputs(batch, seq, device, seed=0):
@@ -115,78 +140,181 @@ class ClockSampler(threading.Thread):
                 "samples": len(s)}
 
 
-def causal_pairs(batch, seq):
-    return batch * HQ * seq * (seq + 1) // 2
+def causal_pairs(batch, seq, heads=HQ):
+    return batch * heads * seq * (seq + 1) // 2
 
 
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         p = json.load(open(path))
-        return {"tflops": p.get("bf16_tflops_sustained", p.get("bf16_tflops")), "hbm_gbs": p.get("hbm_gbs"),
-                "source": "measured (MEASURED_PEAKS.json, sustained bf16)"}
-    return {"tflops": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+        return {"tflops_burst": p.get("bf16_tflops"), "tflops_sustained": p.get("bf16_tflops_sustained", p.get("bf16_tflops")),
+                "hbm_gbs": p.get("hbm_gbs"), "source": "measured (MEASURED_PEAKS.json)"}
+    return {"tflops_burst": 1590.0, "tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
 
 
-CPU_Q_ROWS = 1024  # query rows of the unit that the CPU sample actually evaluates
+def attention_flops(batch, seq, heads=HQ):
+    """Algorithmic flops of one launch of the fused attention kernel: 2d (q.K_hat) + 2d (q_s.sign) + 2d (P.V_hat)
+    per causal pair, plus per query row the preparation q [Pi ; coeff S]^T (2 * 2d * d) and the output
+    back-rotation (2 d^2)."""
+    return 6.0 * D * causal_pairs(batch, seq, heads) + 6.0 * D * D * batch * heads * seq
 
 
-def cpu_sample(bits, seq, repeats=1, threads=None):
-    """Reference PyTorch path (oracle restatement, literal arithmetic: compress of the
-    GQA-expanded K/V, full-width score rows, fp32 softmax, PV) on one (batch, query-head) unit
-    of the workload.  Compression is timed on all `seq` keys; the score/softmax/PV part on the
-    last CPU_Q_ROWS query rows against all keys and scaled by seq/CPU_Q_ROWS (the reference
-    computes every row at full width whatever the mask).  Returns seconds per unit."""
+# ---------------------------------------------------------------------------------------------------------
+# the reference's PyTorch path (oracle restatement) on one unit of the workload: CPU baseline and reference arm
+# ---------------------------------------------------------------------------------------------------------
+
+def reference_unit(bits, seq, device="cpu", row_chunk=2048, seed=0):
+    """One whole (batch, query head) unit of the op-level workload through the reference's PyTorch path
+    (families/llama.py:100-114 of the reference: compress the GQA-expanded K and V of the head, full-width score
+    rows, + causal mask, fp32 softmax cast to the model dtype, P @ decompressed V), literal arithmetic, on
+    `device`.  All `seq` query rows are evaluated, `row_chunk` at a time so that the fp32 score block stays
+    bounded.  Returns the seconds it took."""
     from oracle import tq_oracle as orc
-    threads = threads or os.cpu_count()
-    torch.set_num_threads(threads)
-    kp, vp = orc.make_key_params(D, bits, 42), orc.make_value_params(D, bits, 10042)
-    g = torch.Generator().manual_seed(0)
-    rows = min(CPU_Q_ROWS, seq)
-    q = torch.randn(1, 1, rows, D, generator=g).to(torch.bfloat16)
-    k = torch.randn(1, 1, seq, D, generator=g).to(torch.bfloat16)
-    v = torch.randn(1, 1, seq, D, generator=g).to(torch.bfloat16)
-    mask = orc.causal_mask(seq, seq)[-rows:]
-    best = float("inf")
-    for _ in range(repeats):
-        t0 = time.perf_counter()
-        ck, cv = orc.key_compress(k, kp), orc.value_compress(v, vp)
-        t1 = time.perf_counter()
-        sc = orc.scores_literal(q, ck, kp) / math.sqrt(D) + mask
-        w = torch.softmax(sc.float(), dim=-1).to(q.dtype)
-        _ = w @ orc.value_decompress(cv, vp).to(q.dtype)
-        t2 = time.perf_counter()
-        best = min(best, (t1 - t0) + (t2 - t1) * (seq / rows))
-    return best, threads
+    kp, vp = orc.make_key_params(D, bits, 42).to(device), orc.make_value_params(D, bits, 10042).to(device)
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(1, 1, seq, D, generator=g).to(torch.bfloat16).to(device)
+    k = torch.randn(1, 1, seq, D, generator=g)
+    k[..., torch.randperm(D, generator=torch.Generator().manual_seed(1))[:4]] *= 8.0
+    k = k.to(torch.bfloat16).to(device)
+    v = torch.randn(1, 1, seq, D, generator=g).to(torch.bfloat16).to(device)
+    cuda = torch.device(device).type == "cuda"
+    if cuda:
+        torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    ck, cv = orc.key_compress(k, kp, pack=False), orc.value_compress(v, vp, pack=False)
+    vals = orc.value_decompress(cv, vp).to(q.dtype)
+    out = torch.empty_like(q)
+    for r0 in range(0, seq, row_chunk):
+        r1 = min(seq, r0 + row_chunk)
+        sc = orc.scores_literal(q[:, :, r0:r1], ck, kp) / math.sqrt(D)
+        sc = sc + orc.causal_mask(seq, seq)[r0:r1].to(device)
+        out[:, :, r0:r1] = torch.softmax(sc.float(), dim=-1).to(q.dtype) @ vals
+    if cuda:
+        torch.cuda.synchronize()
+    return time.perf_counter() - t0
+
+
+def workload_config(args, world=1):
+    return {"workload": "op_level_gqa4_s8192", "batch_per_gpu": args.batch, "q_heads": HQ, "kv_heads": HKV,
+            "seq_len": args.seq, "head_dim": D, "bits": args.bits, "causal": True}
 
 
 def run_reference(args):
-    """The reference arm: CPU, rank 0 only."""
+    """The reference arm: the reference's CPU path on the host cores, rank 0 only.  A step is one whole
+    (batch, query head) unit; the workload has batch * q_heads of them (the reference compresses one expanded copy
+    of K and V per query head), independent of one another, so the step scales linearly by that count."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    threads = os.cpu_count()
+    torch.set_num_threads(threads)
     seq, batch = args.seq, args.batch
-    cpu_sample(args.bits, min(seq, 1024))  # warm the thread pool and allocator
-    for _ in range(max(args.warmup - 1, 0)):
-        cpu_sample(args.bits, seq)
-    per_unit = sum(cpu_sample(args.bits, seq)[0] for _ in range(args.steps)) / args.steps
-    units = batch * HQ  # the reference expands K/V to one copy per query head before compressing
-    step_s = per_unit * units
+    reference_unit(args.bits, min(seq, 1024))  # warm the thread pool and allocator
+    for _ in range(max(args.warmup, 1)):
+        reference_unit(args.bits, seq)
+    t0 = time.perf_counter()
+    per_step = [reference_unit(args.bits, seq) for _ in range(args.steps)]
+    wall = time.perf_counter() - t0
+    step_s = sum(per_step) / len(per_step)
+    units = batch * HQ
     keys = batch * HKV * seq
-    value = keys / step_s
+    value = keys / (step_s * units)
+    cfg = workload_config(args)
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "op_level_gqa4_s8192", "batch": batch, "q_heads": HQ, "kv_heads": HKV,
-                       "seq_len": seq, "head_dim": D, "bits": args.bits, "causal": True},
-            "cpu_baseline": {"value": value, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
-                             "sample": f"per step one (batch, query head) unit of {units}: compress of S={seq} keys and "
-                                       f"values, score/softmax/PV rows for {min(CPU_Q_ROWS, seq)} of {seq} queries "
-                                       "at full width, scaled to the unit and then linearly to the workload"},
+            "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": step_s * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg,
+            "sampled_s": wall, "scale_factor": units,
+            "note": "ms_per_step is the measured time of one step = one (batch, query head) unit, all of its "
+                    f"{seq} query rows; value = workload keys / (ms_per_step * scale_factor): the {units} units "
+                    "of the workload are independent and identical in cost",
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                             "sample": f"per step one whole (batch, query head) unit of {units}: compress of S={seq} "
+                                       f"keys and values, all {seq} score rows at full width, fp32 softmax, P@V "
+                                       "(oracle restatement of the reference's PyTorch path); scaled by the unit count"},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
+
+# ---------------------------------------------------------------------------------------------------------
+# distributed plumbing
+# ---------------------------------------------------------------------------------------------------------
+
+class Ctx:
+    """One process per GPU: rank, device and the process group (NCCL) when there is more than one rank."""
+
+    def __init__(self):
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        self.affinity = bind_to_gpu_numa_node(self.local)
+        torch.cuda.set_device(self.local)
+        self.dev = torch.device("cuda", self.local)
+        self.dist = None
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.init_process_group("nccl", device_id=self.dev)
+            self.dist = dist
+
+    def barrier(self):
+        if self.dist is not None:
+            self.dist.barrier()
+        torch.cuda.synchronize(self.dev)
+
+    def max_over_ranks(self, x: float) -> float:
+        t = torch.tensor([x], device=self.dev, dtype=torch.float64)
+        if self.dist is not None:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def min_over_ranks(self, x: float) -> float:
+        return -self.max_over_ranks(-x)
+
+    def close(self):
+        if self.dist is not None:
+            self.dist.destroy_process_group()
+
+
+def bind_to_gpu_numa_node(index: int):
+    """Pin this process to the CPU cores NVML lists as nearest to its GPU, before any pinned host memory is
+    allocated, so that the buffers of the end-to-end path are first touched on that NUMA node.  Changes no GPU or
+    driver setting.  Returns the core list used (None when NVML or the affinity call is unavailable)."""
+    try:
+        import pynvml as nv
+        nv.nvmlInit()
+        h = nv.nvmlDeviceGetHandleByIndex(index)
+        words = (os.cpu_count() + 63) // 64
+        mask = nv.nvmlDeviceGetCpuAffinity(h, words)
+        cpus = [64 * w + b for w, m in enumerate(mask) for b in range(64) if (int(m) >> b) & 1]
+        cpus = [c for c in cpus if c in os.sched_getaffinity(0)]
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return f"{cpus[0]}-{cpus[-1]} ({len(cpus)} cores)"
+    except Exception:
+        pass
+    return None
+
+
+def timed_steps(ctx: Ctx, fn, steps: int, warmup: int):
+    """`warmup` untimed calls, then `steps` calls between a barrier + synchronize on both sides, CUDA events on the
+    current stream; returns (ms per step, MAX over ranks; last result)."""
+    out = None
+    for _ in range(warmup):
+        out = fn()
+    ctx.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        out = fn()
+    e1.record()
+    ctx.barrier()
+    return ctx.max_over_ranks(e0.elapsed_time(e1) / steps), out
+
+
+# ---------------------------------------------------------------------------------------------------------
+# sections of the headline line
+# ---------------------------------------------------------------------------------------------------------
 
 MODEL_SHAPES = {
     # name: (layers, hidden, q heads, kv heads, head_dim, ffn, vocab, rope_theta, global batch, seq)
@@ -195,123 +323,116 @@ MODEL_SHAPES = {
 }
 
 
-def run_model(args):
-    """End-to-end prefill tokens/s of a random-init LLaMA-architecture model (bf16, N(0, 0.02) init, uniform
-    random tokens) with every attention layer replaced by apply_turboquant(bits, seed=42).  The global
-    batch is split over the ranks (full replica per GPU, strong scaling); the only collective is the
-    all_gather of the last-token logits, inside the timed region."""
+def model_section(ctx: Ctx, name: str, bits: int, steps: int = 3, warm: int = 2):
+    """End-to-end prefill tokens/s of a random-init LLaMA-architecture model (bf16, N(0, 0.02) init, uniform random
+    tokens) with every attention layer replaced by apply_turboquant(bits, seed=42).  The global batch is split over
+    the ranks (full replica per GPU: strong scaling); the only collective is the all_gather of the last-token
+    logits, inside the timed region, as are the host-to-device copy of the token ids and the device-to-host read
+    of the logits.  The same model on HF's sdpa attention is timed first, beside it."""
     import turboquant_b200 as tq
     from transformers import LlamaConfig, LlamaForCausalLM
     from turboquant_b200.sharding import gather_rows, unit_range
 
-    L, hid, hq, hkv, hd, ffn, vocab, theta, gbatch, seq = MODEL_SHAPES[args.workload]
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
+    L, hid, hq, hkv, hd, ffn, vocab, theta, gbatch, seq = MODEL_SHAPES[name]
+    dev = ctx.dev
     cfg = LlamaConfig(num_hidden_layers=L, hidden_size=hid, num_attention_heads=hq, num_key_value_heads=hkv,
                       head_dim=hd, intermediate_size=ffn, vocab_size=vocab, rope_theta=theta,
                       max_position_embeddings=seq, initializer_range=0.02)
     torch.manual_seed(0)
     torch.set_default_dtype(torch.bfloat16)
-    with torch.device(dev):
-        model = LlamaForCausalLM(cfg).eval()
-    torch.set_default_dtype(torch.float32)
+    try:
+        with torch.device(dev):
+            model = LlamaForCausalLM(cfg).eval()
+    finally:
+        torch.set_default_dtype(torch.float32)
     ids_all = torch.randint(0, vocab, (gbatch, seq), generator=torch.Generator().manual_seed(0))
-    lo, hi = unit_range(gbatch, rank, world)
+    lo, hi = unit_range(gbatch, ctx.rank, ctx.world)
     ids_host = ids_all[lo:hi].pin_memory()
 
-    def forward(m):
+    def forward():
         with torch.no_grad():
             ids = ids_host.to(dev, non_blocking=True)
-            last = m(ids, logits_to_keep=1).logits[:, -1].float()
-            if dist is not None:
+            last = model(ids, logits_to_keep=1).logits[:, -1].float()
+            if ctx.dist is not None:
                 last = gather_rows(last)
             return last.cpu()
 
-    def timed(m, steps, warm):
-        for _ in range(warm):
-            forward(m)
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize(dev)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            out = forward(m)
-        e1.record()
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize(dev)
-        t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
-        if dist is not None:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item()), out
-
-    steps, warm = max(1, min(args.steps, 5)), max(1, min(args.warmup, 3))
-    ms_plain, logits_plain = timed(model, steps, warm)
-    tq.apply_turboquant(model, bits=args.bits, seed=42)
-    sampler = ClockSampler(local)
+    ms_plain, logits_plain = timed_steps(ctx, forward, steps, warm)
+    tq.apply_turboquant(model, bits=bits, seed=42)
+    sampler = ClockSampler(ctx.local)
     sampler.start()
-    ms_tq, logits_tq = timed(model, steps, warm)
+    ms_tq, logits_tq = timed_steps(ctx, forward, steps, warm)
     clocks = sampler.finish()
-    if rank == 0:
-        cos = torch.nn.functional.cosine_similarity(logits_tq, logits_plain, dim=-1).mean().item()
-        line = {"metric": f"{args.workload}_{args.bits}bit_prefill_tok_per_s", "value": gbatch * seq / (ms_tq * 1e-3),
-                "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warm, "ms_per_step": ms_tq,
-                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
-                "data": "synthetic", "config": {"workload": args.workload, "global_batch": gbatch, "seq_len": seq,
-                                                "layers": L, "bits": args.bits, "parallelism": f"dp{world}",
-                                                "logits": "last token, all_gather inside the timed region"},
-                "clocks": clocks,
-                "e2e": {"value": gbatch * seq / (ms_tq * 1e-3), "unit": "tok/s",
-                        "h2d_bytes_per_step": ids_host.numel() * 8, "d2h_bytes_per_step": gbatch * vocab * 4},
-                "uncompressed_attention_tok_per_s": gbatch * seq / (ms_plain * 1e-3),
-                "last_token_logit_cosine_vs_uncompressed": cos, "device_wait_faults": tq.device_fault_count(dev)}
-        print(json.dumps(line), flush=True)
-    if dist is not None:
-        dist.destroy_process_group()
+    cos = torch.nn.functional.cosine_similarity(logits_tq, logits_plain, dim=-1).mean().item()
+    faults = tq.device_fault_count(dev)
+    del model
+    torch.cuda.empty_cache()
+    return {"metric": f"{name}_{bits}bit_prefill_tok_per_s", "value": gbatch * seq / (ms_tq * 1e-3), "unit": "tok/s",
+            "ms_per_forward": ms_tq, "steps": steps, "warmup": warm, "scaling": "strong", "dtype": "bf16",
+            "config": {"model": name, "layers": L, "hidden": hid, "q_heads": hq, "kv_heads": hkv, "head_dim": hd,
+                       "global_batch": gbatch, "batch_per_gpu": hi - lo, "seq_len": seq, "bits": bits,
+                       "parallelism": f"dp{ctx.world}", "logits": "last token, all_gather inside the timed region"},
+            "h2d_bytes_per_step": ids_host.numel() * 8, "d2h_bytes_per_step": gbatch * vocab * 4,
+            "hf_sdpa_attention_tok_per_s": gbatch * seq / (ms_plain * 1e-3), "hf_sdpa_ms_per_forward": ms_plain,
+            "last_token_logit_cosine_vs_uncompressed": cos, "clocks": clocks, "device_wait_faults": faults}
 
 
-def run_quality(args):
-    """Estimator quality on a Qwen2.5-3B-shaped attention layer (16 query heads, 2 KV heads, d=128), the
-    synthetic stand-in for the reference's validate script (validate.py:137-196): compression ratio by bit
-    accounting, cosine between estimator and exact score rows, top-1 / top-5 agreement of the per-head
-    argmax, with the last key as proxy query.  Random-init projections of N(0,1) hidden states."""
+def config5_section(ctx: Ctx, bits: int, steps: int = 2, warm: int = 1, seq: int = 32768, gbatch: int = 64,
+                    chunk: int = 4):
+    """Strong scaling of the fused path on the sweep shape: K,V bf16 [64, 8, 32768, 128], Q [64, 32, 32768, 128],
+    N(0,1), causal.  The 64 x 8 (batch, KV head) units are split over the ranks by `sharding.unit_range` (whole
+    batch elements when the count divides, as here); every rank generates its share on its own device once
+    (resident inputs) and a step compresses and attends to all of it, `chunk` batch elements per call."""
     import turboquant_b200 as tq
-    dev = torch.device("cuda", 0)
-    out = {}
-    for T in (2048, 4096, 8192):
-        g = torch.Generator(device=dev).manual_seed(T)
-        k = torch.randn(1, 2, T, D, generator=g, device=dev).to(torch.bfloat16)
-        q = k[:, :, -1:, :]  # last key as proxy query, per KV head
-        exact = (q.float() @ k.float().transpose(-1, -2))[0, :, 0]  # [H, T]
-        for bits in (2, 3, 4):
-            kc = tq.TurboQuantCompressorV2(D, bits, 0, device=str(dev))
-            est = kc.asymmetric_attention_scores(q, kc.compress(k))[0, :, 0]
-            cos = torch.nn.functional.cosine_similarity(est, exact, dim=-1).mean().item()
-            top1 = (est.argmax(-1) == exact.argmax(-1)).float().mean().item()
-            top5 = torch.stack([(exact.argmax(-1)[h] == est[h].topk(5).indices).any() for h in range(2)]).float().mean().item()
-            ratio = 32.0 * D / (2 * bits * D + 48)
-            out[f"T{T}_b{bits}"] = {"compression_ratio": round(ratio, 2), "score_cosine": cos, "top1": top1, "top5": top5}
-    print(json.dumps({"metric": "tq_estimator_quality", "workload": "qwen2.5-3b-shaped attention, synthetic", "results": out}))
+    from turboquant_b200.sharding import unit_range
+    dev = ctx.dev
+    lo, hi = unit_range(gbatch * HKV, ctx.rank, ctx.world)
+    assert lo % HKV == 0 and hi % HKV == 0, "the unit split is expected to fall on batch boundaries here"
+    b_lo, b_hi = lo // HKV, hi // HKV
+    kc = tq.TurboQuantCompressorV2(D, bits, 42, device=str(dev))
+    vc = tq.TurboQuantCompressorMSE(D, bits, 10042, device=str(dev))
+    parts = []
+    for b0 in range(b_lo, b_hi, chunk):
+        nb = min(chunk, b_hi - b0)
+        g = torch.Generator(device=dev).manual_seed(1000 + b0)  # the data do not depend on the number of ranks
+        parts.append(tuple(torch.randn(nb, h, seq, D, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+                           for h in (HQ, HKV, HKV)))
+    outs = [torch.empty_like(p[0]) for p in parts]
+
+    def step():
+        for (q, k, v), o in zip(parts, outs):
+            o.copy_(tq.fused_attention(q, kc.compress(k), vc.compress(v), kc, vc, causal=True))
+        return outs[-1]
+
+    sampler = ClockSampler(ctx.local)
+    sampler.start()
+    ms, out = timed_steps(ctx, step, steps, warm)
+    clocks = sampler.finish()
+    keys = gbatch * HKV * seq
+    flops = attention_flops(gbatch, seq)
+    res = {"metric": METRIC, "value": keys / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms, "steps": steps,
+           "warmup": warm, "scaling": "strong",
+           "config": {"workload": "scaling_k64x8x32768", "global_batch": gbatch, "q_heads": HQ, "kv_heads": HKV,
+                      "seq_len": seq, "head_dim": D, "bits": bits, "units": gbatch * HKV,
+                      "units_per_gpu": hi - lo, "batch_per_gpu": b_hi - b_lo, "collectives": "none"},
+           "causal_pairs_per_s": causal_pairs(gbatch, seq) / (ms * 1e-3),
+           "tflops_whole_job": flops / (ms * 1e-3) / 1e12, "clocks": clocks,
+           "output_finite": bool(torch.isfinite(out.float()).all()), "device_wait_faults": tq.device_fault_count(dev)}
+    del parts, outs
+    torch.cuda.empty_cache()
+    return res
 
 
-def run_decode(args):
+def decode_section(ctx: Ctx, bits: int, steps: int = 50, warm: int = 3):
     """Decode step against a resident compressed KV cache: one query token per sequence (32 query / 8 KV heads,
-    d = 128) attends to Sk = 32768 cached keys, batch 8 — the per-GPU share of the scaling shape K,V
+    d = 128) attends to Sk = 32768 cached keys, batch 8 -- the per-GPU share of the scaling shape K,V
     [64, 8, 32768, 128] over 8 GPUs.  The cache (`CompressedKVCache`, capacity above the keys in use) is filled
-    outside the timed region; a step is `cache.attend(q)`.  The work is bound by the packed bytes: per key (16 (b-1) + 16 + 4) + (16 b + 2)."""
+    outside the timed region; a step is `cache.attend(q)`.  The work is bound by the packed bytes:
+    per key (16 (b-1) + 16 + 4) + (16 b + 2)."""
     import turboquant_b200 as tq
     from turboquant_b200 import _lib
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(dev)
-    batch, sk, bits = 8, 32768, args.bits
+    dev = ctx.dev
+    batch, sk = 8, 32768
     g = torch.Generator(device=dev).manual_seed(0)
     k = torch.randn(batch, HKV, sk, D, generator=g, device=dev).to(torch.bfloat16)
     v = torch.randn(batch, HKV, sk, D, generator=g, device=dev).to(torch.bfloat16)
@@ -324,137 +445,169 @@ def run_decode(args):
     k_new, v_new = k[:, :, -1:].clone(), v[:, :, -1:].clone()
     del k, v
 
-    def timed(steps):
-        for _ in range(max(args.warmup, 3)):
-            cache.attend(q, causal=True)
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            out = cache.attend(q, causal=True)
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / steps, out
+    def attend():
+        return cache.attend(q, causal=True)
 
-    def generation_steps(steps):
-        """Append the new token's key and value (two compression launches + six small copies), then attend."""
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        e0.record()
-        for _ in range(steps):
-            cache.append(k_new, v_new)
-            cache.attend(q, causal=True)
-        e1.record()
-        torch.cuda.synchronize()
+    def generation_step():
+        cache.append(k_new, v_new)
+        o = cache.attend(q, causal=True)
         cache.length = sk
-        return e0.elapsed_time(e1) / steps
+        return o
 
-    sampler = ClockSampler(0)
+    sampler = ClockSampler(ctx.local)
     sampler.start()
-    ms, out = timed(args.steps)
+    ms, out = timed_steps(ctx, attend, steps, warm)
     clocks = sampler.finish()
     # per-kernel times from a second pass: the profiling events sit between the three launches of a call and
     # keep them from overlapping (programmatic dependent launch), so the timed pass above runs without them
-    _lib.check(_lib.lib.tq_profile_begin(max(args.steps, 1) + max(args.warmup, 3)))
-    timed(args.steps)
+    _lib.check(_lib.lib.tq_profile_begin(steps + warm))
+    timed_steps(ctx, attend, steps, warm)
     ms_sum, launches = (ctypes.c_float * 5)(), (ctypes.c_int * 5)()
     _lib.check(_lib.lib.tq_profile_end(ms_sum, launches))
-    generation_steps(3)
-    gen_ms = generation_steps(min(max(args.steps, 1), 200))
+    gen_ms, _ = timed_steps(ctx, generation_step, steps, warm)
     kern_ms = ms_sum[3] / max(launches[3], 1)
     keys = batch * HKV * sk
     bytes_per_key = (16 * (bits - 1) + 16 + 4) + (16 * bits + 2)
     peaks = measured_peaks()
     achieved = keys * bytes_per_key / (kern_ms * 1e-3) / 1e9
-    line = {"metric": "tq_decode_keys_per_s", "value": keys / (ms * 1e-3), "unit": "keys/s", "n_gpus": 1,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "decode_b8_h32_kv8_sk32768", "batch_per_gpu": batch, "q_heads": HQ, "kv_heads": HKV,
-                       "new_tokens": 1, "cached_keys": sk, "head_dim": D, "bits": bits,
+    return {"metric": "tq_decode_keys_per_s", "value": keys * ctx.world / (ms * 1e-3), "unit": "keys/s",
+            "ms_per_call": ms, "steps": steps, "warmup": warm, "scaling": "weak", "dtype": "bf16",
+            "config": {"workload": "decode_b8_h32_kv8_sk32768", "batch_per_gpu": batch, "q_heads": HQ,
+                       "kv_heads": HKV, "new_tokens": 1, "cached_keys": sk, "head_dim": D, "bits": bits,
                        "l2": f"packed cache ({keys * bytes_per_key / 1e6:.0f} MB) exceeds the 126 MB L2; no flush"},
-            "clocks": clocks, "gpu_launches": 3 * args.steps,  # per call: query preparation, split-KV kernel, merge + back-rotation
+            "clocks": clocks, "gpu_launches_per_call": 3,  # query preparation, split-KV kernel, merge + back-rotation
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": achieved / peaks["hbm_gbs"], "traffic": None,
-                         "kernel": "decode_kernel", "ms_per_launch": kern_ms,
-                         "peak_source": peaks["source"]},
+                         "frac": achieved / peaks["hbm_gbs"], "traffic": None, "kernel": "decode_kernel",
+                         "ms_per_launch": kern_ms, "algorithmic_bytes_per_launch": keys * bytes_per_key,
+                         "peak_source": peaks["source"] + ", copy bandwidth"},
             "kernel_ms": {"prepare_queries": ms_sum[2] / max(launches[2], 1), "decode": kern_ms,
                           "merge_and_back_rotation": ms_sum[4] / max(launches[4], 1)},
             "generation_step_ms": gen_ms,  # append one token per sequence to the cache, then attend
             "device_wait_faults": tq.device_fault_count(dev), "output_norm": float(out.float().norm())}
-    print(json.dumps(line), flush=True)
 
 
-def main():
-    args = parse()
-    if args.workload in MODEL_SHAPES:
-        return run_model(args)
-    if args.workload == "quality":
-        return run_quality(args)
-    if args.workload == "decode":
-        return run_decode(args)
-    if args.impl == "reference":
-        return run_reference(args)
+def copy_bandwidth(ctx: Ctx, nbytes: int = 256 << 20, reps: int = 5):
+    """Host<->device copy rates of this rank's pinned buffers, one direction at a time (GB/s, best of `reps`),
+    and their minimum over the ranks when all ranks copy at once: what bounds the end-to-end figure."""
+    dev = ctx.dev
+    host = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    devb = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    res = {}
+    for name, (dst, src) in (("h2d", (devb, host)), ("d2h", (host, devb))):
+        best = float("inf")
+        for _ in range(reps):
+            ctx.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            dst.copy_(src, non_blocking=True)
+            e1.record()
+            torch.cuda.synchronize(dev)
+            best = min(best, e0.elapsed_time(e1))
+        gbs = nbytes / (best * 1e-3) / 1e9
+        res[f"{name}_gbs_rank0"] = gbs
+        res[f"{name}_gbs_min_over_ranks"] = ctx.min_over_ranks(gbs)
+    res["bytes"] = nbytes
+    res["concurrent_ranks"] = ctx.world
+    return res
 
+
+def run_headline(args):
     import turboquant_b200 as tq
     from turboquant_b200 import _lib
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
-
+    ctx = Ctx()
+    dev, world, rank = ctx.dev, ctx.world, ctx.rank
     batch, seq, bits = args.batch, args.seq, args.bits
     q, k, v = make_inputs(batch, seq, dev, seed=rank)  # every rank owns its own shard of units
     kc = tq.TurboQuantCompressorV2(D, bits, 42, device=str(dev))
     vc = tq.TurboQuantCompressorMSE(D, bits, 10042, device=str(dev))
 
-    def step(qd, kd, vd):
+    def step(qd=q, kd=k, vd=v):
         ck = kc.compress(kd)
         cv = vc.compress(vd)
         return tq.fused_attention(qd, ck, cv, kc, vc, causal=True)
 
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize(dev)
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
+        out = step()
+    ctx.barrier()
 
-    for _ in range(max(args.warmup, 3)):
-        out = step(q, k, v)
-    barrier()
-
-    sampler = ClockSampler(torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ else local)
+    sampler = ClockSampler(ctx.local)
     sampler.start()
     _lib.check(_lib.lib.tq_profile_begin(max(args.steps, 1)))
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
     for _ in range(args.steps):
-        out = step(q, k, v)
+        out = step()
     ev1.record()
-    barrier()
-    ms_sum = (ctypes.c_float * 5)()
-    launches = (ctypes.c_int * 5)()
+    ctx.barrier()
+    ms_sum, launches = (ctypes.c_float * 5)(), (ctypes.c_int * 5)()
     _lib.check(_lib.lib.tq_profile_end(ms_sum, launches))
     clocks = sampler.finish()
-    elapsed_ms = ev0.elapsed_time(ev1)
-    t = torch.tensor([elapsed_ms], device=dev, dtype=torch.float64)
-    if dist is not None:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    elapsed_ms = float(t.item())
-    ms_per_step = elapsed_ms / args.steps
+    ms_per_step = ctx.max_over_ranks(ev0.elapsed_time(ev1)) / args.steps
     keys_per_rank = batch * HKV * seq
     value = keys_per_rank * world / (ms_per_step * 1e-3)
+    launches_per_step = int(sum(launches)) // max(args.steps, 1)
 
-    # ---- end to end through the public API with pinned host buffers -----------------------
+    # ---- roofline of the dominant kernel (fused attention: tensor-core bound) ---------------------------
+    peaks = measured_peaks()
+    attn_ms = ms_sum[3] / max(launches[3], 1)
+    flops = attention_flops(batch, seq)
+    achieved = flops / (attn_ms * 1e-3) / 1e12
+    # DRAM bytes per launch: one ncu capture of this kernel at batch 1 (profiles/attention_c2_kernel_b1_s8192.md:
+    # dram__bytes_read.sum + dram__bytes_write.sum = 103.3 MB; raw queries in, outputs out, packed keys and
+    # values), scaled by the batch, which it is proportional to; the algorithmic bytes beside it
+    algorithmic_bytes = batch * (2 * HQ * seq * D * 2 + HKV * seq * ((16 * (bits - 1) + 16 + 4) + (16 * bits + 2)))
+    traffic = 103.3e6 * batch if (seq == S and D == 128 and bits == 3) else None
+    roofline = {"bound": "tensor", "achieved": achieved, "unit": "TFLOP/s",
+                "peak": peaks["tflops_burst"], "frac": achieved / peaks["tflops_burst"],
+                "frac_burst": achieved / peaks["tflops_burst"], "frac_sustained": None,
+                "frac_note": "`frac` = `frac_burst`: the timed region lasts tens of milliseconds at full SM clock, the "
+                             "conditions of the burst peak; `frac_sustained` comes from the seconds-long pass below, "
+                             "against the sustained peak",
+                "peak_burst": peaks["tflops_burst"], "peak_sustained": peaks["tflops_sustained"],
+                "traffic": traffic, "algorithmic_bytes_per_launch": algorithmic_bytes,
+                "flops_per_launch": flops, "kernel": "attention_c2_kernel", "ms_per_launch": attn_ms,
+                "peak_source": peaks["source"],
+                "kernel_ms": {"compress": (ms_sum[0] + ms_sum[1]) / max(args.steps, 1),
+                              "compress_keys": ms_sum[0] / max(launches[0], 1),
+                              "compress_values": ms_sum[1] / max(launches[1], 1),
+                              "prepare_queries": ms_sum[2] / max(launches[2], 1),
+                              "attention": attn_ms, "back_rotation": ms_sum[4] / max(launches[4], 1)}}
+    comp_ms = (ms_sum[0] + ms_sum[1]) / max(args.steps, 1)
+    comp_bytes = batch * HKV * seq * (2 * D * 2 + (16 * (bits - 1) + 16 + 4) + (16 * bits + 2))
+    roofline["compress"] = {"bound": "hbm", "achieved": comp_bytes / (comp_ms * 1e-3) / 1e9 if comp_ms > 0 else None,
+                            "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                            "frac": comp_bytes / (comp_ms * 1e-3) / 1e9 / peaks["hbm_gbs"] if comp_ms > 0 else None,
+                            "algorithmic_bytes_per_step": comp_bytes, "ms_per_step": comp_ms}
+
+    # ---- the same kernel under sustained conditions: back-to-back steps for >= 3 s -------------------------
+    if "sustained" in args.want:
+        n_sus = max(50, int(3200.0 / ms_per_step))
+        sampler = ClockSampler(ctx.local)
+        sampler.start()
+        _lib.check(_lib.lib.tq_profile_begin(min(n_sus, 4096)))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n_sus):
+            out = step()
+        e1.record()
+        ctx.barrier()
+        s_sum, s_launch = (ctypes.c_float * 5)(), (ctypes.c_int * 5)()
+        _lib.check(_lib.lib.tq_profile_end(s_sum, s_launch))
+        sus_clocks = sampler.finish()
+        sus_ms = s_sum[3] / max(s_launch[3], 1)
+        sus_ach = flops / (sus_ms * 1e-3) / 1e12
+        roofline["frac_sustained"] = sus_ach / peaks["tflops_sustained"]
+        roofline["sustained_pass"] = {"steps": n_sus, "seconds": e0.elapsed_time(e1) * 1e-3, "ms_per_launch": sus_ms,
+                                      "achieved": sus_ach, "peak": peaks["tflops_sustained"], "clocks": sus_clocks}
+
+    # ---- end to end through the public API with pinned host buffers ----------------------------------------
     # Every step copies its q, k, v from pinned host memory to the device, runs compress + fused attention
     # through the public Python API and copies the output back to pinned host memory.  Copies and compute of
     # consecutive steps overlap on three streams (double-buffered device inputs), as a serving loop would.
     e2e = None
-    if not args.no_e2e:
+    if "e2e" in args.want:
         hq, hk, hv = (t_.cpu().pin_memory() for t_ in (q, k, v))
         houts = [torch.empty(out.shape, dtype=out.dtype).pin_memory() for _ in range(2)]
         n_e2e = max(4, min(args.steps, 10))
@@ -489,71 +642,213 @@ def main():
 
         for ev in free_in + free_out:
             ev.record(torch.cuda.current_stream(dev))
-        barrier()
+        ctx.barrier()
         e2e_loop(2)
-        barrier()
+        ctx.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(s_in)
         keep = e2e_loop(n_e2e)
         s_out.wait_stream(s_run)
         s_out.wait_stream(s_in)
         e1.record(s_out)
-        barrier()
+        ctx.barrier()
         del keep
-        te = torch.tensor([e0.elapsed_time(e1) / n_e2e], device=dev, dtype=torch.float64)
-        if dist is not None:
-            dist.all_reduce(te, op=dist.ReduceOp.MAX)
-        e2e = {"value": keys_per_rank * world / (float(te.item()) * 1e-3), "unit": UNIT,
-               "h2d_bytes_per_step": sum(h.numel() * h.element_size() for h in (hq, hk, hv)),
-               "d2h_bytes_per_step": houts[0].numel() * houts[0].element_size(), "ms_per_step": float(te.item()),
-               "steps": n_e2e, "overlap": "H2D, compute and D2H of consecutive steps on three streams"}
+        te = ctx.max_over_ranks(e0.elapsed_time(e1) / n_e2e)
+        h2d = sum(h.numel() * h.element_size() for h in (hq, hk, hv))
+        d2h = houts[0].numel() * houts[0].element_size()
+        bw = copy_bandwidth(ctx)
+        # what the copies alone would take at the rates just measured with all ranks copying at once
+        floor_ms = max(h2d / (bw["h2d_gbs_min_over_ranks"] * 1e6), d2h / (bw["d2h_gbs_min_over_ranks"] * 1e6))
+        e2e = {"value": keys_per_rank * world / (te * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": te, "steps": n_e2e,
+               "overlap": "H2D, compute and D2H of consecutive steps on three streams",
+               "copy_bandwidth": bw, "copy_floor_ms_per_step": floor_ms, "cpu_affinity": ctx.affinity,
+               "limiter": "host<->device copies" if floor_ms > 0.6 * te else "compute"}
+        del hq, hk, hv, houts, dbuf
 
     faults = tq.device_fault_count(dev)
-    if rank != 0:
-        if dist is not None:
-            dist.destroy_process_group()
-        return
+    out_norm = float(out.float().norm())
+    del q, k, v, out
+    torch.cuda.empty_cache()
 
-    # ---- roofline of the dominant kernel (fused attention: tensor-core bound) ---------------
-    peaks = measured_peaks()
-    attn_ms = ms_sum[3] / max(launches[3], 1)
-    # algorithmic flops of the fused kernel: 2d (q.K_hat) + 2d (q_s.sign) + 2d (P.V_hat) per causal pair, plus
-    # per query row the preparation q [Pi ; coeff S]^T (2 * 2d * d) and the output back-rotation (2 d^2)
-    flops = 6.0 * D * causal_pairs(batch, seq) + 6.0 * D * D * batch * HQ * seq
-    achieved = flops / (attn_ms * 1e-3) / 1e12 if attn_ms > 0 else None
-    roofline = {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
-                "frac": (achieved / peaks["tflops"]) if achieved else None,
-                # DRAM bytes per launch: ncu capture at batch 1 (74.0 MB read + 29.3 MB written; queries in,
-                # outputs out, packed keys and values), which scales with batch
-                "traffic": 103.3e6 * batch if (seq == S and D == 128) else None,
-                "kernel": "attention_c2_kernel", "ms_per_launch": attn_ms, "peak_source": peaks["source"],
-                "kernel_ms": {"compress_keys": ms_sum[0] / max(launches[0], 1),
-                              "compress_values": ms_sum[1] / max(launches[1], 1),
-                              "prepare_queries": ms_sum[2] / max(launches[2], 1),
-                              "attention": attn_ms, "back_rotation": ms_sum[4] / max(launches[4], 1)}}
-
-    cpu = None
-    if not args.no_cpu_baseline and world == 1:
-        cpu_sample(bits, 1024)
-        sec, threads = cpu_sample(bits, seq, repeats=2)
-        units = batch * HQ
+    # ---- baselines on rank 0 --------------------------------------------------------------------------------
+    cpu = gpu_ref = None
+    units = batch * HQ
+    if "cpu" in args.want and world == 1:
+        threads = os.cpu_count()
+        torch.set_num_threads(threads)
+        reference_unit(bits, 1024)
+        secs = [reference_unit(bits, seq) for _ in range(3)]
+        sec = min(secs[1:])
         cpu = {"value": batch * HKV * seq / (sec * units), "unit": UNIT, "cores": threads, "kind": "port",
-               "sample": f"one (batch, query head) unit of {units}: compress of S={seq} keys and values, "
-                         f"score/softmax/PV rows for {min(CPU_Q_ROWS, seq)} of {seq} queries at full width, scaled to "
-                         f"the unit ({sec:.2f} s) and then linearly to the workload; reference PyTorch path"}
+               "sampled_s": sum(secs), "unit_s": sec, "scale_factor": units,
+               "sample": f"one whole (batch, query head) unit of {units}: compress of S={seq} keys and values, all "
+                         f"{seq} score rows at full width, fp32 softmax, P@V, reference PyTorch path (oracle "
+                         f"restatement), best of 2 after a warm-up ({sec:.2f} s); scaled by the unit count"}
+    if "gpuref" in args.want and rank == 0:
+        reference_unit(bits, 1024, device=dev)
+        secs = [reference_unit(bits, seq, device=dev) for _ in range(3)]
+        sec = min(secs[1:])
+        gpu_ref = {"value": batch * HKV * seq / (sec * units), "unit": UNIT, "kind": "port on cuda",
+                   "unit_s": sec, "scale_factor": units,
+                   "what": "secondary baseline: the same reference PyTorch path (oracle restatement, literal "
+                           "arithmetic, GQA-expanded, full score rows) with its tensors on the GPU, one whole "
+                           "(batch, query head) unit, scaled by the unit count; torch/cuBLAS kernels, none of this "
+                           "library's"}
+        torch.cuda.empty_cache()
+    ctx.barrier()
 
-    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "op_level_gqa4_s8192", "batch_per_gpu": batch, "q_heads": HQ, "kv_heads": HKV,
-                       "seq_len": seq, "head_dim": D, "bits": bits, "causal": True,
-                       "l2": "inputs (402 MB per step) exceed the 126 MB L2; no flush",
-                       "causal_pairs_per_s": causal_pairs(batch, seq) * world / (ms_per_step * 1e-3)},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": (int(sum(launches)) + 3 * args.steps) * world,  # + the three constant-operand builders per step
-            "roofline": roofline, "cpu_baseline": cpu, "device_wait_faults": faults}
+    extra = {}
+    if "decode" in args.want:
+        extra["decode"] = decode_section(ctx, bits)
+    if "llama8b" in args.want:
+        extra["models"] = {"llama8b": model_section(ctx, "llama8b", bits)}
+    if "config5" in args.want:
+        extra["scaling_config5"] = config5_section(ctx, bits)
+
+    if rank == 0:
+        cfg = workload_config(args, world)
+        cfg["l2"] = "inputs (402 MB per step) exceed the 126 MB L2; no flush"
+        cfg["causal_pairs_per_s"] = causal_pairs(batch, seq) * world / (ms_per_step * 1e-3)
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": warm, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg,
+                "clocks": clocks, "e2e": e2e,
+                "gpu_launches": launches_per_step * args.steps * world,  # this library's kernels in the timed region
+                "gpu_launches_per_step": launches_per_step,
+                "roofline": roofline, "cpu_baseline": cpu, "gpu_pytorch_baseline": gpu_ref,
+                "device_wait_faults": faults, "output_norm": out_norm}
+        line.update(extra)
+        print(json.dumps(line), flush=True)
+    ctx.close()
+
+
+# ---------------------------------------------------------------------------------------------------------
+# stand-alone workloads (one JSON line each)
+# ---------------------------------------------------------------------------------------------------------
+
+def run_model(args):
+    ctx = Ctx()
+    res = model_section(ctx, args.workload, args.bits, steps=max(1, min(args.steps, 5)), warm=max(1, min(args.warmup, 3)))
+    if ctx.rank == 0:
+        line = {"metric": res["metric"], "value": res["value"], "unit": "tok/s", "n_gpus": ctx.world, "steps": res["steps"],
+                "warmup": res["warmup"], "ms_per_step": res["ms_per_forward"], "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": res["config"],
+                "clocks": res["clocks"],
+                "e2e": {"value": res["value"], "unit": "tok/s", "h2d_bytes_per_step": res["h2d_bytes_per_step"],
+                        "d2h_bytes_per_step": res["d2h_bytes_per_step"]},
+                "uncompressed_attention_tok_per_s": res["hf_sdpa_attention_tok_per_s"],
+                "last_token_logit_cosine_vs_uncompressed": res["last_token_logit_cosine_vs_uncompressed"],
+                "device_wait_faults": res["device_wait_faults"]}
+        print(json.dumps(line), flush=True)
+    ctx.close()
+
+
+def run_config5(args):
+    ctx = Ctx()
+    res = config5_section(ctx, args.bits, steps=max(1, min(args.steps, 5)), warm=max(1, min(args.warmup, 2)))
+    if ctx.rank == 0:
+        res.update({"n_gpus": ctx.world, "higher_is_better": True, "vs_baseline": None, "dtype": "bf16",
+                    "data": "synthetic"})
+        print(json.dumps(res), flush=True)
+    ctx.close()
+
+
+def run_decode(args):
+    ctx = Ctx()
+    res = decode_section(ctx, args.bits, steps=max(args.steps, 1), warm=max(args.warmup, 3))
+    if ctx.rank == 0:
+        res.update({"n_gpus": ctx.world, "ms_per_step": res["ms_per_call"], "higher_is_better": True,
+                    "vs_baseline": None, "data": "synthetic", "gpu_launches": 3 * res["steps"]})
+        print(json.dumps(res), flush=True)
+    ctx.close()
+
+
+def run_gpt2small(args):
+    """The GPT-2-small configuration (12 layers, 768 wide, 12 heads of 64, 1024 uniform random tokens from seed 0,
+    fp32, N(0, 0.02) init from seed 0, 3 bits, seed 42): one full forward through apply_turboquant on the GPU in
+    fp32 parity mode, the oracle model (reference arithmetic) on the host cores beside it, both against
+    uncompressed attention, and the per-layer causal score cosine of the estimator."""
+    import copy
+
+    import turboquant_b200 as tq
+    from oracle.model_oracle import OracleCore, causal_score_cosine, logits_agreement, oracle_model
+    from transformers import GPT2Config, GPT2LMHeadModel
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    torch.manual_seed(0)
+    model = GPT2LMHeadModel(GPT2Config(attn_pdrop=0.0, resid_pdrop=0.0, embd_pdrop=0.0)).eval()
+    ids = torch.randint(0, 50257, (1, 1024), generator=torch.Generator().manual_seed(0))
+    torch.set_num_threads(os.cpu_count())
+    with torch.no_grad():
+        t0 = time.perf_counter()
+        plain = model(ids).logits
+        t_plain = time.perf_counter() - t0
+        ref = oracle_model(model, "GPT2Attention", "gpt2", args.bits, 42)
+        cores = [m for m in ref.modules() if isinstance(m, OracleCore)]
+        for c in cores:
+            c.record = {}
+        t0 = time.perf_counter()
+        want = ref(ids).logits
+        t_ref = time.perf_counter() - t0
+        gpu = tq.apply_turboquant(copy.deepcopy(model).to(dev), bits=args.bits, seed=42)
+        ids_d = ids.to(dev)
+        for _ in range(3):
+            got = gpu(ids_d).logits
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(max(args.steps, 1)):
+            got = gpu(ids_d).logits
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / max(args.steps, 1)
+        got = got.cpu()
+        cos_gpu, cos_ref = [], []
+        for core, adapter in zip(cores, (m for m in gpu.modules() if hasattr(m, "key_compressor"))):
+            qh, kh = core.record["q"], core.record["k"]
+            exact = qh @ kh.transpose(-1, -2)
+            kcomp = adapter.key_compressor
+            est = kcomp.asymmetric_attention_scores(qh.to(dev), kcomp.compress(kh.to(dev))).cpu()
+            cos_gpu.append(round(float(causal_score_cosine(est, exact).mean()), 4))
+            cos_ref.append(round(float(causal_score_cosine(core.record["scores"], exact).mean()), 4))
+    line = {"metric": "gpt2small_3bit_forward_tok_per_s", "value": 1024 / (ms * 1e-3), "unit": "tok/s", "n_gpus": 1,
+            "steps": max(args.steps, 1), "warmup": 3, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "gpt2_small_shape", "layers": 12, "hidden": 768, "heads": 12, "head_dim": 64,
+                       "seq_len": 1024, "batch": 1, "bits": args.bits, "seed": 42, "mode": "fp32 parity kernels"},
+            "logits_vs_oracle_model": logits_agreement(got, want),
+            "logits_vs_uncompressed": logits_agreement(got, plain),
+            "oracle_logits_vs_uncompressed": logits_agreement(want, plain),
+            "reference_figures": {"rel_err": 0.164, "top1": 0.642, "layer_cosines": "0.909 .. 0.928"},
+            "layer_score_cosine": cos_gpu, "oracle_layer_score_cosine": cos_ref,
+            "cpu_baseline": {"value": 1024 / t_ref, "unit": "tok/s", "cores": os.cpu_count(), "kind": "port",
+                             "sample": f"the whole forward of the oracle model on the host cores ({t_ref:.2f} s; "
+                                       f"uncompressed attention {t_plain:.2f} s)"},
+            "device_wait_faults": tq.device_fault_count(dev)}
     print(json.dumps(line), flush=True)
-    if dist is not None:
-        dist.destroy_process_group()
+
+
+def run_quality(args):
+    from turboquant_b200.validate import run_validation
+    print(json.dumps(run_validation(bits_list=(2, 3, 4), contexts=(2048, 4096, 8192))), flush=True)
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        return run_reference(args)
+    if args.workload in MODEL_SHAPES:
+        return run_model(args)
+    if args.workload == "config5":
+        return run_config5(args)
+    if args.workload == "gpt2small":
+        return run_gpt2small(args)
+    if args.workload == "quality":
+        return run_quality(args)
+    if args.workload == "decode":
+        return run_decode(args)
+    return run_headline(args)
 
 
 if __name__ == "__main__":

@@ -117,6 +117,10 @@ class KeyParams:
         (compressors.py:189, tests/test_kernels.py:296-314)."""
         return self.S.float() @ self.Pi.float().T
 
+    def to(self, device) -> "KeyParams":
+        """The same constants on another device (the reference's `device=` constructor argument)."""
+        return KeyParams(self.head_dim, self.bits, self.Pi.to(device), self.S.to(device), self.centroids.to(device))
+
 
 @dataclass
 class ValueParams:
@@ -129,6 +133,9 @@ class ValueParams:
     @property
     def boundaries(self) -> torch.Tensor:
         return (self.centroids[:-1] + self.centroids[1:]) / 2
+
+    def to(self, device) -> "ValueParams":
+        return ValueParams(self.head_dim, self.bits, self.Pi.to(device), self.centroids.to(device))
 
 
 def make_key_params(d: int, bits: int, seed: int) -> KeyParams:
@@ -219,8 +226,10 @@ def _normalise_rotate(states: torch.Tensor, Pi: torch.Tensor):
     return flat, norms, rotated
 
 
-def key_compress(states: torch.Tensor, P: KeyParams) -> dict:
+def key_compress(states: torch.Tensor, P: KeyParams, pack: bool = True) -> dict:
     """Key compression, reference PyTorch branch (compressors.py:98-112, :139-161).
+    `pack=False` leaves out the packed wire-format view (host-side numpy work that the
+    reference's PyTorch branch does not do): what a timed baseline runs, on any device.
 
     Returns the reference's dict (`k_mse` fp16, `qjl_signs` int8 +-1,
     `residual_norm` fp16, `shape`) plus the quantities the packed wire format
@@ -236,6 +245,10 @@ def key_compress(states: torch.Tensor, P: KeyParams) -> dict:
     rnorm = torch.norm(resid, dim=-1)
     proj = resid @ P.S.float().T
     bits01 = (proj >= 0)
+    if not pack:
+        return {"k_mse": k_mse.to(torch.float16).reshape(B, H, S, D),
+                "qjl_signs": (bits01.to(torch.int8) * 2 - 1).reshape(B, H, S, D),
+                "residual_norm": rnorm.to(torch.float16).reshape(B, H, S), "shape": (B, H, S, D)}
     return {
         "k_mse": k_mse.to(torch.float16).reshape(B, H, S, D),
         "qjl_signs": (bits01.to(torch.int8) * 2 - 1).reshape(B, H, S, D),
@@ -253,11 +266,13 @@ def key_compress(states: torch.Tensor, P: KeyParams) -> dict:
     }
 
 
-def value_compress(states: torch.Tensor, P: ValueParams) -> dict:
-    """Value compression (compressors.py:270-294)."""
+def value_compress(states: torch.Tensor, P: ValueParams, pack: bool = True) -> dict:
+    """Value compression (compressors.py:270-294); `pack` as in key_compress."""
     B, H, S, D = states.shape
     _, norms, rotated = _normalise_rotate(states, P.Pi)
     idx = quantize_indices(rotated, P.centroids.float())
+    if not pack:
+        return {"indices": idx.to(torch.uint8), "vec_norms": norms.squeeze(-1).to(torch.float16), "shape": (B, H, S, D)}
     return {
         "indices": idx.to(torch.uint8),
         "vec_norms": norms.squeeze(-1).to(torch.float16),
