@@ -401,7 +401,8 @@ def config5_section(ctx: Ctx, bits: int, steps: int = 2, warm: int = 1, seq: int
 
     def step():
         for (q, k, v), o in zip(parts, outs):
-            o.copy_(tq.fused_attention(q, kc.compress(k), vc.compress(v), kc, vc, causal=True))
+            ck, cv = tq.compress_kv(k, v, kc, vc)
+            o.copy_(tq.fused_attention(q, ck, cv, kc, vc, causal=True))
         return outs[-1]
 
     sampler = ClockSampler(ctx.local)
@@ -523,8 +524,7 @@ def run_headline(args):
     vc = tq.TurboQuantCompressorMSE(D, bits, 10042, device=str(dev))
 
     def step(qd=q, kd=k, vd=v):
-        ck = kc.compress(kd)
-        cv = vc.compress(vd)
+        ck, cv = tq.compress_kv(kd, vd, kc, vc)
         return tq.fused_attention(qd, ck, cv, kc, vc, causal=True)
 
     warm = max(args.warmup, 3)

@@ -128,7 +128,40 @@ int tq_quantize_rotated(const float* rotated, int64_t n, int d, const float* bou
 int tq_dequantize(const uint8_t* packed, int64_t n, int d, const float* centroids, int b,
                   float* out, void* stream);
 
+/* ---- per-compressor constants, prepared once ------------------------------------------- */
+
+/* Everything a launch needs that depends only on a (key compressor, value compressor) pair -- the fp32 matrices
+ * and codebooks and the operand images the tensor-core kernels copy into shared memory -- in one device buffer of
+ * tq_constants_bytes(d, bits) bytes (256-byte aligned, owned by the caller), filled once per layer by
+ * tq_prepare_constants.  The *_prepared / tq_compress_kv entry points read it and rebuild nothing, so a call is
+ * its own kernels only.  Arguments as for tq_compress_keys / tq_compress_values / tq_attention_fwd:
+ *   Pi_k, S_eff [d, d], centroids_k [2^(bits-1)], boundaries_k [2^(bits-1) - 1]   (key side)
+ *   Pi_v [d, d], centroids_v [2^bits], boundaries_v [2^bits - 1]                  (value side)
+ * Replaces the constants the reference's compressors hold as attributes and re-read in every call
+ * (compressors.py:42-70, :230-246) and the per-call table builds of kernels/attention.py:300-330. */
+size_t tq_constants_bytes(int d, int bits);
+int tq_prepare_constants(const float* Pi_k, const float* S_eff, const float* centroids_k,
+                         const float* boundaries_k, const float* Pi_v, const float* centroids_v,
+                         const float* boundaries_v, int bits, int d, void* constants, size_t constants_bytes,
+                         void* stream);
+
 /* ---- compression ---------------------------------------------------------------- */
+
+/* Keys and values of one layer in ONE launch: tq_compress_keys(keys) and tq_compress_values(values) with the
+ * constants taken from a prepared buffer.  keys, values: [B, H, S, d] of `dtype` with their own element strides;
+ * either may be NULL, which skips that side.  Vector (b, h, s) goes to row (b*H + h)*kv_capacity + kv_offset + s
+ * of every output array (kv_capacity = S, kv_offset = 0: the contiguous layout of the separate calls).
+ * bf16 inputs of head_dim 128 in TQ_MODE_BF16 take the fused kernel (TMA-staged tiles, rotation and sketch on
+ * tcgen05); anything else runs the per-side kernels, same bytes.
+ * Replaces TurboQuantCompressorV2.compress + TurboQuantCompressorMSE.compress as the family adapters call them
+ * back to back (src/transformers_turboquant/families/llama.py:103-104; compressors.py:98-161, :270-294). */
+int tq_compress_kv(const void* keys, const void* values, int dtype, int64_t B, int64_t H, int64_t S, int d,
+                   int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s,
+                   int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_s,
+                   const void* constants, int bits,
+                   uint8_t* key_idx, uint8_t* key_signs, uint16_t* key_vec_norms, uint16_t* key_residual_norms,
+                   uint8_t* val_idx, uint16_t* val_vec_norms,
+                   int64_t kv_capacity, int64_t kv_offset, int mode, void* stream);
 
 /* Key compression: norm, normalise, rotate by Pi^T, Lloyd-Max index with bits-1 bits,
  * residual, its norm, and the sign of its QJL sketch, for every vector of
@@ -217,6 +250,24 @@ int tq_attention_fwd(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq
                      void* out, int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s,
                      void* workspace, size_t workspace_bytes, int mode, void* stream);
 
+/* tq_attention_fwd / tq_attention_fwd_cached with the constants taken from a prepared buffer: no operand is
+ * rebuilt per call, and the scratch need drops to tq_attention_prepared_workspace_bytes -- zero for prefill-sized
+ * calls at head_dim 128 in TQ_MODE_BF16 (`workspace` may then be NULL).  kv_capacity = Sk is the contiguous
+ * layout; a larger capacity is the persistent-cache layout of tq_attention_fwd_cached (same shape limits).
+ * Replaces the attention core of the family adapters (families/llama.py:100-114, gpt2.py:90-110). */
+size_t tq_attention_prepared_workspace_bytes(int64_t B, int64_t Hq, int64_t Sq, int64_t Hkv, int64_t Sk,
+                                             int64_t kv_capacity, int d, int mode);
+int tq_attention_fwd_prepared(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq, int d,
+                              int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                              int64_t Hkv, int64_t Sk, int64_t kv_capacity,
+                              const uint8_t* key_idx, const uint8_t* key_signs,
+                              const uint16_t* key_vec_norms, const uint16_t* key_residual_norms,
+                              const uint8_t* val_idx, const uint16_t* val_vec_norms,
+                              const void* constants, int bits, float sm_scale, int causal,
+                              const float* mask, int64_t mask_stride_b, int64_t mask_stride_q,
+                              void* out, int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s,
+                              void* workspace, size_t workspace_bytes, int mode, void* stream);
+
 /* tq_attention_fwd for callers that cannot hand over scratch memory (no counterpart in the
  * reference).  Meant for hosts that may not call cudaMalloc or any other allocator: a plugin
  * inside a serving process whose device memory belongs to someone else, or a call site that
@@ -226,9 +277,11 @@ int tq_attention_fwd(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq
  *   - A problem whose tq_attention_workspace_bytes exceeds that size is rejected with
  *     TQ_ERR_WORKSPACE and nothing is launched (at d=128 the array covers about 43 000 query
  *     rows B*Hq*Sq in bf16 mode, 32 000 in fp32 mode).
- *   - The first call on each device looks up the array's device address (one runtime query,
- *     no allocation); make that first call outside any stream capture.  No call allocates or
- *     frees device memory.
+ *   - The first call on each device looks up the array's device address (one runtime query) and,
+ *     like the first call of any entry point on a device, installs the library's status page
+ *     (pinning 4 KB of the library's own static storage, a few small synchronous copies); neither
+ *     allocates.  Make that first call outside any stream capture.  No call allocates or frees
+ *     device memory.
  *   - All calls on a device share the one array.  Every byte a call reads from it was written
  *     earlier in the same call, so stale contents are harmless and nothing has to be cleared;
  *     but two calls that overlap on the GPU (different streams, or threads) race on it.

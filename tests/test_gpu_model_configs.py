@@ -99,16 +99,18 @@ def test_llama8b_shaped_bf16_layers_match_oracle():
         return out
 
     raw_kv = []
-    for a in adapters:
-        for comp in (a.key_compressor, a.val_compressor):
-            fn = comp.compress
-            comp.compress = (lambda x, fn=fn: (raw_kv.append(x.detach().float().cpu()), fn(x))[1])
-    _rope_gqa.fused_attention = recording
+    real_compress = _rope_gqa.compress_kv
+
+    def recording_compress(k, v, kc, vc):
+        raw_kv.extend((k.detach().float().cpu(), v.detach().float().cpu()))
+        return real_compress(k, v, kc, vc)
+
+    _rope_gqa.fused_attention, _rope_gqa.compress_kv = recording, recording_compress
     try:
         with torch.no_grad():
             got = gpu(ids.cuda()).logits.float().cpu()
     finally:
-        _rope_gqa.fused_attention = real
+        _rope_gqa.fused_attention, _rope_gqa.compress_kv = real, real_compress
     assert len(seen) == 2 and len(raw_kv) == 4
     # (1) every layer's attention core against the oracle core on the same bf16 q, k, v
     for layer, rec in enumerate(seen):

@@ -7,6 +7,36 @@
 
 namespace tq {
 
+// Layout of the per-compressor constants buffer that tq_prepare_constants fills once: byte offsets of its parts
+// (each a multiple of 256) for head_dim d.  Everything a launch needs that depends only on the compressor pair:
+// the fp32 matrices and codebooks themselves, and the operand images the tensor-core kernels bulk-copy into
+// shared memory (so that no call rebuilds them).
+struct ConstLayout {
+  size_t header;                                                  // magic, d, bits
+  size_t pi_k, s_eff, pi_v, cen_k, bnd_k, cen_v, bnd_v;           // fp32 originals
+  size_t w_cat_pair, w_unrot_pair, luts, w_cat_plain, w_unrot_plain;  // attention: bf16 operand images, fp16 pair tables
+  size_t pik_hi, pik_lo, se_hi, se_lo, piv_hi, piv_lo;            // compression: split-bf16 K-major operand images
+  size_t total;
+};
+constexpr uint32_t kConstMagic = 0x31425154u;  // "TQB1"
+inline ConstLayout const_layout(int d) {
+  ConstLayout L{};
+  size_t off = 0;
+  auto take = [&](size_t bytes) { const size_t at = off; off += (bytes + 255) & ~(size_t)255; return at; };
+  const size_t m32 = (size_t)d * d * 4, m16 = (size_t)d * d * 2;
+  L.header = take(256);
+  L.pi_k = take(m32); L.s_eff = take(m32); L.pi_v = take(m32);
+  L.cen_k = take(64); L.bnd_k = take(64); L.cen_v = take(64); L.bnd_v = take(64);
+  L.w_cat_pair = take(2 * m16); L.w_unrot_pair = take(m16); L.luts = take(2048);
+  L.w_cat_plain = take(2 * m16); L.w_unrot_plain = take(m16);
+  L.pik_hi = take(m16); L.pik_lo = take(m16); L.se_hi = take(m16); L.se_lo = take(m16);
+  L.piv_hi = take(m16); L.piv_lo = take(m16);
+  L.total = off;
+  return L;
+}
+int prepare_constants(const float* Pi_k, const float* S_eff, const float* cen_k, const float* bnd_k, const float* Pi_v,
+                      const float* cen_v, const float* bnd_v, int bits, int d, void* constants, cudaStream_t stream);
+
 struct AttnArgs {
   const void* q_cat;   // fp32 [n, 2d] (fp32 mode) or bf16 [n, 2d] (bf16 mode), row n = (b*Hq+h)*Sq+s
   int64_t Hq, Sq, Hkv, Sk;
@@ -40,9 +70,15 @@ int attention_fwd_fp32(const void* q, int dtype, int64_t B, int64_t Hq, int64_t 
                        cudaStream_t stream);
 
 // bf16 mode: tcgen05 query preparation, tcgen05 flash kernel, tcgen05 back-rotation.
+// `prepared` (optional): a constants buffer filled by prepare_constants for the same matrices; the operand images
+// are then taken from it and nothing is rebuilt.
 int attention_fwd_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq, int d, int64_t sb, int64_t sh,
                        int64_t ss, const float* Pi_k, const float* S_eff, AttnArgs a, int bits, void* workspace,
-                       cudaStream_t stream);
+                       cudaStream_t stream, const uint8_t* prepared = nullptr);
+// scratch bytes of a bf16-mode call, by the kernel that will serve it (0 when the SM-pair kernel runs from a
+// prepared constants buffer)
+size_t workspace_bytes_bf16_prepared(int64_t B, int64_t Hq, int64_t Sq, int64_t Hkv, int64_t Sk, int64_t kv_stride,
+                                     int d);
 
 size_t workspace_bytes_bf16(int64_t BHq, int64_t Sq, int d);
 

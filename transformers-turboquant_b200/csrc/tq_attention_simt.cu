@@ -650,11 +650,20 @@ static int attention_entry(const void* q, int dtype, int64_t B, int64_t Hq, int6
                                 const float* centroids_k, const float* Pi_v, const float* centroids_v, int bits,
                                 float sm_scale, int causal, const float* mask, int64_t mask_stride_b,
                                 int64_t mask_stride_q, void* out, int64_t o_stride_b, int64_t o_stride_h,
-                                int64_t o_stride_s, void* workspace, size_t workspace_bytes, int mode, void* stream) {
+                                int64_t o_stride_s, void* workspace, size_t workspace_bytes, int mode, void* stream,
+                                const uint8_t* prepared = nullptr) {
   if (int st = check_attention_common(q, dtype, B, Hq, Sq, d, q_stride_b, q_stride_h, q_stride_s, Hkv, Sk, bits,
                                       mode))
     return st;
   if (B * Hq * Sq == 0) return TQ_OK;
+  if (prepared != nullptr) {  // the matrices and codebooks are the fp32 copies inside the constants buffer
+    const ConstLayout L = const_layout(d);
+    Pi_k = reinterpret_cast<const float*>(prepared + L.pi_k);
+    S_eff = reinterpret_cast<const float*>(prepared + L.s_eff);
+    centroids_k = reinterpret_cast<const float*>(prepared + L.cen_k);
+    Pi_v = reinterpret_cast<const float*>(prepared + L.pi_v);
+    centroids_v = reinterpret_cast<const float*>(prepared + L.cen_v);
+  }
   TQ_REQUIRE(Sk > 0, "attention over zero keys is undefined");
   TQ_REQUIRE(!causal || Sk >= Sq, "causal attention needs Sk >= Sq (got Sq=%lld, Sk=%lld)", (long long)Sq,
              (long long)Sk);
@@ -666,8 +675,10 @@ static int attention_entry(const void* q, int dtype, int64_t B, int64_t Hq, int6
   TQ_REQUIRE(o_stride_b % al == 0 && o_stride_h % al == 0 && o_stride_s % al == 0,
              "out strides must keep every row 16-byte aligned");
   TQ_REQUIRE(sm_scale == sm_scale, "sm_scale is NaN");
-  const size_t need = tq_attention_workspace_bytes(B, Hq, Sq, d, mode);
-  if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u))
+  const size_t need = prepared != nullptr
+                          ? tq_attention_prepared_workspace_bytes(B, Hq, Sq, Hkv, Sk, kv_stride, d, mode)
+                          : tq_attention_workspace_bytes(B, Hq, Sq, d, mode);
+  if (need > 0 && (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u)))
     return fail(TQ_ERR_WORKSPACE, "workspace of %zu bytes needed (256-byte aligned), got %zu", need,
                 workspace_bytes);
   CallScope scope(q, "q", static_cast<cudaStream_t>(stream));
@@ -682,7 +693,59 @@ static int attention_entry(const void* q, int dtype, int64_t B, int64_t Hq, int6
                               workspace, s);
   }
   return attention_fwd_bf16(q, dtype, B, Hq, Sq, d, q_stride_b, q_stride_h, q_stride_s, Pi_k, S_eff, a, bits,
-                            workspace, s);
+                            workspace, s, prepared);
+}
+
+extern "C" size_t tq_constants_bytes(int d, int bits) {
+  if (!valid_head_dim(d) || !valid_bits(bits)) return 0;
+  return const_layout(d).total;
+}
+
+extern "C" int tq_prepare_constants(const float* Pi_k, const float* S_eff, const float* centroids_k,
+                                    const float* boundaries_k, const float* Pi_v, const float* centroids_v,
+                                    const float* boundaries_v, int bits, int d, void* constants,
+                                    size_t constants_bytes, void* stream) {
+  TQ_REQUIRE(valid_head_dim(d), "head_dim %d unsupported (64 or 128)", d);
+  TQ_REQUIRE(valid_bits(bits), "bits %d unsupported (2, 3 or 4)", bits);
+  TQ_REQUIRE(Pi_k && S_eff && centroids_k && boundaries_k && Pi_v && centroids_v && boundaries_v,
+             "NULL constant pointer");
+  const size_t need = const_layout(d).total;
+  if (constants == nullptr || constants_bytes < need || (reinterpret_cast<uintptr_t>(constants) & 255u))
+    return fail(TQ_ERR_WORKSPACE, "constants buffer of %zu bytes needed (256-byte aligned), got %zu", need,
+                constants_bytes);
+  CallScope scope(constants, "constants", static_cast<cudaStream_t>(stream));
+  if (scope.status()) return scope.status();
+  return prepare_constants(Pi_k, S_eff, centroids_k, boundaries_k, Pi_v, centroids_v, boundaries_v, bits, d, constants,
+                           static_cast<cudaStream_t>(stream));
+}
+
+extern "C" size_t tq_attention_prepared_workspace_bytes(int64_t B, int64_t Hq, int64_t Sq, int64_t Hkv, int64_t Sk,
+                                                        int64_t kv_capacity, int d, int mode) {
+  if (B <= 0 || Hq <= 0 || Sq <= 0 || d <= 0 || Hkv <= 0) return 0;
+  if (mode == TQ_MODE_FP32) return ((size_t)B * Hq * Sq * 2 * d * 4 + 255) & ~(size_t)255;
+  return workspace_bytes_bf16_prepared(B, Hq, Sq, Hkv, Sk, kv_capacity, d);
+}
+
+extern "C" int tq_attention_fwd_prepared(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq, int d,
+                                         int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s, int64_t Hkv,
+                                         int64_t Sk, int64_t kv_capacity, const uint8_t* key_idx,
+                                         const uint8_t* key_signs, const uint16_t* key_vec_norms,
+                                         const uint16_t* key_residual_norms, const uint8_t* val_idx,
+                                         const uint16_t* val_vec_norms, const void* constants, int bits,
+                                         float sm_scale, int causal, const float* mask, int64_t mask_stride_b,
+                                         int64_t mask_stride_q, void* out, int64_t o_stride_b, int64_t o_stride_h,
+                                         int64_t o_stride_s, void* workspace, size_t workspace_bytes, int mode,
+                                         void* stream) {
+  TQ_REQUIRE(constants != nullptr && (reinterpret_cast<uintptr_t>(constants) & 255u) == 0,
+             "constants must be a 256-byte aligned buffer filled by tq_prepare_constants");
+  TQ_REQUIRE(kv_capacity >= Sk, "cache capacity %lld is smaller than the %lld keys in use", (long long)kv_capacity,
+             (long long)Sk);
+  const float* dummy = reinterpret_cast<const float*>(constants);  // replaced from the buffer inside
+  return attention_entry(q, dtype, B, Hq, Sq, d, q_stride_b, q_stride_h, q_stride_s, Hkv, Sk, kv_capacity, key_idx,
+                         key_signs, key_vec_norms, key_residual_norms, val_idx, val_vec_norms, dummy, dummy, dummy,
+                         dummy, dummy, bits, sm_scale, causal, mask, mask_stride_b, mask_stride_q, out, o_stride_b,
+                         o_stride_h, o_stride_s, workspace, workspace_bytes, mode, stream,
+                         static_cast<const uint8_t*>(constants));
 }
 
 extern "C" int tq_attention_fwd(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq, int d, int64_t q_stride_b,

@@ -105,6 +105,54 @@ __global__ void build_luts_kernel(const float* __restrict__ cen_k, const float* 
   }
 }
 
+// Canonical K-major operand image of a row-major fp32 [d, d] matrix, split into bf16 hi = bf16(m) and
+// lo = bf16(m - hi): what the compression kernel's MMAs take as B operands (x (hi + lo)^T carries ~16 mantissa bits).
+__global__ void build_split_image_kernel(const float* __restrict__ M, int d, __nv_bfloat16* __restrict__ hi,
+                                         __nv_bfloat16* __restrict__ lo) {
+  const int j = blockIdx.x, i = threadIdx.x;
+  const float v = M[j * d + i];
+  const __nv_bfloat16 h = __float2bfloat16_rn(v);
+  const int at = operand_index(j, i, d, d);
+  hi[at] = h;
+  lo[at] = __float2bfloat16_rn(v - __bfloat162float(h));
+}
+__global__ void copy_floats_kernel(const float* __restrict__ src, float* __restrict__ dst, int n) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) dst[i] = src[i];
+}
+__global__ void write_header_kernel(uint32_t* hdr, int d, int bits) {
+  hdr[0] = kConstMagic;
+  hdr[1] = (uint32_t)d;
+  hdr[2] = (uint32_t)bits;
+}
+
+int prepare_constants(const float* Pi_k, const float* S_eff, const float* cen_k, const float* bnd_k, const float* Pi_v,
+                      const float* cen_v, const float* bnd_v, int bits, int d, void* constants, cudaStream_t stream) {
+  const ConstLayout L = const_layout(d);
+  uint8_t* c = static_cast<uint8_t*>(constants);
+  auto f32 = [&](size_t off) { return reinterpret_cast<float*>(c + off); };
+  auto b16 = [&](size_t off) { return reinterpret_cast<__nv_bfloat16*>(c + off); };
+  const int kb = bits - 1, vb = bits;
+  const struct { const float* src; size_t off; int n; } copies[] = {
+      {Pi_k, L.pi_k, d * d}, {S_eff, L.s_eff, d * d}, {Pi_v, L.pi_v, d * d}, {cen_k, L.cen_k, 1 << kb},
+      {bnd_k, L.bnd_k, (1 << kb) - 1}, {cen_v, L.cen_v, 1 << vb}, {bnd_v, L.bnd_v, (1 << vb) - 1}};
+  for (const auto& cp : copies) {
+    copy_floats_kernel<<<cp.n >= 4096 ? 16 : 1, 256, 0, stream>>>(cp.src, f32(cp.off), cp.n);
+    TQ_CUDA_OK(cudaGetLastError());
+  }
+  const float coeff = sqrtf(1.5707963267948966f) / (float)d;
+  build_wcat_kernel<<<d, d, 0, stream>>>(Pi_k, S_eff, d, coeff, b16(L.w_cat_pair), d);
+  build_wcat_kernel<<<d, d, 0, stream>>>(Pi_k, S_eff, d, coeff, b16(L.w_cat_plain), 0);
+  build_wunrot_kernel<<<d, d, 0, stream>>>(Pi_v, d, b16(L.w_unrot_pair), d / 2);
+  build_wunrot_kernel<<<d, d, 0, stream>>>(Pi_v, d, b16(L.w_unrot_plain), 0);
+  build_luts_kernel<<<1, 128, 0, stream>>>(cen_k, cen_v, kb, vb, reinterpret_cast<uint32_t*>(c + L.luts));
+  build_split_image_kernel<<<d, d, 0, stream>>>(Pi_k, d, b16(L.pik_hi), b16(L.pik_lo));
+  build_split_image_kernel<<<d, d, 0, stream>>>(S_eff, d, b16(L.se_hi), b16(L.se_lo));
+  build_split_image_kernel<<<d, d, 0, stream>>>(Pi_v, d, b16(L.piv_hi), b16(L.piv_lo));
+  write_header_kernel<<<1, 1, 0, stream>>>(reinterpret_cast<uint32_t*>(c + L.header), d, bits);
+  TQ_CUDA_OK(cudaGetLastError());
+  return TQ_OK;
+}
+
 // ---- row GEMM ----------------------------------------------------------------------------
 
 struct RowsGemmArgs {
@@ -815,8 +863,10 @@ int prepare_queries_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_
   const int64_t n_q = B * Hq * Sq;
   ProfScope prof(kProfPrepareQueries, stream);
   __nv_bfloat16* w_cat = static_cast<__nv_bfloat16*>(w_cat_scratch);
-  build_wcat_kernel<<<d, d, 0, stream>>>(Pi_k, S_eff, d, sqrtf(1.5707963267948966f) / (float)d, w_cat, 0);
-  TQ_CUDA_OK(cudaGetLastError());
+  if (Pi_k != nullptr) {  // NULL: `w_cat_scratch` already holds the row-major operand (a prepared constants buffer)
+    build_wcat_kernel<<<d, d, 0, stream>>>(Pi_k, S_eff, d, sqrtf(1.5707963267948966f) / (float)d, w_cat, 0);
+    TQ_CUDA_OK(cudaGetLastError());
+  }
   const int tiles = (int)((n_q + 127) / 128);
   RowsGemmArgs prep{q, dtype, n_q, Hq, Sq, sb, sh, ss, w_cat, q_cat, q_cat_dtype,
                     Hq * Sq * 2 * d, Sq * 2 * d, (int64_t)2 * d, tiles};
@@ -834,45 +884,82 @@ static bool use_sm_pairs() {
   return cached == 1;
 }
 
+// Which kernel serves a bf16-mode call.
+enum class Bf16Path { kDecode, kPairs, kSingle };
+static Bf16Path bf16_path(const AttnArgs& a, int64_t Sq, int d) {
+  if (decode_applies(a, d) && Sq <= 16) return Bf16Path::kDecode;
+  return (d == 128 && use_sm_pairs()) ? Bf16Path::kPairs : Bf16Path::kSingle;
+}
+
+size_t workspace_bytes_bf16_prepared(int64_t B, int64_t Hq, int64_t Sq, int64_t Hkv, int64_t Sk, int64_t kv_stride,
+                                     int d) {
+  AttnArgs a{};
+  a.Hq = Hq; a.Sq = Sq; a.Hkv = Hkv; a.Sk = Sk; a.kv_stride = kv_stride;
+  const int64_t n_q = B * Hq * Sq;
+  switch (bf16_path(a, Sq, d)) {
+    case Bf16Path::kPairs: return 0;  // everything it needs is in the constants buffer and on the chip
+    case Bf16Path::kDecode: return round256((size_t)n_q * 2 * d * 2) + decode_workspace_bytes(B * Hq);
+    default: return round256((size_t)n_q * 2 * d * 2) + round256((size_t)n_q * d * 2);
+  }
+}
+
 int attention_fwd_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq, int d, int64_t sb, int64_t sh,
                        int64_t ss, const float* Pi_k, const float* S_eff, AttnArgs a, int bits, void* workspace,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, const uint8_t* prepared) {
   const int64_t n_q = B * Hq * Sq;
   TQ_REQUIRE(B <= 65535 && Hq <= 65535, "batch and head counts are limited to 65535 in bf16 mode");
   TQ_REQUIRE(a.sm_scale > 0.f && a.sm_scale < 1e30f, "sm_scale must be positive and finite in bf16 mode");
+  const Bf16Path path = bf16_path(a, Sq, d);
+  TQ_REQUIRE(path == Bf16Path::kDecode || a.kv_stride == a.Sk,
+             "a cache with capacity %lld > Sk is served by the split-KV kernel only: head_dim 128, "
+             "(Hq / Hkv) * Sq <= 16", (long long)a.kv_stride);
+  const bool pairs = path == Bf16Path::kPairs;
   uint8_t* ws = static_cast<uint8_t*>(workspace);
-  __nv_bfloat16* w_cat = reinterpret_cast<__nv_bfloat16*>(ws);
-  ws += round256((size_t)2 * d * d * 2);
-  __nv_bfloat16* w_unrot = reinterpret_cast<__nv_bfloat16*>(ws);
-  ws += round256((size_t)d * d * 2);
-  uint32_t* luts = reinterpret_cast<uint32_t*>(ws);
-  ws += kLutBytes;
+  const __nv_bfloat16 *w_cat, *w_unrot;
+  const uint32_t* luts;
+  if (prepared != nullptr) {
+    // operand images built once per compressor pair; the scratch holds per-call data only
+    const ConstLayout L = const_layout(d);
+    w_cat = reinterpret_cast<const __nv_bfloat16*>(prepared + (pairs ? L.w_cat_pair : L.w_cat_plain));
+    w_unrot = reinterpret_cast<const __nv_bfloat16*>(prepared + (pairs ? L.w_unrot_pair : L.w_unrot_plain));
+    luts = reinterpret_cast<const uint32_t*>(prepared + L.luts);
+  } else {
+    w_cat = reinterpret_cast<__nv_bfloat16*>(ws);
+    ws += round256((size_t)2 * d * d * 2);
+    w_unrot = reinterpret_cast<__nv_bfloat16*>(ws);
+    ws += round256((size_t)d * d * 2);
+    luts = reinterpret_cast<uint32_t*>(ws);
+    ws += kLutBytes;
+  }
   __nv_bfloat16* q_cat = reinterpret_cast<__nv_bfloat16*>(ws);
   ws += round256((size_t)n_q * 2 * d * 2);
   __nv_bfloat16* o_rot = reinterpret_cast<__nv_bfloat16*>(ws);
 
-  const bool decode = decode_applies(a, d) && Sq <= 16;
-  TQ_REQUIRE(decode || a.kv_stride == a.Sk,
-             "a cache with capacity %lld > Sk is served by the split-KV kernel only: head_dim 128, "
-             "(Hq / Hkv) * Sq <= 16", (long long)a.kv_stride);
-  const bool pairs = d == 128 && use_sm_pairs() && !decode;
-  if (decode)  // its own small kernels on both sides of the split-KV kernel; none of the bf16 operand images
+  if (path == Bf16Path::kDecode)  // its own small kernels on both sides of the split-KV kernel; none of the operand images
     return attention_decode(a, B, bits, q, dtype, sb, sh, ss, Pi_k, S_eff, q_cat,
-                            reinterpret_cast<uint8_t*>(o_rot) + round256((size_t)n_q * d * 2), stream);
-  build_wunrot_kernel<<<d, d, 0, stream>>>(a.Pi_v, d, w_unrot, pairs ? d / 2 : 0);
-  TQ_CUDA_OK(cudaGetLastError());
+                            prepared != nullptr ? reinterpret_cast<uint8_t*>(o_rot)
+                                                : reinterpret_cast<uint8_t*>(o_rot) + round256((size_t)n_q * d * 2),
+                            stream);
+  if (prepared == nullptr) {
+    build_wunrot_kernel<<<d, d, 0, stream>>>(a.Pi_v, d, const_cast<__nv_bfloat16*>(w_unrot), pairs ? d / 2 : 0);
+    TQ_CUDA_OK(cudaGetLastError());
+  }
   if (pairs) {
     // the SM-pair kernel prepares its query tiles and back-rotates its outputs itself; each CTA of a pair
     // bulk-copies its half of either constant operand (d rows of w_cat, d/2 rows of w_unrot)
-    build_wcat_kernel<<<d, d, 0, stream>>>(Pi_k, S_eff, d, sqrtf(1.5707963267948966f) / (float)d, w_cat, d);
-    TQ_CUDA_OK(cudaGetLastError());
-    build_luts_kernel<<<1, 128, 0, stream>>>(a.cen_k, a.cen_v, bits - 1, bits, luts);
-    TQ_CUDA_OK(cudaGetLastError());
+    if (prepared == nullptr) {
+      build_wcat_kernel<<<d, d, 0, stream>>>(Pi_k, S_eff, d, sqrtf(1.5707963267948966f) / (float)d,
+                                             const_cast<__nv_bfloat16*>(w_cat), d);
+      TQ_CUDA_OK(cudaGetLastError());
+      build_luts_kernel<<<1, 128, 0, stream>>>(a.cen_k, a.cen_v, bits - 1, bits, const_cast<uint32_t*>(luts));
+      TQ_CUDA_OK(cudaGetLastError());
+    }
     const PairArgs x{q, dtype, sb, sh, ss, w_cat, w_unrot, luts};
     return attention_c2(a, x, B, d, bits, stream);
   }
   // the attention kernel's score contraction runs on fp16 operands: its prepared queries are fp16
-  if (int st = prepare_queries_bf16(q, dtype, B, Hq, Sq, d, sb, sh, ss, Pi_k, S_eff, w_cat, q_cat, stream, TQ_F16))
+  if (int st = prepare_queries_bf16(q, dtype, B, Hq, Sq, d, sb, sh, ss, prepared != nullptr ? nullptr : Pi_k, S_eff,
+                                    const_cast<__nv_bfloat16*>(w_cat), q_cat, stream, TQ_F16))
     return st;
   const int tiles = (int)((n_q + 127) / 128);
 

@@ -61,6 +61,7 @@ constexpr int kMaxDevices = 64;
 int set_fault_mailbox_c2(unsigned long long* slot);
 int set_fault_mailbox_tc(unsigned long long* slot);
 int set_fault_mailbox_compress(unsigned long long* slot);
+int set_fault_mailbox_compress_kv(unsigned long long* slot);
 int set_fault_mailbox_selftest(unsigned long long* slot);
 
 // Device side of the mailbox: `slot` is the translation unit's copy of the pointer (NULL until installed).
@@ -75,6 +76,7 @@ __device__ __forceinline__ void notify_host_of_fault(unsigned long long* slot) {
 // translation unit) to the host.
 int read_wait_faults(unsigned long long* out);
 int read_compress_faults(unsigned long long* out);
+int read_compress_kv_faults(unsigned long long* out);
 int trace_enable(int on);
 int trace_read(long long* host_buf, int max_records, int* n_out);
 

@@ -17,6 +17,7 @@
 #include "tq_common.cuh"
 #include "tq_simt.cuh"
 #include "tq_compress.cuh"
+#include "tq_attention.cuh"
 
 namespace tq {
 
@@ -235,6 +236,51 @@ static int compress_values_entry(const void* values, int dtype, int64_t B, int64
   CompressArgs a{values, n, H, S, stride_b, stride_h, stride_s, Pi, nullptr, nullptr, boundaries,
                  packed_idx, nullptr, vec_norms, nullptr, (int)((n + kTileRows - 1) / kTileRows), out_stride, out_offset};
   return dispatch_compress<false>(dtype, d, bits, a, mode, static_cast<cudaStream_t>(stream));
+}
+
+int tq_compress_kv(const void* keys, const void* values, int dtype, int64_t B, int64_t H, int64_t S, int d,
+                   int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s, int64_t v_stride_b,
+                   int64_t v_stride_h, int64_t v_stride_s, const void* constants, int bits, uint8_t* key_idx,
+                   uint8_t* key_signs, uint16_t* key_vec_norms, uint16_t* key_residual_norms, uint8_t* val_idx,
+                   uint16_t* val_vec_norms, int64_t kv_capacity, int64_t kv_offset, int mode, void* stream) {
+  TQ_REQUIRE(constants != nullptr && (reinterpret_cast<uintptr_t>(constants) & 255u) == 0,
+             "constants must be a 256-byte aligned buffer filled by tq_prepare_constants");
+  TQ_REQUIRE(kv_offset >= 0 && S >= 0 && kv_offset + S <= kv_capacity,
+             "%lld new tokens behind %lld do not fit a cache of %lld", (long long)S, (long long)kv_offset,
+             (long long)kv_capacity);
+  TQ_REQUIRE(mode == TQ_MODE_FP32 || mode == TQ_MODE_BF16, "unknown mode %d", mode);
+  if (keys != nullptr)
+    if (int st = check_states(keys, dtype, B, H, S, d, k_stride_b, k_stride_h, k_stride_s, bits)) return st;
+  if (values != nullptr)
+    if (int st = check_states(values, dtype, B, H, S, d, v_stride_b, v_stride_h, v_stride_s, bits)) return st;
+  if (keys == nullptr && values == nullptr) {
+    TQ_REQUIRE(B * H * S == 0, "NULL input pointers");
+    return check_states(nullptr, dtype, B, H, S, d, 0, 0, d, bits);
+  }
+  if (B * H * S == 0) return TQ_OK;
+  TQ_REQUIRE(keys == nullptr || (key_idx && key_signs && key_vec_norms && key_residual_norms), "NULL key output pointer");
+  TQ_REQUIRE(values == nullptr || (val_idx && val_vec_norms), "NULL value output pointer");
+  const uint8_t* c = static_cast<const uint8_t*>(constants);
+  if (compress_kv_applies(dtype, d, mode)) {
+    CallScope scope(keys != nullptr ? keys : values, "keys/values", static_cast<cudaStream_t>(stream));
+    if (scope.status()) return scope.status();
+    const int64_t ks[3] = {k_stride_b, k_stride_h, k_stride_s}, vs[3] = {v_stride_b, v_stride_h, v_stride_s};
+    const int st = compress_kv(keys, values, B, H, S, ks, vs, c, bits, key_idx, key_signs, key_vec_norms,
+                               key_residual_norms, val_idx, val_vec_norms, kv_capacity, kv_offset,
+                               static_cast<cudaStream_t>(stream));
+    if (st != TQ_ERR_UNSUPPORTED) return st;  // strides no tensor map describes: the per-side kernels read them
+  }
+  const ConstLayout L = const_layout(d);
+  auto f32 = [&](size_t off) { return reinterpret_cast<const float*>(c + off); };
+  if (keys != nullptr)
+    if (int st = compress_keys_entry(keys, dtype, B, H, S, d, k_stride_b, k_stride_h, k_stride_s, f32(L.pi_k),
+                                     f32(L.s_eff), f32(L.cen_k), f32(L.bnd_k), bits, key_idx, key_signs,
+                                     key_vec_norms, key_residual_norms, kv_capacity, kv_offset, mode, stream))
+      return st;
+  if (values != nullptr)
+    return compress_values_entry(values, dtype, B, H, S, d, v_stride_b, v_stride_h, v_stride_s, f32(L.pi_v),
+                                 f32(L.bnd_v), bits, val_idx, val_vec_norms, kv_capacity, kv_offset, mode, stream);
+  return TQ_OK;
 }
 
 int tq_compress_keys(const void* keys, int dtype, int64_t B, int64_t H, int64_t S, int d,

@@ -73,7 +73,7 @@ void install_status_page(int dev, cudaStream_t stream) {
   }
   unsigned long long* base = static_cast<unsigned long long*>(dptr);
   unsigned long long* self = base + kMaxDevices + dev;
-  if (set_fault_mailbox_c2(base + dev) || set_fault_mailbox_tc(base + dev) || set_fault_mailbox_compress(base + dev) ||
+  if (set_fault_mailbox_c2(base + dev) || set_fault_mailbox_tc(base + dev) || set_fault_mailbox_compress(base + dev) || set_fault_mailbox_compress_kv(base + dev) ||
       cudaMemcpyToSymbol(g_mailbox_selftest, &self, sizeof(self)) != cudaSuccess) {
     cudaGetLastError();
     return;
@@ -302,8 +302,10 @@ int tq_device_fault_count(void* stream, int64_t* count_host) {
   unsigned long long w = 0;
   if (int st = read_wait_faults(&v)) return st;
   if (int st = read_compress_faults(&w)) return st;
-  unsigned long long x = 0;
+  unsigned long long x = 0, y = 0;
   if (int st = read_c2_faults(&x)) return st;
+  if (int st = read_compress_kv_faults(&y)) return st;
+  x += y;
   *count_host = static_cast<int64_t>(v + w + x);
   int dev = -1;
   if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices && v + w + x != 0) g_sticky_fault[dev] = true;

@@ -48,6 +48,13 @@ SIGNATURES = {
     "tq_unpack_bits": (_i, [_p, _l, _i, _i, _p, _p]),
     "tq_quantize_rotated": (_i, [_p, _l, _i, _p, _i, _p, _p]),
     "tq_dequantize": (_i, [_p, _l, _i, _p, _i, _p, _p]),
+    "tq_constants_bytes": (_z, [_i, _i]),
+    "tq_prepare_constants": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _p, _z, _p]),
+    "tq_compress_kv": (_i, [_p, _p, _i, _l, _l, _l, _i, _l, _l, _l, _l, _l, _l, _p, _i, _p, _p, _p, _p, _p, _p,
+                            _l, _l, _i, _p]),
+    "tq_attention_prepared_workspace_bytes": (_z, [_l, _l, _l, _l, _l, _l, _i, _i]),
+    "tq_attention_fwd_prepared": (_i, [_p, _i, _l, _l, _l, _i, _l, _l, _l, _l, _l, _l, _p, _p, _p, _p, _p, _p,
+                                       _p, _i, _f, _i, _p, _l, _l, _p, _l, _l, _l, _p, _z, _i, _p]),
     "tq_compress_keys": (_i, [_p, _i, _l, _l, _l, _i, _l, _l, _l, _p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _p]),
     "tq_compress_values": (_i, [_p, _i, _l, _l, _l, _i, _l, _l, _l, _p, _p, _i, _p, _p, _i, _p]),
     "tq_append_keys": (_i, [_p, _i, _l, _l, _l, _i, _l, _l, _l, _p, _p, _p, _p, _i, _p, _p, _p, _p, _l, _l, _i, _p]),

@@ -70,6 +70,13 @@ class _Constants:
 
     _tensor_attrs: tuple[str, ...] = ()
 
+    def __setattr__(self, name, value):
+        # Replacing a constant (tests overwrite them with the oracle's) invalidates the operand images prepared
+        # from it.  In-place edits of a constant tensor are not seen: assign a new tensor instead.
+        if name in self._tensor_attrs:
+            self.__dict__["_version"] = self.__dict__.get("_version", 0) + 1
+        object.__setattr__(self, name, value)
+
     def to(self, device):
         device = torch.device(device)
         for name in self._tensor_attrs:
@@ -80,6 +87,114 @@ class _Constants:
     def _check_device(self, t: torch.Tensor) -> None:
         if self.Pi.device != t.device:
             self.to(t.device)
+
+
+_PAD = {}
+
+
+def _zeros16(dev) -> torch.Tensor:
+    """Stand-in for the codebook of a side that a one-sided constants buffer does not have."""
+    key = str(dev)
+    if key not in _PAD:
+        _PAD[key] = torch.zeros(16, dtype=torch.float32, device=dev)
+    return _PAD[key]
+
+
+def _prepare(kc, vc, bits: int, d: int, dev) -> torch.Tensor:
+    """One constants buffer (tq_prepare_constants) for a key compressor, a value compressor or both; the missing
+    side is filled with stand-ins that no call reads."""
+    pad = _zeros16(dev)
+    any_pi = (kc or vc).Pi
+    args = [kc.Pi if kc else any_pi, kc.S_eff if kc else any_pi, kc.centroids if kc else pad,
+            kc.boundaries if kc else pad, vc.Pi if vc else any_pi, vc.centroids if vc else pad,
+            vc.boundaries if vc else pad]
+    nbytes = _lib.lib.tq_constants_bytes(d, bits)
+    buf = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    _lib.check(_lib.lib.tq_prepare_constants(*[t.data_ptr() for t in args], bits, d, buf.data_ptr(), nbytes,
+                                             _stream_ptr(dev)))
+    return buf
+
+
+def prepared_constants(kc=None, vc=None) -> torch.Tensor:
+    """The device buffer of operand images and fp32 constants for this compressor pair (or one compressor),
+    built on first use and kept until one of the constants is replaced or moved."""
+    owner = kc if kc is not None else vc
+    key = (id(kc) if kc else 0, id(vc) if vc else 0)
+    ver = (kc._version if kc else 0, vc._version if vc else 0)
+    cache = owner.__dict__.setdefault("_prepared", {})
+    hit = cache.get(key)
+    if hit is None or hit[0] != ver:
+        if kc is not None and vc is not None and (kc.bits != vc.bits or kc.head_dim != vc.head_dim):
+            raise ValueError("key and value compressors must share bit width and head_dim")
+        cache[key] = hit = (ver, _prepare(kc, vc, owner.bits, owner.head_dim, owner.Pi.device))
+    return hit[1]
+
+
+_WORKSPACES: dict = {}
+
+
+def _workspace(dev, nbytes: int) -> torch.Tensor:
+    """Scratch for one call.  One buffer per (device, stream) is kept and grown: calls on a stream run in order,
+    so they can share it; during stream capture a fresh tensor is taken from the graph's pool instead."""
+    nbytes = max(int(nbytes), 256)
+    if torch.cuda.is_current_stream_capturing():
+        return torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), _stream_ptr(dev))
+    ws = _WORKSPACES.get(key)
+    if ws is None or ws.numel() < nbytes:
+        _WORKSPACES[key] = ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    return ws
+
+
+def _packed_buffers(kc, vc, B: int, H: int, S: int, D: int, dev):
+    ck = cv = None
+    n = B * H * S
+    if kc is not None:
+        ck = {"packed_key_indices": torch.empty((n, D * kc.mse_bits // 8), dtype=torch.uint8, device=dev),
+              "packed_qjl_signs": torch.empty((n, D // 8), dtype=torch.uint8, device=dev),
+              "residual_norm": torch.empty((B, H, S), dtype=torch.float16, device=dev),
+              "vec_norms": torch.empty((B, H, S), dtype=torch.float16, device=dev), "shape": (B, H, S, D)}
+    if vc is not None:
+        cv = {"packed_indices": torch.empty((n, D * vc.bits // 8), dtype=torch.uint8, device=dev),
+              "vec_norms": torch.empty((n,), dtype=torch.float16, device=dev), "shape": (B, H, S, D)}
+    return ck, cv
+
+
+@torch.no_grad()
+def compress_kv(keys, values, key_compressor=None, val_compressor=None):
+    """Compress keys and values [B, H, S, D] in ONE launch (either may be None): what the family adapters do with
+    `key_compressor.compress(k)` and `val_compressor.compress(v)` back to back (families/llama.py:103-104 of
+    the reference).  Returns (compressed_keys, compressed_values) in the packed layout of `compress`."""
+    kc, vc = (key_compressor if keys is not None else None), (val_compressor if values is not None else None)
+    ref = keys if keys is not None else values
+    if ref is None or (kc is None and vc is None):
+        raise ValueError("nothing to compress")
+    _require_cuda(ref, "states")
+    for comp in (kc, vc):
+        if comp is not None:
+            comp._check_device(ref)
+    B, H, S, D = ref.shape
+    owner = kc or vc
+    if D != owner.head_dim or (keys is not None and values is not None and values.shape != keys.shape):
+        raise ValueError(f"expected [B, H, S, {owner.head_dim}] keys and values of one shape")
+    k = _rows_view(keys) if kc is not None else None
+    v = _rows_view(values) if vc is not None else None
+    if k is not None and v is not None and k.dtype != v.dtype:
+        v = v.to(k.dtype)
+    x = k if k is not None else v
+    dev = x.device
+    ck, cv = _packed_buffers(kc, vc, B, H, S, D, dev)
+    consts = prepared_constants(kc, vc)
+    ks = k.stride() if k is not None else (0, 0, D, 1)
+    vs = v.stride() if v is not None else (0, 0, D, 1)
+    _lib.check(_lib.lib.tq_compress_kv(
+        k.data_ptr() if k is not None else None, v.data_ptr() if v is not None else None, _DTYPES[x.dtype],
+        B, H, S, D, ks[0], ks[1], ks[2], vs[0], vs[1], vs[2], consts.data_ptr(), owner.bits,
+        ck["packed_key_indices"].data_ptr() if ck else None, ck["packed_qjl_signs"].data_ptr() if ck else None,
+        ck["vec_norms"].data_ptr() if ck else None, ck["residual_norm"].data_ptr() if ck else None,
+        cv["packed_indices"].data_ptr() if cv else None, cv["vec_norms"].data_ptr() if cv else None,
+        S, 0, resolve_mode(x.dtype, owner.mode), _stream_ptr(dev)))
+    return ck, cv
 
 
 class TurboQuantCompressorV2(_Constants):
@@ -109,25 +224,9 @@ class TurboQuantCompressorV2(_Constants):
     @torch.no_grad()
     def compress(self, states: torch.Tensor) -> dict:
         """[B, H, S, D] -> packed dict (one fused kernel)."""
-        _require_cuda(states, "states")
-        self._check_device(states)
-        B, H, S, D = states.shape
-        if D != self.head_dim:
-            raise ValueError(f"last dimension {D} != head_dim {self.head_dim}")
-        x = _rows_view(states)
-        n = B * H * S
-        dev = x.device
-        idx = torch.empty((n, D * self.mse_bits // 8), dtype=torch.uint8, device=dev)
-        sgn = torch.empty((n, D // 8), dtype=torch.uint8, device=dev)
-        vn = torch.empty((B, H, S), dtype=torch.float16, device=dev)
-        rn = torch.empty((B, H, S), dtype=torch.float16, device=dev)
-        _lib.check(_lib.lib.tq_compress_keys(
-            x.data_ptr(), _DTYPES[x.dtype], B, H, S, D, x.stride(0), x.stride(1), x.stride(2),
-            self.Pi.data_ptr(), self.S_eff.data_ptr(), self.centroids.data_ptr(), self.boundaries.data_ptr(),
-            self.bits, idx.data_ptr(), sgn.data_ptr(), vn.data_ptr(), rn.data_ptr(),
-            resolve_mode(x.dtype, self.mode), _stream_ptr(dev)))
-        return {"packed_key_indices": idx, "packed_qjl_signs": sgn, "residual_norm": rn, "vec_norms": vn,
-                "shape": (B, H, S, D)}
+        if states.dim() != 4 or states.shape[-1] != self.head_dim:
+            raise ValueError(f"expected [B, H, S, {self.head_dim}] states, got {tuple(states.shape)}")
+        return compress_kv(states, None, key_compressor=self)[0]
 
     @torch.no_grad()
     def asymmetric_attention_scores(self, queries: torch.Tensor, compressed: dict) -> torch.Tensor:
@@ -176,21 +275,9 @@ class TurboQuantCompressorMSE(_Constants):
 
     @torch.no_grad()
     def compress(self, states: torch.Tensor) -> dict:
-        _require_cuda(states, "states")
-        self._check_device(states)
-        B, H, S, D = states.shape
-        if D != self.head_dim:
-            raise ValueError(f"last dimension {D} != head_dim {self.head_dim}")
-        x = _rows_view(states)
-        n = B * H * S
-        dev = x.device
-        idx = torch.empty((n, D * self.bits // 8), dtype=torch.uint8, device=dev)
-        vn = torch.empty((n,), dtype=torch.float16, device=dev)
-        _lib.check(_lib.lib.tq_compress_values(
-            x.data_ptr(), _DTYPES[x.dtype], B, H, S, D, x.stride(0), x.stride(1), x.stride(2),
-            self.Pi.data_ptr(), self.boundaries.data_ptr(), self.bits, idx.data_ptr(), vn.data_ptr(),
-            resolve_mode(x.dtype, self.mode), _stream_ptr(dev)))
-        return {"packed_indices": idx, "vec_norms": vn, "shape": (B, H, S, D)}
+        if states.dim() != 4 or states.shape[-1] != self.head_dim:
+            raise ValueError(f"expected [B, H, S, {self.head_dim}] states, got {tuple(states.shape)}")
+        return compress_kv(None, states, val_compressor=self)[1]
 
     @torch.no_grad()
     def decompress(self, compressed: dict) -> torch.Tensor:
@@ -262,18 +349,16 @@ def fused_attention(q: torch.Tensor, compressed_k: dict, compressed_v: dict,
     dev = qv.device
     m = resolve_mode(qv.dtype, mode or key_compressor.mode)
     out = torch.empty((B, Hq, Sq, D), dtype=qv.dtype, device=dev)
-    ws_bytes = _lib.lib.tq_attention_workspace_bytes(B, Hq, Sq, D, m)
-    ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
+    consts = prepared_constants(key_compressor, val_compressor)
+    ws = _workspace(dev, _lib.lib.tq_attention_prepared_workspace_bytes(B, Hq, Sq, Hkv, Sk, Sk, D, m))
     mk, mask_ptr, msb, msq = _mask_args(attention_mask, B, Sq, Sk, dev)  # mk keeps the converted mask alive
     scale = float(sm_scale) if sm_scale is not None else 1.0 / math.sqrt(D)
-    _lib.check(_lib.lib.tq_attention_fwd(
-        qv.data_ptr(), _DTYPES[qv.dtype], B, Hq, Sq, D, qv.stride(0), qv.stride(1), qv.stride(2), Hkv, Sk,
+    _lib.check(_lib.lib.tq_attention_fwd_prepared(
+        qv.data_ptr(), _DTYPES[qv.dtype], B, Hq, Sq, D, qv.stride(0), qv.stride(1), qv.stride(2), Hkv, Sk, Sk,
         compressed_k["packed_key_indices"].data_ptr(), compressed_k["packed_qjl_signs"].data_ptr(),
         compressed_k["vec_norms"].data_ptr(), compressed_k["residual_norm"].data_ptr(),
         compressed_v["packed_indices"].data_ptr(), compressed_v["vec_norms"].data_ptr(),
-        key_compressor.Pi.data_ptr(), key_compressor.S_eff.data_ptr(), key_compressor.centroids.data_ptr(),
-        val_compressor.Pi.data_ptr(), val_compressor.centroids.data_ptr(), key_compressor.bits,
-        scale, 1 if causal else 0, mask_ptr, msb, msq,
+        consts.data_ptr(), key_compressor.bits, scale, 1 if causal else 0, mask_ptr, msb, msq,
         out.data_ptr(), out.stride(0), out.stride(1), out.stride(2),
         ws.data_ptr(), ws.numel(), m, _stream_ptr(dev)))
     return out

@@ -14,7 +14,7 @@ from __future__ import annotations
 import torch
 import torch.nn as nn
 
-from ..compressors import fused_attention
+from ..compressors import compress_kv, fused_attention
 from ..plugin import TurboQuantAttentionBase
 
 
@@ -57,8 +57,7 @@ class RopeGQAAttention(TurboQuantAttentionBase):
         if self.kv_cache_capacity is not None and past_key_values is not None:
             out = self._attend_cached(q, k, v, past_key_values, attention_mask)
             return self.o_proj(out.transpose(1, 2).reshape(B, T, self.num_heads * self.head_dim)), None
-        ck = self.key_compressor.compress(k)
-        cv = self.val_compressor.compress(v)
+        ck, cv = compress_kv(k, v, self.key_compressor, self.val_compressor)
         out = fused_attention(q, ck, cv, self.key_compressor, self.val_compressor, causal=True,
                               attention_mask=attention_mask)
         out = out.transpose(1, 2).reshape(B, T, self.num_heads * self.head_dim)

@@ -5,7 +5,7 @@ from __future__ import annotations
 
 import torch.nn as nn
 
-from ..compressors import fused_attention
+from ..compressors import compress_kv, fused_attention
 from ..plugin import TurboQuantAttentionBase, register_family
 
 
@@ -39,8 +39,7 @@ class TurboQuantGPT2Attention(TurboQuantAttentionBase):
         B, T, _ = hidden_states.shape
         q, k, v = self.c_attn(hidden_states).split(self.embed_dim, dim=2)
         q, k, v = (t.view(B, T, self.num_heads, self.head_dim).transpose(1, 2) for t in (q, k, v))
-        ck = self.key_compressor.compress(k)
-        cv = self.val_compressor.compress(v)
+        ck, cv = compress_kv(k, v, self.key_compressor, self.val_compressor)
         # attention-probability dropout (attn_pdrop) has no counterpart in the fused kernel; it is
         # inactive in eval mode and warned about above in train mode
         out = fused_attention(q, ck, cv, self.key_compressor, self.val_compressor, causal=True,

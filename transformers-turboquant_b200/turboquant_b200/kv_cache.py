@@ -16,8 +16,9 @@ import math
 import torch
 
 from . import _lib
-from .compressors import (_DTYPES, _mask_args, _require_cuda, _rows_view, _stream_ptr, TurboQuantCompressorMSE,
-                          TurboQuantCompressorV2, fused_attention, resolve_mode)
+from .compressors import (_DTYPES, _mask_args, _require_cuda, _rows_view, _stream_ptr, _workspace,
+                          TurboQuantCompressorMSE, TurboQuantCompressorV2, fused_attention, prepared_constants,
+                          resolve_mode)
 
 
 class CompressedKVCache:
@@ -74,17 +75,15 @@ class CompressedKVCache:
         kc._check_device(keys)
         vc._check_device(keys)
         k, v = _rows_view(keys), _rows_view(values)
-        stream = _stream_ptr(k.device)
-        # the compression kernels write their rows straight behind the tokens in use: no scratch, no copies
-        _lib.check(_lib.lib.tq_append_keys(
-            k.data_ptr(), _DTYPES[k.dtype], B, H, S, D, k.stride(0), k.stride(1), k.stride(2),
-            kc.Pi.data_ptr(), kc.S_eff.data_ptr(), kc.centroids.data_ptr(), kc.boundaries.data_ptr(), kc.bits,
+        if v.dtype != k.dtype:
+            v = v.to(k.dtype)
+        # one launch compresses both sides straight behind the tokens in use: no scratch, no copies
+        _lib.check(_lib.lib.tq_compress_kv(
+            k.data_ptr(), v.data_ptr(), _DTYPES[k.dtype], B, H, S, D, k.stride(0), k.stride(1), k.stride(2),
+            v.stride(0), v.stride(1), v.stride(2), prepared_constants(kc, vc).data_ptr(), kc.bits,
             self.key_indices.data_ptr(), self.key_signs.data_ptr(), self.key_norms.data_ptr(),
-            self.key_residual_norms.data_ptr(), self.capacity, self.length, resolve_mode(k.dtype, kc.mode), stream))
-        _lib.check(_lib.lib.tq_append_values(
-            v.data_ptr(), _DTYPES[v.dtype], B, H, S, D, v.stride(0), v.stride(1), v.stride(2),
-            vc.Pi.data_ptr(), vc.boundaries.data_ptr(), vc.bits, self.value_indices.data_ptr(),
-            self.value_norms.data_ptr(), self.capacity, self.length, resolve_mode(v.dtype, vc.mode), stream))
+            self.key_residual_norms.data_ptr(), self.value_indices.data_ptr(), self.value_norms.data_ptr(),
+            self.capacity, self.length, resolve_mode(k.dtype, kc.mode), _stream_ptr(k.device)))
         self.length += S
 
     def _contiguous_prefix(self) -> tuple[dict, dict]:
@@ -124,17 +123,16 @@ class CompressedKVCache:
         qv = _rows_view(q)
         dev = qv.device
         out = torch.empty((B, Hq, Sq, D), dtype=qv.dtype, device=dev)
-        ws_bytes = _lib.lib.tq_attention_workspace_bytes(B, Hq, Sq, D, _lib.TQ_MODE_BF16)
-        ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
+        ws = _workspace(dev, _lib.lib.tq_attention_prepared_workspace_bytes(B, Hq, Sq, self.kv_heads, self.length,
+                                                                            self.capacity, D, _lib.TQ_MODE_BF16))
         scale = float(sm_scale) if sm_scale is not None else 1.0 / math.sqrt(D)
         mk, mask_ptr, msb, msq = _mask_args(attention_mask, B, Sq, self.length, dev)  # mk keeps the mask alive
-        _lib.check(_lib.lib.tq_attention_fwd_cached(
+        _lib.check(_lib.lib.tq_attention_fwd_prepared(
             qv.data_ptr(), _DTYPES[qv.dtype], B, Hq, Sq, D, qv.stride(0), qv.stride(1), qv.stride(2),
             self.kv_heads, self.length, self.capacity,
             self.key_indices.data_ptr(), self.key_signs.data_ptr(), self.key_norms.data_ptr(),
             self.key_residual_norms.data_ptr(), self.value_indices.data_ptr(), self.value_norms.data_ptr(),
-            kc.Pi.data_ptr(), kc.S_eff.data_ptr(), kc.centroids.data_ptr(), vc.Pi.data_ptr(), vc.centroids.data_ptr(),
-            kc.bits, scale, 1 if causal else 0, mask_ptr, msb, msq,
+            prepared_constants(kc, vc).data_ptr(), kc.bits, scale, 1 if causal else 0, mask_ptr, msb, msq,
             out.data_ptr(), out.stride(0), out.stride(1), out.stride(2),
-            ws.data_ptr(), ws.numel(), _stream_ptr(dev)))
+            ws.data_ptr(), ws.numel(), _lib.TQ_MODE_BF16, _stream_ptr(dev)))
         return out

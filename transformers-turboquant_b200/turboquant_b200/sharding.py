@@ -60,10 +60,10 @@ def sharded_attention(attend: Callable, q, k, v, rank: int, world: int):
 
 def local_attention(key_compressor, val_compressor, causal: bool = True) -> Callable:
     """compress K, compress V, fused attention: the per-rank work of the hot path."""
-    from .compressors import fused_attention
+    from .compressors import compress_kv, fused_attention
 
     def attend(q, k, v):
-        ck, cv = key_compressor.compress(k), val_compressor.compress(v)
+        ck, cv = compress_kv(k, v, key_compressor, val_compressor)
         return fused_attention(q, ck, cv, key_compressor, val_compressor, causal=causal)
 
     return attend
