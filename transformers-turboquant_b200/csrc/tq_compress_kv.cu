@@ -62,9 +62,9 @@ static_assert(kSmemBytes <= 227 * 1024, "shared memory over-subscribed");
 constexpr uint32_t kColYP = 0, kColRH = 3 * kD, kColRL = 3 * kD + kD / 2;
 
 struct KvArgs {
-  int64_t units_k, units_v;   // 128-vector tiles on either side
-  int64_t tiles_per_head;     // ceil(S / 128)
-  int64_t S, H;
+  uint32_t units_k, units_v;  // 128-vector tiles on either side (32-bit: unit arithmetic runs per thread and tile)
+  uint32_t tiles_per_head;    // ceil(S / 128)
+  uint32_t S, H;
   const uint8_t* consts;      // constants buffer of tq_prepare_constants
   uint8_t* key_idx;
   uint8_t* key_sgn;
@@ -172,8 +172,8 @@ compress_kv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   auto x_read = [&](int s) { return bar(22 + s); };
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-  const int64_t total = a.units_k + a.units_v;
-  const int64_t G = gridDim.x, c = blockIdx.x;
+  const uint32_t total = a.units_k + a.units_v;
+  const uint32_t G = gridDim.x, c = blockIdx.x;
   const int n = (int)((total - c + G - 1) / G);                                  // units of this CTA
   const int nk = c < a.units_k ? (int)((a.units_k - c + G - 1) / G) : 0;         // ... of which key tiles (first)
 
@@ -204,11 +204,12 @@ compress_kv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
 
   // global unit of this CTA's i-th unit -> side, (batch * head), first row
   auto unit_of = [&](int i, bool& is_key, int64_t& bh, int& s0) {
-    const int64_t g = c + (int64_t)i * G;
+    const uint32_t g = c + (uint32_t)i * G;
     is_key = g < a.units_k;
-    const int64_t t = is_key ? g : g - a.units_k;
-    bh = t / a.tiles_per_head;
-    s0 = (int)(t % a.tiles_per_head) * 128;
+    const uint32_t t = is_key ? g : g - a.units_k;
+    const uint32_t h = t / a.tiles_per_head;
+    bh = h;
+    s0 = (int)(t - h * a.tiles_per_head) * 128;
   };
 
   if (warp == kEpiWarps) {
@@ -224,8 +225,9 @@ compress_kv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         const CUtensorMap* map = is_key ? &map_k : &map_v;
         const uint32_t dst = tc::smem_u32(smem + kOffX + s * kTileBytes);
         tc::mbar_arrive_expect_tx(x_full(s), kTileBytes);
-        tma_load_tile(dst, map, 0, s0, (int)(bh % a.H), (int)(bh / a.H), x_full(s));
-        tma_load_tile(dst + kTileBytes / 2, map, 64, s0, (int)(bh % a.H), (int)(bh / a.H), x_full(s));
+        const uint32_t bi = (uint32_t)bh / a.H, hi = (uint32_t)bh - bi * a.H;
+        tma_load_tile(dst, map, 0, s0, (int)hi, (int)bi, x_full(s));
+        tma_load_tile(dst + kTileBytes / 2, map, 64, s0, (int)hi, (int)bi, x_full(s));
         issued = i + 1;
       };
       auto load_consts = [&](bool keys) {
@@ -356,7 +358,7 @@ compress_kv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         int64_t bh;
         int s0;
         unit_of(i, is_key, bh, s0);
-        const bool live = s0 + row < a.S;
+        const bool live = (uint32_t)(s0 + row) < a.S;
         const int64_t no = bh * a.out_stride + a.out_offset + s0 + row;
         // ---- norm of the row: this thread's 64 bytes of the tile as it landed (128-byte swizzle) ----
         if (!(ok = tc::mbar_wait_or_abort(x_full(s), u & 1, abort_flag))) break;
@@ -483,7 +485,7 @@ compress_kv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
           const uint32_t sb = raw[e] & 0x80000000u;
           neg = (e == 31 ? sb : __umulhi(sb, 2u << e)) + neg;
         }
-        if (s0 + row < a.S)
+        if ((uint32_t)(s0 + row) < a.S)
           *reinterpret_cast<uint32_t*>(a.key_sgn + (bh * a.out_stride + a.out_offset + s0 + row) * (kD / 8) + 4 * part) = ~neg;
       }
     }
@@ -554,9 +556,11 @@ int compress_kv(const void* k, const void* v, int64_t B, int64_t H, int64_t S, c
   if (int st = make_map(&map_v, v != nullptr ? v : any, B, H, S, (v ? v_strides : any_strides)[0],
                         (v ? v_strides : any_strides)[1], (v ? v_strides : any_strides)[2]))
     return st;
-  KvArgs a{k != nullptr ? units : 0, v != nullptr ? units : 0, tiles_per_head, S, H, consts, key_idx, key_sgn, key_vn,
-           key_rn, val_idx, val_vn, out_stride, out_offset, const_layout(kD)};
-  const int64_t total = a.units_k + a.units_v;
+  TQ_REQUIRE(2 * units < ((int64_t)1 << 31), "problem too large");
+  KvArgs a{(uint32_t)(k != nullptr ? units : 0), (uint32_t)(v != nullptr ? units : 0), (uint32_t)tiles_per_head,
+           (uint32_t)S, (uint32_t)H, consts, key_idx, key_sgn, key_vn, key_rn, val_idx, val_vn, out_stride, out_offset,
+           const_layout(kD)};
+  const int64_t total = (int64_t)a.units_k + a.units_v;
   int grid = sm_count();
   if (grid > total) grid = (int)total;
   auto kern = bits == 2 ? compress_kv_kernel<2> : bits == 3 ? compress_kv_kernel<3> : compress_kv_kernel<4>;

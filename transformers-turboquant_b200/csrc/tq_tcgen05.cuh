@@ -107,14 +107,17 @@ __device__ __forceinline__ bool mbar_wait_or_abort(uint32_t bar, uint32_t parity
                                                    long long limit = 400000000ll) {
   if (mbar_test(bar, parity)) return true;
   const long long t0 = clock64();
-  while (!mbar_try_wait(bar, parity, 2000u)) {
+  for (;;) {
+    // four suspended waits between two looks at the abort flag and the clock
+    if (mbar_try_wait(bar, parity, 8000u) || mbar_try_wait(bar, parity, 8000u) || mbar_try_wait(bar, parity, 8000u) ||
+        mbar_try_wait(bar, parity, 8000u))
+      return true;
     if (*abort_flag) return false;
     if (clock64() - t0 > limit) {
       *abort_flag = 1;
       return false;
     }
   }
-  return true;
 }
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
