@@ -149,3 +149,48 @@ def test_tensor_core_compress_ragged(S):
     assert _index_mismatch(ck["packed_key_indices"].cpu().numpy(), ok["packed_key_indices"], bits - 1, d) <= 1e-3
     assert _index_mismatch(cv["packed_indices"].cpu().numpy(), ov["packed_indices"], bits, d) <= 1e-3
     assert _bit_mismatch(ck["packed_qjl_signs"].cpu().numpy(), ok["packed_qjl_signs"]) <= 2e-3
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4])
+def test_fused_kv_launch_equals_one_sided_launches(bits):
+    """`compress_kv` (keys and values in one launch: every CTA walks key tiles, swaps its constant operands, then
+    walks value tiles) gives the bytes of the two one-sided calls, on more tiles than there are SMs, a ragged
+    last tile per head and strided [B, S, H, d] inputs; and the oracle's within the tensor-core bounds."""
+    from turboquant_b200 import compress_kv
+    d, B, H, S = 128, 2, 8, 4100               # 2 x 8 x 33 = 528 tiles per side
+    g = torch.Generator().manual_seed(bits)
+    k = torch.randn(B, S, H, d, generator=g)
+    k[..., 3] *= 8
+    v = torch.randn(B, S, H, d, generator=g)
+    k, v = k.to(torch.bfloat16).cuda().transpose(1, 2), v.to(torch.bfloat16).cuda().transpose(1, 2)
+    kc, vc = device_compressors(d, bits, mode="bf16")
+    ck, cv = compress_kv(k, v, kc, vc)
+    ck1, cv1 = kc.compress(k), vc.compress(v)
+    for name in ("packed_key_indices", "packed_qjl_signs", "vec_norms", "residual_norm"):
+        assert torch.equal(ck[name], ck1[name]), name
+    for name in ("packed_indices", "vec_norms"):
+        assert torch.equal(cv[name], cv1[name]), name
+    # one (batch, head) against the oracle
+    kp, vp = oracle_params(d, bits)
+    ok = orc.key_compress(k[1:2, 5:6].cpu(), kp)
+    ov = orc.value_compress(v[1:2, 5:6].cpu(), vp)
+    sel = slice((1 * H + 5) * S, (1 * H + 6) * S)
+    assert _index_mismatch(ck["packed_key_indices"][sel].cpu().numpy(), ok["packed_key_indices"], bits - 1, d) <= 1e-4
+    assert _index_mismatch(cv["packed_indices"][sel].cpu().numpy(), ov["packed_indices"], bits, d) <= 1e-4
+    assert _bit_mismatch(ck["packed_qjl_signs"][sel].cpu().numpy(), ok["packed_qjl_signs"]) <= 5e-4
+    assert _fp16_close(ck["vec_norms"][1, 5], ok["vec_norms"][0, 0]) and _fp16_close(cv["vec_norms"][sel], ov["vec_norms"])
+
+
+def test_prepared_constants_follow_replaced_tensors():
+    """The per-pair constants buffer is rebuilt when a compressor's constant is replaced (tests overwrite them
+    with the oracle's) and reused otherwise."""
+    from turboquant_b200 import TurboQuantCompressorMSE, TurboQuantCompressorV2, prepared_constants
+    kc = TurboQuantCompressorV2(128, 3, 42, device="cuda")
+    vc = TurboQuantCompressorMSE(128, 3, 10042, device="cuda")
+    a = prepared_constants(kc, vc)
+    assert prepared_constants(kc, vc) is a
+    x = torch.randn(1, 1, 64, 128, device="cuda").to(torch.bfloat16)
+    before = kc.compress(x)["packed_key_indices"].clone()
+    kc.Pi = kc.Pi.flip(0).contiguous()          # another rotation
+    assert prepared_constants(kc, vc) is not a
+    assert not torch.equal(kc.compress(x)["packed_key_indices"], before)
