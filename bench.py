@@ -15,6 +15,8 @@ The same line carries, as extra objects, the other halves of the metric (`--sect
   models.llama8b  prefill tokens/s of a LLaMA-3.1-8B-shaped random-init model, global batch 8 x 4096 split over
                   the ranks, 3-bit TurboQuant attention, logits all_gather inside the timed region, with the same
                   model on HF sdpa attention beside it
+  models.deepseek7b  the same for a DeepSeek-7B-shaped model (30 layers, 32 heads of 128, multi-head attention:
+                  one query head per KV head), global batch 16 x 4096
   scaling_config5 STRONG scaling of the fused path on K,V [64,8,32768,128] / Q [64,32,32768,128], the 512
                   (batch, KV head) units split over the ranks
 
@@ -49,7 +51,7 @@ import torch  # noqa: E402
 B, HQ, HKV, S, D = 4, 32, 8, 8192, 128
 METRIC = "fused_tq_attention_keys_per_s"
 UNIT = "keys/s"
-ALL_SECTIONS = ("e2e", "cpu", "gpuref", "sustained", "decode", "llama8b", "config5")
+ALL_SECTIONS = ("e2e", "cpu", "gpuref", "sustained", "decode", "llama8b", "deepseek7b", "config5")
 
 
 def parse():
@@ -726,8 +728,9 @@ def run_headline(args):
     extra = {}
     if "decode" in args.want:
         extra["decode"] = decode_section(ctx, bits)
-    if "llama8b" in args.want:
-        extra["models"] = {"llama8b": model_section(ctx, "llama8b", bits)}
+    for name in ("llama8b", "deepseek7b"):
+        if name in args.want:
+            extra.setdefault("models", {})[name] = model_section(ctx, name, bits)
     if "config5" in args.want:
         extra["scaling_config5"] = config5_section(ctx, bits)
 
