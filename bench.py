@@ -446,6 +446,17 @@ def decode_section(ctx: Ctx, bits: int, steps: int = 50, warm: int = 3):
     cache = tq.CompressedKVCache(kc, vc, batch, HKV, sk + 256, device=dev)
     cache.append(k, v)
     k_new, v_new = k[:, :, -1:].clone(), v[:, :, -1:].clone()
+
+    # beside it: the same decode step over the UNCOMPRESSED bf16 cache with torch's fused attention (what a stock HF
+    # model does per layer; 512 B per key against 102 packed bytes)
+    def sdpa_step():
+        return torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=False, enable_gqa=True)
+
+    try:
+        sdpa_ms, _ = timed_steps(ctx, sdpa_step, steps, warm)
+    except Exception as exc:  # a torch build without a grouped-query kernel for this shape
+        sdpa_ms = None
+        sdpa_note = repr(exc)[:200]
     del k, v
 
     def attend():
@@ -486,6 +497,8 @@ def decode_section(ctx: Ctx, bits: int, steps: int = 50, warm: int = 3):
             "kernel_ms": {"prepare_queries": ms_sum[2] / max(launches[2], 1), "decode": kern_ms,
                           "merge_and_back_rotation": ms_sum[4] / max(launches[4], 1)},
             "generation_step_ms": gen_ms,  # append one token per sequence to the cache, then attend
+            "uncompressed_bf16_cache_sdpa_ms_per_call": sdpa_ms,
+            "uncompressed_bf16_cache_bytes": keys * 2 * D * 2,
             "device_wait_faults": tq.device_fault_count(dev), "output_norm": float(out.float().norm())}
 
 
