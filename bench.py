@@ -643,7 +643,7 @@ def run_headline(args):
     if "e2e" in args.want:
         hq, hk, hv = (t_.cpu().pin_memory() for t_ in (q, k, v))
         houts = [torch.empty(out.shape, dtype=out.dtype).pin_memory() for _ in range(2)]
-        n_e2e = max(4, min(args.steps, 10))
+        n_e2e = max(4, min(args.steps, 40))  # the pipeline fills and drains once per pass: as many steps as the kernel arm
         s_in, s_run, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
         dbuf = [[torch.empty_like(t_) for t_ in (q, k, v)] for _ in range(2)]
         free_in = [torch.cuda.Event() for _ in range(2)]    # device inputs of slot i consumed
