@@ -12,6 +12,8 @@ Inputs (402 MB) exceed the 126 MB L2, so no flush between steps.  Rank 0 prints 
 
 The same line carries, as extra objects, the other halves of the metric (`--sections` selects them):
   decode          one new token per sequence against a 32768-key compressed cache (split-KV kernel, HBM roofline)
+  head_dim64      the same op-level step at head_dim 64 (GPT-2's head dimension): headline shape and a
+                  GPT-2-small-shaped call
   models.llama8b  prefill tokens/s of a LLaMA-3.1-8B-shaped random-init model, global batch 8 x 4096 split over
                   the ranks, 3-bit TurboQuant attention, logits all_gather inside the timed region, with the same
                   model on HF sdpa attention beside it
@@ -51,7 +53,7 @@ import torch  # noqa: E402
 B, HQ, HKV, S, D = 4, 32, 8, 8192, 128
 METRIC = "fused_tq_attention_keys_per_s"
 UNIT = "keys/s"
-ALL_SECTIONS = ("e2e", "cpu", "gpuref", "sustained", "decode", "llama8b", "deepseek7b", "config5")
+ALL_SECTIONS = ("e2e", "cpu", "gpuref", "sustained", "decode", "head_dim64", "llama8b", "deepseek7b", "config5")
 
 
 def parse():
@@ -426,6 +428,36 @@ def config5_section(ctx: Ctx, bits: int, steps: int = 2, warm: int = 1, seq: int
     return res
 
 
+def head_dim64_section(ctx: Ctx, bits: int, steps: int = 10, warm: int = 3):
+    """The op-level step (compress K and V, fused causal attention) on the headline shape with head_dim 64, the
+    head dimension of every GPT-2 size, plus a GPT-2-small-shaped call (12 heads, no grouping, 1024 positions):
+    the SM-pair kernel serves both head dimensions."""
+    import turboquant_b200 as tq
+    dev, d = ctx.dev, 64
+    peaks = measured_peaks()
+    kc = tq.TurboQuantCompressorV2(d, bits, 42, device=str(dev))
+    vc = tq.TurboQuantCompressorMSE(d, bits, 10042, device=str(dev))
+    out = {}
+    for name, (batch, hq, hkv, seq) in {"gqa4_s8192": (B, HQ, HKV, S), "gpt2small_s1024": (8, 12, 12, 1024)}.items():
+        g = torch.Generator(device=dev).manual_seed(0)
+        q = torch.randn(batch, hq, seq, d, generator=g, device=dev).to(torch.bfloat16)
+        k = torch.randn(batch, hkv, seq, d, generator=g, device=dev).to(torch.bfloat16)
+        v = torch.randn(batch, hkv, seq, d, generator=g, device=dev).to(torch.bfloat16)
+
+        def step():
+            ck, cv = tq.compress_kv(k, v, kc, vc)
+            return tq.fused_attention(q, ck, cv, kc, vc, causal=True, mode="bf16")
+
+        ms, _ = timed_steps(ctx, step, steps, warm)
+        flops = batch * hq * (seq * (seq + 1) / 2) * 6 * d
+        out[name] = {"ms_per_step": ms, "keys_per_s": batch * hkv * seq * ctx.world / (ms * 1e-3),
+                     "tflops": flops / (ms * 1e-3) / 1e12, "frac_of_burst_bf16": flops / (ms * 1e-3) / 1e12 / peaks["tflops_burst"],
+                     "shape": {"batch_per_gpu": batch, "q_heads": hq, "kv_heads": hkv, "seq": seq, "head_dim": d}}
+        del q, k, v
+    return {"dtype": "bf16", "bits": bits, "steps": steps, "warmup": warm, "kernel": "attention_c2_kernel<64, bits>",
+            "flops": "6 d per visible (query, key) pair", **out}
+
+
 def decode_section(ctx: Ctx, bits: int, steps: int = 50, warm: int = 3):
     """Decode step against a resident compressed KV cache: one query token per sequence (32 query / 8 KV heads,
     d = 128) attends to Sk = 32768 cached keys, batch 8 -- the per-GPU share of the scaling shape K,V
@@ -741,6 +773,8 @@ def run_headline(args):
     extra = {}
     if "decode" in args.want:
         extra["decode"] = decode_section(ctx, bits)
+    if "head_dim64" in args.want:
+        extra["head_dim64"] = head_dim64_section(ctx, bits)
     for name in ("llama8b", "deepseek7b"):
         if name in args.want:
             extra.setdefault("models", {})[name] = model_section(ctx, name, bits)

@@ -252,7 +252,7 @@ int tq_attention_fwd(const void* q, int dtype, int64_t B, int64_t Hq, int64_t Sq
 
 /* tq_attention_fwd / tq_attention_fwd_cached with the constants taken from a prepared buffer: no operand is
  * rebuilt per call, and the scratch need drops to tq_attention_prepared_workspace_bytes -- zero for prefill-sized
- * calls at head_dim 128 in TQ_MODE_BF16 (`workspace` may then be NULL).  kv_capacity = Sk is the contiguous
+ * calls in TQ_MODE_BF16 (`workspace` may then be NULL).  kv_capacity = Sk is the contiguous
  * layout; a larger capacity is the persistent-cache layout of tq_attention_fwd_cached (same shape limits).
  * Replaces the attention core of the family adapters (families/llama.py:100-114, gpt2.py:90-110). */
 size_t tq_attention_prepared_workspace_bytes(int64_t B, int64_t Hq, int64_t Sq, int64_t Hkv, int64_t Sk,

@@ -9,8 +9,11 @@ import torch
 
 from helpers import (device_compressors, oracle_attention_from_packed, oracle_key_dict_to_device, oracle_params,
                      oracle_value_dict_to_device, rel_err)
+from pathlib import Path
+
 from oracle import tq_oracle as orc
 
+ROOT = Path(__file__).resolve().parent.parent
 pytestmark = pytest.mark.gpu
 TOL = {"fp32": 1e-4, "bf16": 1e-2}
 
@@ -46,7 +49,7 @@ def test_scores_match_reference_fixture(d, bits, golden_comp):
 
 
 @pytest.mark.parametrize("mode", ["fp32", "bf16"])
-@pytest.mark.parametrize("d,bits", [(128, 3), (128, 2), (128, 4), (64, 3)])
+@pytest.mark.parametrize("d,bits", [(128, 3), (128, 2), (128, 4), (64, 3), (64, 2), (64, 4)])
 def test_fused_attention_causal_gqa(mode, d, bits):
     B, Hq, Hkv, S = 2, 4, 2, 200   # two query heads per KV head, ragged tile edge
     dtype = torch.float32 if mode == "fp32" else torch.bfloat16
@@ -194,14 +197,15 @@ def test_no_device_wait_faults():
     assert device_fault_count() == 0
 
 
+@pytest.mark.parametrize("d", [128, 64])
 @pytest.mark.parametrize("Hq,Hkv", [(8, 2), (3, 3)])
-def test_long_sequence_tensor_core_vs_fp32_kernel_and_oracle(Hq, Hkv):
+def test_long_sequence_tensor_core_vs_fp32_kernel_and_oracle(Hq, Hkv, d):
     """S = 4096 (64 key tiles, many ring and barrier-phase wrap-arounds, several CTAs per head; head
-    pairs for the even group, position-block pairs for MHA): the tensor-core kernel against the
-    independent fp32 CUDA-core kernel on the whole output, and against the oracle on the last 32
-    query rows of one head."""
+    pairs for the even group, position-block pairs for MHA), both head dimensions of the SM-pair kernel:
+    the tensor-core kernel against the independent fp32 CUDA-core kernel on the whole output, and against
+    the oracle on the last 32 query rows of one head."""
     from turboquant_b200 import fused_attention
-    d, bits, B, S = 128, 3, 2, 4096
+    bits, B, S = 3, 2, 4096
     g = torch.Generator(device="cuda").manual_seed(7)
     q = torch.randn(B, Hq, S, d, generator=g, device="cuda").to(torch.bfloat16)
     k = torch.randn(B, Hkv, S, d, generator=g, device="cuda").to(torch.bfloat16)
@@ -399,3 +403,32 @@ def test_tensors_on_a_device_that_is_not_current():
         outs.append((out.cpu(), dec.cpu()))
         assert device_fault_count(dev) == 0
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+
+
+def test_single_sm_kernel_selected_by_environment():
+    """TQ_B200_ATTN=ws (read once per process, hence the child process) routes tensor-core mode to the single-SM
+    kernel with its separate query-preparation and back-rotation launches; it must agree with the fp32 kernel
+    like the default SM-pair kernel does."""
+    import os
+    import subprocess
+    import sys
+    code = """
+import sys, torch
+sys.path[:0] = [%r, %r]
+from turboquant_b200 import fused_attention, TurboQuantCompressorV2, TurboQuantCompressorMSE
+for d in (64, 128):
+    g = torch.Generator(device="cuda").manual_seed(d)
+    q = torch.randn(2, 4, 300, d, generator=g, device="cuda").to(torch.bfloat16)
+    k = torch.randn(2, 2, 300, d, generator=g, device="cuda").to(torch.bfloat16)
+    v = torch.randn(2, 2, 300, d, generator=g, device="cuda").to(torch.bfloat16)
+    kc, vc = TurboQuantCompressorV2(d, 3, 42, device="cuda"), TurboQuantCompressorMSE(d, 3, 10042, device="cuda")
+    ck, cv = kc.compress(k), vc.compress(v)
+    a = fused_attention(q, ck, cv, kc, vc, causal=True, mode="bf16").float()
+    b = fused_attention(q, ck, cv, kc, vc, causal=True, mode="fp32").float()
+    err = float((a - b).norm() / b.norm())
+    assert err < 1e-2, (d, err)
+print("agree")
+""" % (str(ROOT), str(ROOT / "transformers-turboquant_b200"))
+    env = dict(os.environ, TQ_B200_ATTN="ws")
+    res = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0 and "agree" in res.stdout, res.stdout + res.stderr

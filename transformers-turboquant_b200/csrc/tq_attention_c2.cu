@@ -519,8 +519,8 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
     if (ok && n_tiles > 0) {
       // the two warps of the quadrant store 16 of its 32 rows each
       const int esz = a.out_dtype == TQ_F32 ? 4 : 2;
-      const int lcpr = a.out_dtype == TQ_F32 ? 5 : 4;  // log2 of the 16-byte chunks per row (D = 128)
-      static_assert(D == 128, "chunks per row are derived for head_dim 128");
+      static_assert(D == 128 || D == 64, "chunks per row are derived for head_dim 64 and 128");
+      const int lcpr = (a.out_dtype == TQ_F32 ? 5 : 4) - (D == 64 ? 1 : 0);  // log2 of the 16-byte chunks per row
       const int pitch = D * esz + 16, cpr = 1 << lcpr;
       const uint8_t* Ot = smem_raw + L::kOutOff;
       uint8_t* obase = static_cast<uint8_t*>(a.out) + (b * a.o_stride_b + head * a.o_stride_h) * esz;
@@ -542,8 +542,10 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
     __builtin_assume(p >= 0 && p < kProducers);      // lets the compiler drop the always-true unit guards below
     constexpr int GPK = G / 2;                       // 16-coordinate items per key row
     constexpr int GPV = G / 4;                       // ... per half value row
-    constexpr int UK = L::kIdxK / 8, US = L::kSgn / 8, UV = L::kIdxV / 8;  // 8-byte units staged per tile
     constexpr int VROW = (G / 2) * VB;               // packed bytes of half a value row
+    constexpr int VU = VROW % 8 == 0 ? 8 : 4;        // bytes per staged unit of the value rows (12-byte half rows: 4)
+    static_assert(VROW % VU == 0 && (G * KB) % 8 == 0, "staged units must not straddle rows");
+    constexpr int UK = L::kIdxK / 8, US = L::kSgn / 8, UV = L::kIdxV / VU;  // units staged per tile (keys, signs: 8 bytes)
     constexpr int NK = (UK + kProducers - 1) / kProducers, NV = (UV + kProducers - 1) / kProducers;
     constexpr int NIK = (kHalfN * GPK + kProducers - 1) / kProducers;
     constexpr int NIV = (kBN * GPV + kProducers - 1) / kProducers;
@@ -565,8 +567,8 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int un = i * kProducers + p;
-      const int key = (un * 8) / VROW;
-      v_off[i] = key * (G * VB) + (un * 8) % VROW;
+      const int key = (un * VU) / VROW;
+      v_off[i] = key * (G * VB) + (un * VU) % VROW;
       v_row[i] = un < UV ? key : (1 << 30);
     }
     const int s_row = p < US ? koff + (p * 8) / G : (1 << 30);
@@ -578,7 +580,10 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
 #pragma unroll
       for (int i = 0; i < NK; ++i) rk[i] = k_row[i] < left ? *reinterpret_cast<const uint2*>(tk + k_off[i]) : zero;
 #pragma unroll
-      for (int i = 0; i < NV; ++i) rv[i] = v_row[i] < left ? *reinterpret_cast<const uint2*>(tv + v_off[i]) : zero;
+      for (int i = 0; i < NV; ++i) {
+        if constexpr (VU == 8) rv[i] = v_row[i] < left ? *reinterpret_cast<const uint2*>(tv + v_off[i]) : zero;
+        else rv[i] = v_row[i] < left ? make_uint2(*reinterpret_cast<const uint32_t*>(tv + v_off[i]), 0u) : zero;
+      }
       rs = s_row < left ? *reinterpret_cast<const uint2*>(gs + (int64_t)(k0 + koff) * G + p * 8) : zero;
       if (p < kHalfN) {
         const bool live = koff + p < left;
@@ -613,8 +618,10 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
         if (i * kProducers + p < UK) *reinterpret_cast<uint2*>(pk + (i * kProducers + p) * 8) = rk[i];
 #pragma unroll
       for (int i = 0; i < NV; ++i)
-        if (i * kProducers + p < UV)
-          *reinterpret_cast<uint2*>(pk + L::kIdxK + L::kSgn + (i * kProducers + p) * 8) = rv[i];
+        if (i * kProducers + p < UV) {
+          if constexpr (VU == 8) *reinterpret_cast<uint2*>(pk + L::kIdxK + L::kSgn + (i * kProducers + p) * 8) = rv[i];
+          else *reinterpret_cast<uint32_t*>(pk + L::kIdxK + L::kSgn + (i * kProducers + p) * 4) = rv[i].x;
+        }
       if (p < US) *reinterpret_cast<uint2*>(pk + L::kIdxK + p * 8) = rs;
       if (p < kHalfN) {
         nk_s[ps][p] = (rn[0] & 0xffffu) * 0x10001u;
@@ -843,7 +850,10 @@ int attention_c2(const AttnArgs& a, const PairArgs& x, int64_t B, int d, int bit
   if (d == 128)
     return bits == 2 ? launch_c2<128, 2>(a, x, B, stream) : bits == 3 ? launch_c2<128, 3>(a, x, B, stream)
                                                                       : launch_c2<128, 4>(a, x, B, stream);
-  return fail(TQ_ERR_UNSUPPORTED, "the SM-pair attention kernel is built for head_dim 128 only");
+  if (d == 64)
+    return bits == 2 ? launch_c2<64, 2>(a, x, B, stream) : bits == 3 ? launch_c2<64, 3>(a, x, B, stream)
+                                                                    : launch_c2<64, 4>(a, x, B, stream);
+  return fail(TQ_ERR_UNSUPPORTED, "the SM-pair attention kernel is built for head_dim 64 and 128 only");
 }
 
 }  // namespace tq

@@ -873,7 +873,7 @@ int prepare_queries_bf16(const void* q, int dtype, int64_t B, int64_t Hq, int64_
   return d == 128 ? launch_rows_gemm<128, 256>(prep, stream) : launch_rows_gemm<64, 128>(prep, stream);
 }
 
-// The SM-pair kernel (tq_attention_c2.cu) serves head_dim 128; TQ_B200_ATTN=ws selects the single-SM
+// The SM-pair kernel (tq_attention_c2.cu) serves head_dim 64 and 128; TQ_B200_ATTN=ws selects the single-SM
 // kernel instead (diagnostics).
 static bool use_sm_pairs() {
   static int cached = -1;
@@ -888,7 +888,7 @@ static bool use_sm_pairs() {
 enum class Bf16Path { kDecode, kPairs, kSingle };
 static Bf16Path bf16_path(const AttnArgs& a, int64_t Sq, int d) {
   if (decode_applies(a, d) && Sq <= 16) return Bf16Path::kDecode;
-  return (d == 128 && use_sm_pairs()) ? Bf16Path::kPairs : Bf16Path::kSingle;
+  return ((d == 128 || d == 64) && use_sm_pairs()) ? Bf16Path::kPairs : Bf16Path::kSingle;
 }
 
 size_t workspace_bytes_bf16_prepared(int64_t B, int64_t Hq, int64_t Sq, int64_t Hkv, int64_t Sk, int64_t kv_stride,
