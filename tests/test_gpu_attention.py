@@ -66,9 +66,10 @@ def test_fused_attention_causal_gqa(mode, d, bits):
 
 
 @pytest.mark.parametrize("mode", ["fp32", "bf16"])
+@pytest.mark.parametrize("d", [128, 64])
 @pytest.mark.parametrize("Sq,Sk", [(1, 1), (7, 7), (129, 129), (64, 300), (1, 513), (256, 256)])
-def test_fused_attention_shapes(mode, Sq, Sk):
-    d, bits = 128, 3
+def test_fused_attention_shapes(mode, Sq, Sk, d):
+    bits = 3
     dtype = torch.float32 if mode == "fp32" else torch.bfloat16
     q, k, v = _case(1, 2, 1, Sq, Sk, d, seed=Sq + Sk, dtype=dtype)
     kp, vp = oracle_params(d, bits)
@@ -81,12 +82,13 @@ def test_fused_attention_shapes(mode, Sq, Sk):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("d", [128, 64])
 @pytest.mark.parametrize("Hq,Hkv", [(4, 2), (3, 3)])
-def test_tensor_core_mode_converts_other_dtypes_and_follows_strides(dtype, Hq, Hkv):
+def test_tensor_core_mode_converts_other_dtypes_and_follows_strides(dtype, Hq, Hkv, d):
     """bf16 (tensor-core) mode fed fp16 / fp32 queries laid out [B, S, H, D] (the layout the family
     adapters see before their transpose): the kernel converts the rows itself, follows the strides and
     writes the output in the query dtype.  An odd GQA group pairs position blocks instead of heads."""
-    d, bits, B, S = 128, 3, 2, 300
+    bits, B, S = 3, 2, 300
     q, k, v = _case(B, Hq, Hkv, S, S, d, seed=11, dtype=torch.float32)
     kp, vp = oracle_params(d, bits)
     ok, ov = orc.key_compress(k, kp), orc.value_compress(v, vp)
@@ -121,11 +123,12 @@ def test_decode_sized_calls_use_the_split_kv_kernel(bits, Sq, Sk, causal):
     assert rel_err(out, want) < TOL["bf16"], rel_err(out, want)
 
 
+@pytest.mark.parametrize("d", [128, 64])
 @pytest.mark.parametrize("mode", ["fp32", "bf16"])
-def test_fused_attention_additive_mask_and_noncausal(mode):
+def test_fused_attention_additive_mask_and_noncausal(mode, d):
     """Padding-style additive mask (finite large negative, as HF builds it) and the
     non-causal path."""
-    d, bits, B, S = 128, 3, 2, 150
+    bits, B, S = 3, 2, 150
     dtype = torch.float32 if mode == "fp32" else torch.bfloat16
     q, k, v = _case(B, 2, 2, S, S, d, seed=5, dtype=dtype)
     kp, vp = oracle_params(d, bits)
