@@ -428,7 +428,7 @@ def config5_section(ctx: Ctx, bits: int, steps: int = 2, warm: int = 1, seq: int
     return res
 
 
-def head_dim64_section(ctx: Ctx, bits: int, steps: int = 10, warm: int = 3):
+def head_dim64_section(ctx: Ctx, bits: int, batch: int = B, steps: int = 10, warm: int = 3):
     """The op-level step (compress K and V, fused causal attention) on the headline shape with head_dim 64, the
     head dimension of every GPT-2 size, plus a GPT-2-small-shaped call (12 heads, no grouping, 1024 positions):
     the SM-pair kernel serves both head dimensions."""
@@ -438,7 +438,7 @@ def head_dim64_section(ctx: Ctx, bits: int, steps: int = 10, warm: int = 3):
     kc = tq.TurboQuantCompressorV2(d, bits, 42, device=str(dev))
     vc = tq.TurboQuantCompressorMSE(d, bits, 10042, device=str(dev))
     out = {}
-    for name, (batch, hq, hkv, seq) in {"gqa4_s8192": (B, HQ, HKV, S), "gpt2small_s1024": (8, 12, 12, 1024)}.items():
+    for name, (batch, hq, hkv, seq) in {"gqa4_s8192": (batch, HQ, HKV, S), "gpt2small_s1024": (8, 12, 12, 1024)}.items():
         g = torch.Generator(device=dev).manual_seed(0)
         q = torch.randn(batch, hq, seq, d, generator=g, device=dev).to(torch.bfloat16)
         k = torch.randn(batch, hkv, seq, d, generator=g, device=dev).to(torch.bfloat16)
@@ -774,7 +774,7 @@ def run_headline(args):
     if "decode" in args.want:
         extra["decode"] = decode_section(ctx, bits)
     if "head_dim64" in args.want:
-        extra["head_dim64"] = head_dim64_section(ctx, bits)
+        extra["head_dim64"] = head_dim64_section(ctx, bits, batch=batch)
     for name in ("llama8b", "deepseek7b"):
         if name in args.want:
             extra.setdefault("models", {})[name] = model_section(ctx, name, bits)
