@@ -125,6 +125,34 @@ def test_generation_with_the_compressed_cache_matches_recomputation():
         assert gen.shape == (1, 36)
 
 
+def test_gpt2_generation_with_the_compressed_cache_matches_recomputation():
+    """The same extension on the GPT-2 adapter (head_dim 64, learned positions, fused c_attn): token-by-token
+    decoding against the compressed cache must give the logits of the cache-less flow, and generate() the same
+    greedy tokens."""
+    from transformers import GPT2Config, GPT2LMHeadModel
+    from turboquant_b200 import apply_turboquant
+    torch.manual_seed(0)
+    cfg = GPT2Config(n_embd=256, n_head=4, n_layer=2, vocab_size=512, n_positions=512, attn_pdrop=0.0,
+                     resid_pdrop=0.0, embd_pdrop=0.0)
+    base = GPT2LMHeadModel(cfg).eval().cuda().to(torch.bfloat16)
+    plain = apply_turboquant(copy.deepcopy(base), bits=3, seed=42)
+    cached = apply_turboquant(copy.deepcopy(base), bits=3, seed=42, kv_cache_capacity=400)
+    assert plain.config.use_cache is False and cached.config.use_cache is True
+    ids = torch.randint(0, 512, (2, 200), generator=torch.Generator().manual_seed(4)).cuda()
+    steps = 4
+    with torch.no_grad():
+        out = cached(input_ids=ids[:, :200 - steps], use_cache=True)
+        pkv = out.past_key_values
+        assert rel_err(out.logits[:, -1].float(), plain(input_ids=ids[:, :200 - steps]).logits[:, -1].float()) < 1e-6
+        for t in range(200 - steps, 200):
+            out = cached(input_ids=ids[:, t:t + 1], past_key_values=pkv, use_cache=True)
+            want = plain(input_ids=ids[:, :t + 1]).logits[:, -1].float()
+            assert rel_err(out.logits[:, -1].float(), want) < 3e-2, (t, rel_err(out.logits[:, -1].float(), want))
+        gen = cached.generate(ids[:1, :32], max_new_tokens=4, do_sample=False, pad_token_id=0)
+        want = plain.generate(ids[:1, :32], max_new_tokens=4, do_sample=False, pad_token_id=0)
+        assert gen.shape == (1, 36) and torch.equal(gen[:, :33], want[:, :33])  # the first new token comes from the same prefill
+
+
 def test_generate_without_cache_recomputes_the_whole_sequence():
     """The reference switches `config.use_cache` off (patch.py:80-81); current transformers read the flag from
     `generation_config`, which has to follow, or generate() would hand the adapters single tokens."""

@@ -7,10 +7,11 @@ import torch.nn as nn
 
 from ..compressors import compress_kv, fused_attention
 from ..plugin import TurboQuantAttentionBase, register_family
+from ._cached import CompressedCacheMixin
 
 
 @register_family("gpt2")
-class TurboQuantGPT2Attention(TurboQuantAttentionBase):
+class TurboQuantGPT2Attention(CompressedCacheMixin, TurboQuantAttentionBase):
     ATTENTION_CLASS_NAMES = ("GPT2Attention",)
 
     @classmethod
@@ -39,6 +40,10 @@ class TurboQuantGPT2Attention(TurboQuantAttentionBase):
         B, T, _ = hidden_states.shape
         q, k, v = self.c_attn(hidden_states).split(self.embed_dim, dim=2)
         q, k, v = (t.view(B, T, self.num_heads, self.head_dim).transpose(1, 2) for t in (q, k, v))
+        if self.kv_cache_capacity is not None and past_key_values is not None:
+            # generation against a persistent compressed cache (an extension: the reference runs cache-less)
+            out = self._attend_cached(q, k, v, past_key_values, attention_mask)
+            return self.resid_dropout(self.c_proj(out.transpose(1, 2).reshape(B, T, self.embed_dim))), None
         ck, cv = compress_kv(k, v, self.key_compressor, self.val_compressor)
         # attention-probability dropout (attn_pdrop) has no counterpart in the fused kernel; it is
         # inactive in eval mode and warned about above in train mode
