@@ -145,6 +145,23 @@ int tq_prepare_constants(const float* Pi_k, const float* S_eff, const float* cen
                          const float* boundaries_v, int bits, int d, void* constants, size_t constants_bytes,
                          void* stream);
 
+/* ---- rotary position embedding (the adapters' step before compression) ---------------- */
+
+/* q_out = q * cos + rotate_half(q) * sin and the same for k, both in ONE launch: every element read once and
+ * written once.  q: [B, Hq, S, d], k: [B, Hkv, S, d] of `dtype` with their own element strides (the transposed
+ * view of a projection output is fine); cos, sin: [B or 1, S, d] of the same dtype, rows contiguous, element
+ * strides cs_stride_b (0 for a broadcast batch) and cs_stride_s; q_out, k_out: contiguous [B, H, S, d], must not
+ * alias the inputs.  rotate_half(x) = concat(-x[d/2:], x[:d/2]).  Each product and the sum are rounded to `dtype`
+ * separately, which is what the separate torch kernels do: the result equals HF's to the bit.  All pointers
+ * 16-byte aligned, strides multiples of 16 bytes, d a multiple of 32.  Either side may have zero heads.
+ * Replaces apply_rotary_pos_emb as the family adapters call it (src/transformers_turboquant/families/llama.py:98,
+ * qwen2.py:98). */
+int tq_rope(const void* q, const void* k, int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int d,
+            int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+            int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s,
+            const void* cos, const void* sin, int64_t cs_stride_b, int64_t cs_stride_s,
+            void* q_out, void* k_out, void* stream);
+
 /* ---- compression ---------------------------------------------------------------- */
 
 /* Keys and values of one layer in ONE launch: tq_compress_keys(keys) and tq_compress_values(values) with the

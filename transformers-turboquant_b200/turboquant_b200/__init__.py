@@ -14,10 +14,11 @@ from .kernels import (asymmetric_attention_scores, lloyd_max_dequantize, lloyd_m
 from .scalar_codebook import LloydMaxCodebook, solve_lloyd_max  # noqa: E402
 from .quantizers import TurboQuantKVCache, TurboQuantMSE, TurboQuantProd  # noqa: E402
 from .kv_cache import CompressedKVCache  # noqa: E402
+from .rotary import rope  # noqa: E402
 
 __version__ = "0.1.0"
 __all__ = ["apply_turboquant", "register_family", "get_attention_class", "UnsupportedModelError",
            "TurboQuantAttentionBase", "TurboQuantCompressorV2", "TurboQuantCompressorMSE",
-           "fused_attention", "compress_kv", "prepared_constants", "device_fault_count", "pack_bits", "unpack_bits", "lloyd_max_quantize",
-           "lloyd_max_dequantize", "asymmetric_attention_scores", "LloydMaxCodebook", "solve_lloyd_max",
+           "fused_attention", "compress_kv", "prepared_constants", "rope", "device_fault_count", "pack_bits",
+           "unpack_bits", "lloyd_max_quantize", "lloyd_max_dequantize", "asymmetric_attention_scores", "LloydMaxCodebook", "solve_lloyd_max",
            "TurboQuantMSE", "TurboQuantProd", "TurboQuantKVCache", "CompressedKVCache"]

@@ -68,6 +68,7 @@ SIGNATURES = {
                               _p, _p, _i, _f, _i, _p, _l, _l, _p, _l, _l, _l, _p, _z, _i, _p]),
     "tq_attention_fwd_cached": (_i, [_p, _i, _l, _l, _l, _i, _l, _l, _l, _l, _l, _l, _p, _p, _p, _p, _p, _p, _p, _p, _p,
                                      _p, _p, _i, _f, _i, _p, _l, _l, _p, _l, _l, _l, _p, _z, _p]),
+    "tq_rope": (_i, [_p, _p, _i, _l, _l, _l, _l, _i, _l, _l, _l, _l, _l, _l, _p, _p, _l, _l, _p, _p, _p]),
     "tq_static_scratch_bytes": (_z, []),
     "tq_attention_fwd_static": (_i, [_p, _i, _l, _l, _l, _i, _l, _l, _l, _l, _l, _p, _p, _p, _p, _p, _p, _p, _p, _p,
                                      _p, _p, _i, _f, _i, _p, _l, _l, _p, _l, _l, _l, _i, _p]),

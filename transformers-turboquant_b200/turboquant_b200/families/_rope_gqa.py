@@ -24,6 +24,11 @@ class RopeGQAAttention(CompressedCacheMixin, TurboQuantAttentionBase):
 
     @staticmethod
     def _rotary(q, k, cos, sin):
+        """apply_rotary_pos_emb of the reference's adapters (families/llama.py:98), in one launch of the
+        library's own kernel where it applies (same bits); HF's function otherwise (partial rotary widths)."""
+        from ..rotary import rope, rope_applies
+        if rope_applies(q, k, cos, sin):
+            return rope(q, k, cos, sin)
         from transformers.models.llama.modeling_llama import apply_rotary_pos_emb
         return apply_rotary_pos_emb(q, k, cos, sin)
 
