@@ -334,7 +334,8 @@ def fused_attention(q: torch.Tensor, compressed_k: dict, compressed_v: dict,
 
     q [B, Hq, Sq, D]; the compressed tensors hold Hkv heads with Hq % Hkv == 0 (query head h
     reads KV head h // (Hq // Hkv), the `repeat_interleave` grouping).  `attention_mask` is an
-    optional additive mask broadcastable to [B, 1, Sq, Sk].  Returns [B, Hq, Sq, D] in q.dtype.
+    optional additive mask broadcastable to [B, 1, Sq, Sk].  Returns [B, Hq, Sq, D] in q.dtype (stored
+    position-major, i.e. contiguous after `.transpose(1, 2)`).
     """
     _require_cuda(q, "q")
     key_compressor._check_device(q)
@@ -348,7 +349,9 @@ def fused_attention(q: torch.Tensor, compressed_k: dict, compressed_v: dict,
     qv = _rows_view(q)
     dev = qv.device
     m = resolve_mode(qv.dtype, mode or key_compressor.mode)
-    out = torch.empty((B, Hq, Sq, D), dtype=qv.dtype, device=dev)
+    # [B, Hq, Sq, D] as a view of a [B, Sq, Hq, D] buffer: the adapters' `out.transpose(1, 2).reshape(B, Sq, Hq * D)`
+    # in front of the output projection is then a view, not a copy (the kernels write through the strides)
+    out = torch.empty((B, Sq, Hq, D), dtype=qv.dtype, device=dev).transpose(1, 2)
     consts = prepared_constants(key_compressor, val_compressor)
     ws = _workspace(dev, _lib.lib.tq_attention_prepared_workspace_bytes(B, Hq, Sq, Hkv, Sk, Sk, D, m))
     mk, mask_ptr, msb, msq = _mask_args(attention_mask, B, Sq, Sk, dev)  # mk keeps the converted mask alive

@@ -122,7 +122,7 @@ class CompressedKVCache:
         vc._check_device(q)
         qv = _rows_view(q)
         dev = qv.device
-        out = torch.empty((B, Hq, Sq, D), dtype=qv.dtype, device=dev)
+        out = torch.empty((B, Sq, Hq, D), dtype=qv.dtype, device=dev).transpose(1, 2)  # position-major, as fused_attention
         ws = _workspace(dev, _lib.lib.tq_attention_prepared_workspace_bytes(B, Hq, Sq, self.kv_heads, self.length,
                                                                             self.capacity, D, _lib.TQ_MODE_BF16))
         scale = float(sm_scale) if sm_scale is not None else 1.0 / math.sqrt(D)
