@@ -57,20 +57,22 @@ struct alignas(16) Chunk {
 // One work item = one 16-byte chunk of the first half of a row and its partner in the second half.
 // Items are numbered in the memory order of the projection output ([B, S, H, D]: consecutive threads read
 // consecutive bytes); each output row is written in two 16-byte-per-thread runs.
-template <int DTYPE>
+// IDX: uint32_t when the item count fits (64-bit divisions would otherwise dominate the instruction stream).
+template <int DTYPE, typename IDX>
 __global__ void __launch_bounds__(256) rope_kernel(const RopeArgs a) {
   using E = Elem<DTYPE>;
   using T = typename E::T;
   constexpr int N = 16 / (int)sizeof(T);  // elements per chunk
-  const int half = a.d / 2, cpr = half / N;  // chunks per half row
-  const int64_t H = a.Hq + a.Hkv;
-  const int64_t items = a.B * a.S * H * cpr;
-  for (int64_t it = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; it < items; it += (int64_t)gridDim.x * blockDim.x) {
+  const int half = a.d / 2;
+  const IDX cpr = (IDX)(half / N);  // chunks per half row
+  const IDX H = (IDX)(a.Hq + a.Hkv), S = (IDX)a.S;
+  const IDX items = (IDX)a.B * S * H * cpr;
+  for (IDX it = (IDX)blockIdx.x * blockDim.x + threadIdx.x; it < items; it += (IDX)gridDim.x * blockDim.x) {
     const int c = (int)(it % cpr);
-    int64_t r = it / cpr;
-    const int64_t h = r % H;
+    IDX r = it / cpr;
+    const int64_t h = (int64_t)(r % H);
     r /= H;
-    const int64_t s = r % a.S, b = r / a.S;
+    const int64_t s = (int64_t)(r % S), b = (int64_t)(r / S);
     const bool is_q = h < a.Hq;
     const int64_t hh = is_q ? h : h - a.Hq;
     const T* src = is_q ? static_cast<const T*>(a.q) + b * a.qsb + hh * a.qsh + s * a.qss
@@ -134,9 +136,17 @@ extern "C" int tq_rope(const void* q, const void* k, int dtype, int64_t B, int64
   TQ_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const int64_t want = (items + 255) / 256, cap = (int64_t)sms * 8;  // 8 resident CTAs of 256 threads per SM
   const unsigned grid = (unsigned)(want < cap ? want : cap);
-  if (dtype == TQ_BF16) rope_kernel<TQ_BF16><<<grid, 256, 0, s>>>(a);
-  else if (dtype == TQ_F16) rope_kernel<TQ_F16><<<grid, 256, 0, s>>>(a);
-  else rope_kernel<TQ_F32><<<grid, 256, 0, s>>>(a);
+  const bool small = items + (int64_t)grid * 256 < (int64_t)0xffffffffu;  // the loop counter may overshoot once
+  if (dtype == TQ_BF16) {
+    if (small) rope_kernel<TQ_BF16, uint32_t><<<grid, 256, 0, s>>>(a);
+    else rope_kernel<TQ_BF16, int64_t><<<grid, 256, 0, s>>>(a);
+  } else if (dtype == TQ_F16) {
+    if (small) rope_kernel<TQ_F16, uint32_t><<<grid, 256, 0, s>>>(a);
+    else rope_kernel<TQ_F16, int64_t><<<grid, 256, 0, s>>>(a);
+  } else {
+    if (small) rope_kernel<TQ_F32, uint32_t><<<grid, 256, 0, s>>>(a);
+    else rope_kernel<TQ_F32, int64_t><<<grid, 256, 0, s>>>(a);
+  }
   TQ_CUDA_OK(cudaGetLastError());
   return TQ_OK;
 }
