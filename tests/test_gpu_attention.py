@@ -403,9 +403,14 @@ def test_tensors_on_a_device_that_is_not_current():
         out = fused_attention(qd, kc.compress(kd), vc.compress(vd), kc, vc, causal=True)
         dec = fused_attention(qd[:, :, -1:], kc.compress(kd), vc.compress(vd), kc, vc, causal=True)
         assert out.device == torch.device(dev) and torch.cuda.current_device() == 0
-        outs.append((out.cpu(), dec.cpu()))
+        # the rotary kernel too
+        from turboquant_b200 import rope
+        ang = torch.arange(200, dtype=torch.float32)[None, :, None] * torch.linspace(0.01, 1.0, d)[None, None, :]
+        rq, rk = rope(qd, kd, ang.cos().to(torch.bfloat16).to(dev), ang.sin().to(torch.bfloat16).to(dev))
+        assert rq.device == torch.device(dev) and torch.cuda.current_device() == 0
+        outs.append((out.cpu(), dec.cpu(), rq.cpu(), rk.cpu()))
         assert device_fault_count(dev) == 0
-    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    assert all(torch.equal(a, b) for a, b in zip(outs[0], outs[1]))
 
 
 def test_single_sm_kernel_selected_by_environment():
