@@ -332,7 +332,8 @@ def model_section(ctx: Ctx, name: str, bits: int, steps: int = 3, warm: int = 2)
     tokens) with every attention layer replaced by apply_turboquant(bits, seed=42).  The global batch is split over
     the ranks (full replica per GPU: strong scaling); the only collective is the all_gather of the last-token
     logits, inside the timed region, as are the host-to-device copy of the token ids and the device-to-host read
-    of the logits.  The same model on HF's sdpa attention is timed first, beside it."""
+    of the logits.  The same model as HF ships it (sdpa attention, HF's own rotary-embedding function) is timed
+    first, beside it; the adapters rotate q and k with the library's one-launch kernel."""
     import turboquant_b200 as tq
     from transformers import LlamaConfig, LlamaForCausalLM
     from turboquant_b200.sharding import gather_rows, unit_range
