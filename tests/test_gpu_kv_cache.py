@@ -117,3 +117,29 @@ def test_fully_masked_row_averages_uniformly():
     # uniform weights: every query head of a KV head gets the same mean of the decompressed values
     want = vc.decompress(vc.compress(v)).mean(dim=2, keepdim=True).repeat_interleave(Hq // Hkv, dim=1)
     assert rel_err(got, want) < 2e-2, rel_err(got, want)
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_single_token_cache_through_the_gather_path(d):
+    """One token per head in a cache with room for more: the prefix gathered for the prefill kernels must be a
+    dense copy (for a single token `reshape` alone returns a view whose rows are a whole capacity apart).  fp32
+    queries take the gather path at both head dimensions."""
+    from turboquant_b200 import CompressedKVCache, compress_kv, fused_attention
+    bits, B, Hq, Hkv = 3, 3, 4, 2
+    kc, vc = device_compressors(d, bits)
+    g = torch.Generator(device="cuda").manual_seed(d)
+    k = torch.randn(B, Hkv, 1, d, generator=g, device="cuda").to(torch.bfloat16)
+    v = torch.randn(B, Hkv, 1, d, generator=g, device="cuda").to(torch.bfloat16)
+    q = torch.randn(B, Hq, 1, d, generator=g, device="cuda")
+    cache = CompressedKVCache(kc, vc, B, Hkv, 64, device="cuda")
+    cache.append(k, v)
+    ck, cv = compress_kv(k, v, kc, vc)
+    for query, tol in ((q, 1e-6), (q.to(torch.bfloat16), 1e-6 if d == 64 else 1e-2)):
+        # same kernel on both sides through the gather path; at head_dim 128 a 16-bit query reads the cache in place
+        # with the split-KV kernel instead
+        got = cache.attend(query, causal=True)
+        want = fused_attention(query, ck, cv, kc, vc, causal=True)
+        assert rel_err(got, want) < tol, rel_err(got, want)
+    # and the consumers of a compressed dictionary refuse arrays that do not match its shape
+    with pytest.raises(ValueError):
+        fused_attention(q, dict(ck, packed_key_indices=ck["packed_key_indices"][:-1]), cv, kc, vc)

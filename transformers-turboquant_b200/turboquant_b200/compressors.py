@@ -44,6 +44,24 @@ def _require_cuda(t: torch.Tensor, what: str) -> None:
         raise RuntimeError(f"{what} must be a CUDA tensor: turboquant_b200 has no CPU path")
 
 
+_KEY_ARRAYS = ("packed_key_indices", "packed_qjl_signs", "vec_norms", "residual_norm")
+_VALUE_ARRAYS = ("packed_indices", "vec_norms")
+
+
+def _dense_packed(compressed: dict, keys: tuple) -> dict:
+    """The packed arrays of a compressed dictionary as the kernels read them: dense rows, one per (b, h, s) in that
+    order.  A strided view (a slice of a larger buffer) is copied; a wrong row count is refused, not read past."""
+    B, H, S, _ = compressed["shape"]
+    out = dict(compressed)
+    for name in keys:
+        t = compressed[name]
+        rows = t.numel() // max(t.shape[-1], 1) if name.startswith("packed") else t.numel()  # packed: [..., bytes]
+        if rows != B * H * S:
+            raise ValueError(f"{name} holds {tuple(t.shape)} entries for a compressed shape {compressed['shape']}")
+        out[name] = t if t.is_contiguous() else t.contiguous()
+    return out
+
+
 def _rows_view(t: torch.Tensor) -> torch.Tensor:
     """[B, H, S, D] tensor whose rows the kernels can read in place: supported dtype, unit
     inner stride, 16-byte aligned rows.  Anything else is copied once."""
@@ -238,6 +256,7 @@ class TurboQuantCompressorV2(_Constants):
         Bk, Hkv, Sk, Dk = compressed["shape"]
         if (Bk, Dk) != (B, D) or D != self.head_dim:
             raise ValueError(f"queries {tuple(queries.shape)} do not match compressed keys {compressed['shape']}")
+        compressed = _dense_packed(compressed, _KEY_ARRAYS)
         q = _rows_view(queries)
         dev = q.device
         scores = torch.empty((B, Hq, Sq, Sk), dtype=torch.float32, device=dev)
@@ -283,6 +302,7 @@ class TurboQuantCompressorMSE(_Constants):
     def decompress(self, compressed: dict) -> torch.Tensor:
         """packed dict -> fp32 [B, H, S, D] (compressors.py:296-317)."""
         B, H, S, D = compressed["shape"]
+        compressed = _dense_packed(compressed, _VALUE_ARRAYS)
         idx = compressed["packed_indices"]
         _require_cuda(idx, "compressed values")
         self._check_device(idx)
@@ -346,6 +366,7 @@ def fused_attention(q: torch.Tensor, compressed_k: dict, compressed_v: dict,
         raise ValueError("q, compressed keys and compressed values disagree on shape")
     if key_compressor.bits != val_compressor.bits:
         raise ValueError("key and value compressors must use the same bit width")
+    compressed_k, compressed_v = _dense_packed(compressed_k, _KEY_ARRAYS), _dense_packed(compressed_v, _VALUE_ARRAYS)
     qv = _rows_view(q)
     dev = qv.device
     m = resolve_mode(qv.dtype, mode or key_compressor.mode)

@@ -87,13 +87,18 @@ class CompressedKVCache:
         self.length += S
 
     def _contiguous_prefix(self) -> tuple[dict, dict]:
+        """The tokens in use as the contiguous dictionaries `compress()` returns (copies: the cache rows are
+        `capacity` apart).  `reshape` alone is not enough: for a single token per head it returns a strided view."""
         n, shape = self.length, (self.batch, self.kv_heads, self.length, self.head_dim)
-        ck = {"packed_key_indices": self.key_indices[:, :, :n].reshape(-1, self.key_indices.shape[-1]),
-              "packed_qjl_signs": self.key_signs[:, :, :n].reshape(-1, self.key_signs.shape[-1]),
+
+        def rows(t):
+            return t[:, :, :n].reshape(-1, t.shape[-1]).contiguous()
+
+        ck = {"packed_key_indices": rows(self.key_indices), "packed_qjl_signs": rows(self.key_signs),
               "vec_norms": self.key_norms[:, :, :n].contiguous(),
               "residual_norm": self.key_residual_norms[:, :, :n].contiguous(), "shape": shape}
-        cv = {"packed_indices": self.value_indices[:, :, :n].reshape(-1, self.value_indices.shape[-1]),
-              "vec_norms": self.value_norms[:, :, :n].reshape(-1), "shape": shape}
+        cv = {"packed_indices": rows(self.value_indices),
+              "vec_norms": self.value_norms[:, :, :n].reshape(-1).contiguous(), "shape": shape}
         return ck, cv
 
     @torch.no_grad()
