@@ -14,6 +14,7 @@ The same line carries, as extra objects, the other halves of the metric (`--sect
   decode          one new token per sequence against a 32768-key compressed cache (split-KV kernel, HBM roofline)
   head_dim64      the same op-level step at head_dim 64 (GPT-2's head dimension): headline shape and a
                   GPT-2-small-shaped call
+  rope            rotary embedding of one LLaMA-8B-shaped layer's q and k: the library's kernel against HF's function
   models.llama8b  prefill tokens/s of a LLaMA-3.1-8B-shaped random-init model, global batch 8 x 4096 split over
                   the ranks, 3-bit TurboQuant attention, logits all_gather inside the timed region, with the same
                   model on HF sdpa attention beside it
@@ -53,7 +54,7 @@ import torch  # noqa: E402
 B, HQ, HKV, S, D = 4, 32, 8, 8192, 128
 METRIC = "fused_tq_attention_keys_per_s"
 UNIT = "keys/s"
-ALL_SECTIONS = ("e2e", "cpu", "gpuref", "sustained", "decode", "head_dim64", "llama8b", "deepseek7b", "config5")
+ALL_SECTIONS = ("e2e", "cpu", "gpuref", "sustained", "decode", "head_dim64", "rope", "llama8b", "deepseek7b", "config5")
 
 
 def parse():
@@ -459,6 +460,31 @@ def head_dim64_section(ctx: Ctx, bits: int, batch: int = B, steps: int = 10, war
             "flops": "6 d per visible (query, key) pair", **out}
 
 
+def rope_section(ctx: Ctx, steps: int = 20, warm: int = 3):
+    """Rotary embedding of the q and k heads of one LLaMA-3.1-8B-shaped layer (batch 8 x 4096 tokens, 32 + 8 heads of
+    128, bf16, the [B, H, S, D] views of [B, S, H, D] projection outputs): the library's one-launch kernel against
+    HF's apply_rotary_pos_emb, which the reference's adapters call.  HBM-bound: every element in and out once."""
+    import turboquant_b200 as tq
+    from transformers.models.llama.modeling_llama import apply_rotary_pos_emb
+    dev = ctx.dev
+    batch, seq, d = 8, 4096, D
+    g = torch.Generator(device=dev).manual_seed(0)
+    q = torch.randn(batch, seq, HQ, d, generator=g, device=dev).to(torch.bfloat16).transpose(1, 2)
+    k = torch.randn(batch, seq, HKV, d, generator=g, device=dev).to(torch.bfloat16).transpose(1, 2)
+    ang = torch.arange(seq, device=dev, dtype=torch.float32)[None, :, None] * \
+        (1.0 / 500000.0 ** (torch.arange(0, d, 2, device=dev, dtype=torch.float32) / d)).repeat(2)[None, None, :]
+    cos, sin = ang.cos().to(torch.bfloat16).expand(batch, seq, d), ang.sin().to(torch.bfloat16).expand(batch, seq, d)
+    ms, (rq, rk) = timed_steps(ctx, lambda: tq.rope(q, k, cos, sin), steps, warm)
+    ms_hf, (hq, hk) = timed_steps(ctx, lambda: apply_rotary_pos_emb(q, k, cos, sin), max(steps // 4, 2), warm)
+    nbytes = 2 * batch * (HQ + HKV) * seq * d * 2 + 2 * seq * d * 2
+    peaks = measured_peaks()
+    return {"kernel": "rope_kernel<bf16>", "ms_per_call": ms, "hf_apply_rotary_pos_emb_ms_per_call": ms_hf,
+            "bit_identical_to_hf": bool(torch.equal(rq, hq) and torch.equal(rk, hk)),
+            "roofline": {"bound": "hbm", "achieved": nbytes / (ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "algorithmic_bytes_per_call": nbytes},
+            "shape": {"batch_per_gpu": batch, "seq": seq, "q_heads": HQ, "kv_heads": HKV, "head_dim": d, "dtype": "bf16"}}
+
+
 def decode_section(ctx: Ctx, bits: int, steps: int = 50, warm: int = 3):
     """Decode step against a resident compressed KV cache: one query token per sequence (32 query / 8 KV heads,
     d = 128) attends to Sk = 32768 cached keys, batch 8 -- the per-GPU share of the scaling shape K,V
@@ -774,6 +800,8 @@ def run_headline(args):
     extra = {}
     if "decode" in args.want:
         extra["decode"] = decode_section(ctx, bits)
+    if "rope" in args.want:
+        extra["rope"] = rope_section(ctx)
     if "head_dim64" in args.want:
         extra["head_dim64"] = head_dim64_section(ctx, bits, batch=batch)
     for name in ("llama8b", "deepseek7b"):
