@@ -379,9 +379,31 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
           t[32 + c] = __uint_as_float(raw1[c]);
         }
       }
-      float mx = -INFINITY;
       const bool edge = (k0 + kBN > a.Sk) || (a.causal && k0 + kBN - 1 > q0 + shift) || a.mask != nullptr;
-      if (!edge) {
+      if (edge) {
+        // Tiles that cross the end of the keys or the causal diagonal, and every tile under an additive mask.  A
+        // thread's 64 columns are the keys kc0 .. kc0 + 63: `vsk` is the last column that exists, `vis` the last one
+        // this row may see.  Everything stays in raw score units (the mask is divided by sm_scale instead of the
+        // scores being multiplied by it), so that the common path below takes the maximum: one compare and one
+        // select per score here, where a branchy per-element form cost more than two whole tile periods.
+        const int vsk = (int)a.Sk - 1 - kc0;
+        const int vis = a.causal ? min(vsk, qi + shift - kc0) : vsk;
+        if (a.mask != nullptr && qi < a.Sq) {
+          const float* mrow = a.mask + b * a.mask_stride_b + (int64_t)qi * a.mask_stride_q + kc0;
+          // The large negative value HF masks with is clamped to -60000 in log2 units (exp2 of it is still exactly
+          // 0 beside any real score) so that it stays finite: a row whose visible keys are all masked then averages
+          // them uniformly, as a softmax over equal finite scores does in the reference, instead of coming out as
+          // zeros.
+          const float m_unit = kLog2e * rcexp, floor_raw = -60000.f * rcexp;
+#pragma unroll
+          for (int c = 0; c < HC; ++c)
+            if (c <= vsk) t[c] = fmaxf(fmaf(mrow[c], m_unit, t[c]), floor_raw);
+        }
+#pragma unroll
+        for (int c = 0; c < HC; ++c) t[c] = c <= vis ? t[c] : -INFINITY;
+      }
+      float mx;
+      {
         float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;  // three-input maxima, four chains
 #pragma unroll
         for (int c8 = 0; c8 < HC; c8 += 8) {
@@ -391,23 +413,6 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
           m3 = tc::fmax3(m3, t[c8 + 6], t[c8 + 7]);
         }
         mx = fmaxf(tc::fmax3(m0, m1, m2), m3) * cexp;
-      } else {
-        const float* mrow = (a.mask != nullptr && qi < a.Sq)
-                                ? a.mask + b * a.mask_stride_b + (int64_t)qi * a.mask_stride_q + kc0
-                                : nullptr;
-#pragma unroll
-        for (int c = 0; c < HC; ++c) {
-          const int k = kc0 + c;
-          float v = t[c] * cexp;
-          // The large negative value HF masks with is clamped to -60000 (log2 units: exp2 of it is still exactly 0
-          // beside any real score) so that it stays finite and small enough for the raw-unit round trip below to be
-          // accurate: a row whose visible keys are all masked then averages them uniformly, as a softmax over equal
-          // finite scores does in the reference, instead of coming out as zeros.
-          if (mrow != nullptr && k < a.Sk) v = fmaxf(fmaf(mrow[c], kLog2e, v), -60000.f);
-          if (k >= a.Sk || (a.causal && k > qi + shift)) v = -INFINITY;
-          t[c] = v * rcexp;
-          mx = fmaxf(mx, v);
-        }
       }
       // exchange half-row maxima with the partner warp (slots alternate with the tile parity)
       tr.mark(2, j);
