@@ -305,9 +305,12 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
   asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
 }
-// fp16 pair of values clamped to the largest finite fp16 magnitude (an operand must never carry an infinity)
+// fp16 pair of values clamped to the largest finite fp16 magnitude (an operand must never carry an infinity):
+// one saturating conversion instead of four clamps and a conversion
 __device__ __forceinline__ uint32_t pack_f16x2_sat(float lo, float hi) {
-  return pack_f16x2(fminf(fmaxf(lo, -65504.f), 65504.f), fminf(fmaxf(hi, -65504.f), 65504.f));
+  uint32_t r;
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
 }
 // two fp16 products of packed pairs
 __device__ __forceinline__ uint32_t mul_f16x2(uint32_t a, uint32_t b) {
