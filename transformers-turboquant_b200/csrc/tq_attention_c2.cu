@@ -527,14 +527,22 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
       static_assert(D == 128 || D == 64, "chunks per row are derived for head_dim 64 and 128");
       const int lcpr = (a.out_dtype == TQ_F32 ? 5 : 4) - (D == 64 ? 1 : 0);  // log2 of the 16-byte chunks per row
       const int pitch = D * esz + 16, cpr = 1 << lcpr;
-      const uint8_t* Ot = smem_raw + L::kOutOff;
-      uint8_t* obase = static_cast<uint8_t*>(a.out) + (b * a.o_stride_b + head * a.o_stride_h) * esz;
+      // lane -> (row within the iteration, 16-byte chunk); every iteration moves on by 32 / cpr rows: pointers advance
+      // by constant steps (no 64-bit multiplies inside the loop)
+      const int rpi = 32 >> lcpr;
+      int r = quad * 32 + chalf * 16 + (lane >> lcpr);
+      const int c = lane & (cpr - 1);
+      const uint8_t* src = smem_raw + L::kOutOff + r * pitch + c * 16;
+      uint8_t* dst = static_cast<uint8_t*>(a.out) +
+                     (b * a.o_stride_b + head * a.o_stride_h + (int64_t)(q0 + r) * a.o_stride_s) * esz + c * 16;
+      const int64_t dstep = (int64_t)rpi * a.o_stride_s * esz;
+      const int sstep = rpi * pitch;
 #pragma unroll 4
-      for (int idx = lane; idx < 16 * cpr; idx += 32) {
-        const int r = quad * 32 + chalf * 16 + (idx >> lcpr), c = idx & (cpr - 1);
-        if (q0 + r < a.Sq)
-          *reinterpret_cast<uint4*>(obase + (int64_t)(q0 + r) * a.o_stride_s * esz + c * 16) =
-              *reinterpret_cast<const uint4*>(Ot + r * pitch + c * 16);
+      for (int i = 0; i < 16 / rpi; ++i) {
+        if (q0 + r < a.Sq) *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+        r += rpi;
+        src += sstep;
+        dst += dstep;
       }
       tr.mark(17, 999);
       tr.mark_ns(19, 999);
