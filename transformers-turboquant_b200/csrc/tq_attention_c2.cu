@@ -202,7 +202,9 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
     q0 = (2 * xpair + (int)rank) * kBM;
     q0_last = (2 * xpair + 1) * kBM;
   }
-  const int64_t kv_base = (b * a.Hkv + head / (a.Hq / a.Hkv)) * a.Sk;
+  // 32-bit division (head counts are below 65536): the 64-bit form is a subroutine of ~100 instructions, twice,
+  // on every thread's way to its first load
+  const int64_t kv_base = (b * a.Hkv + (int)head / ((int)a.Hq / (int)a.Hkv)) * a.Sk;
   const int shift = (int)(a.Sk - a.Sq);
   int k_end = (int)a.Sk;
   if (a.causal) k_end = min(k_end, min(q0_last + kBM - 1, (int)a.Sq - 1) + shift + 1);
@@ -238,11 +240,15 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
   constexpr int NA = kBM * (D / 8) / kSoftmax;
   uint4 qv[NA];
   if (tid < kSoftmax) {
-    const int64_t qbase = b * x.q_stride_b + head * x.q_stride_h;
+    // chunk c of row r0 + i * rstep: the offset advances by a constant per load
+    constexpr int rstep = kSoftmax / (D / 8);
+    static_assert(rstep % 8 == 0, "a thread keeps its row within the 8-row group and its chunk");
+    const int r0 = tid % 8 + 8 * (tid / (8 * (D / 8))), c = (tid / 8) % (D / 8);
+    int64_t off = b * x.q_stride_b + head * x.q_stride_h + (int64_t)(q0 + r0) * x.q_stride_s + c * 8;
+    const int64_t ostep = (int64_t)rstep * x.q_stride_s;
 #pragma unroll
-    for (int i = 0; i < NA; ++i) {
-      const int e = i * kSoftmax + tid, r = e % 8 + 8 * (e / (8 * (D / 8))), c = (e / 8) % (D / 8);
-      const int64_t off = qbase + (int64_t)(q0 + r) * x.q_stride_s + c * 8;
+    for (int i = 0; i < NA; ++i, off += ostep) {
+      const int r = r0 + i * rstep;
       qv[i] = make_uint4(0, 0, 0, 0);
       if (q0 + r < a.Sq) {
         if (x.q_dtype == TQ_BF16) qv[i] = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(x.q) + off);
