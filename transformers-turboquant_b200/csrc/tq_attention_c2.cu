@@ -611,18 +611,23 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
       }
       if (p < kBN) rn[2] = (p < left) ? a.val_vn[kv_base + k0 + p] : 0;
     };
-    int kkey[NIK], kgp[NIK], vkey[NIV], vgp[NIV];
+    // Per-thread constants of the decode, as byte offsets ready for use: where an item's packed indices and sign
+    // bits sit in the staging slot, where its decoded chunks go in the operand stage, which norm row it scales by
+    int kkey[NIK], ksrc[NIK], ksgn[NIK], kdst[NIK], vkey[NIV], vsrc[NIV], vdst[NIV];
 #pragma unroll
     for (int i = 0; i < NIK; ++i) {
-      const int e = i * kProducers + p;
-      kkey[i] = (e % 8) + 8 * (e / (8 * GPK));
-      kgp[i] = (e / 8) % GPK;
+      const int e = i * kProducers + p, key = (e % 8) + 8 * (e / (8 * GPK)), gp = (e / 8) % GPK;
+      kkey[i] = key;
+      ksrc[i] = key * (G * KB) + gp * 2 * KB;
+      ksgn[i] = (int)L::kIdxK + key * G + gp * 2;
+      kdst[i] = (key / 8) * (int)L::kSboK + (key % 8) * 16 + 2 * gp * 128;
     }
 #pragma unroll
     for (int i = 0; i < NIV; ++i) {
-      const int e = i * kProducers + p;
-      vkey[i] = (e % 8) + 8 * (e / (8 * GPV));
-      vgp[i] = (e / 8) % GPV;
+      const int e = i * kProducers + p, key = (e % 8) + 8 * (e / (8 * GPV)), gp = (e / 8) % GPV;
+      vkey[i] = key;
+      vsrc[i] = (int)(L::kIdxK + L::kSgn) + key * VROW + gp * 2 * VB;
+      vdst[i] = (key / 8) * (int)L::kLboV + (key % 8) * 16 + 2 * gp * (int)L::kSboV;
     }
     if (n_tiles > 0) {
       prefetch(0);
@@ -662,7 +667,7 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
 #pragma unroll
         for (int i = 0; i < NIK; ++i) {
           if (i * kProducers + p < kHalfN * GPK) {
-            const uint16_t* sk = reinterpret_cast<const uint16_t*>(pk + kkey[i] * (G * KB) + kgp[i] * 2 * KB);
+            const uint16_t* sk = reinterpret_cast<const uint16_t*>(pk + ksrc[i]);
             uint64_t w = 0;
             if constexpr (KB == 2) {
               w = *reinterpret_cast<const uint32_t*>(sk);  // 4-byte aligned: rows are 32 bytes, items 4
@@ -672,7 +677,7 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
             }
             gw[i][0] = (uint32_t)w & ((1u << (8 * KB)) - 1);
             gw[i][1] = (uint32_t)(w >> (8 * KB));
-            sb[i] = 0xffffu ^ (uint32_t)*reinterpret_cast<const uint16_t*>(pk + L::kIdxK + kkey[i] * G + kgp[i] * 2);
+            sb[i] = 0xffffu ^ (uint32_t)*reinterpret_cast<const uint16_t*>(pk + ksgn[i]);
             rr[i] = rho_s[ps][kkey[i]];
             nk2[i] = nk_s[ps][kkey[i]];
           }
@@ -680,7 +685,7 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
 #pragma unroll
         for (int i = 0; i < NIK; ++i) {
           if (i * kProducers + p < kHalfN * GPK) {
-            uint8_t* kd = Kd + (kkey[i] / 8) * L::kSboK + (kkey[i] % 8) * 16;
+            uint8_t* kd = Kd + kdst[i];
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
               uint32_t kq[4], sq[4];
@@ -694,9 +699,8 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
                 const uint32_t x = (half == 0 && q == 0) ? (sb[i] & 3u) : (sb[i] >> (8 * half + 2 * q));
                 sq[q] = rr[i] ^ ((x * 0x40008000u) & 0x80008000u);
               }
-              const int g = 2 * kgp[i] + half;
-              *reinterpret_cast<uint4*>(kd + g * 128) = make_uint4(kq[0], kq[1], kq[2], kq[3]);
-              *reinterpret_cast<uint4*>(kd + (G + g) * 128) = make_uint4(sq[0], sq[1], sq[2], sq[3]);
+              *reinterpret_cast<uint4*>(kd + half * 128) = make_uint4(kq[0], kq[1], kq[2], kq[3]);
+              *reinterpret_cast<uint4*>(kd + (G + half) * 128) = make_uint4(sq[0], sq[1], sq[2], sq[3]);
             }
           }
         }
@@ -715,8 +719,7 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
 #pragma unroll
         for (int i = 0; i < NIV; ++i) {
           if (i * kProducers + p < kBN * GPV) {
-            const uint16_t* sv =
-                reinterpret_cast<const uint16_t*>(pk + L::kIdxK + L::kSgn + vkey[i] * VROW + vgp[i] * 2 * VB);
+            const uint16_t* sv = reinterpret_cast<const uint16_t*>(pk + vsrc[i]);
             uint64_t w = 0;
             if constexpr (VB == 2) {
               w = *reinterpret_cast<const uint32_t*>(sv);
@@ -734,7 +737,7 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
 #pragma unroll
         for (int i = 0; i < NIV; ++i) {
           if (i * kProducers + p < kBN * GPV) {
-            uint8_t* vd = Vd + (vkey[i] / 8) * L::kLboV + (vkey[i] % 8) * 16;
+            uint8_t* vd = Vd + vdst[i];
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
               uint32_t vq[4];
@@ -743,7 +746,7 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
               for (int q = 0; q < 4; ++q) {
                 vq[q] = tc::mul_f16x2(vq[q], nv2[i]);
               }
-              *reinterpret_cast<uint4*>(vd + (2 * vgp[i] + half) * L::kSboV) = make_uint4(vq[0], vq[1], vq[2], vq[3]);
+              *reinterpret_cast<uint4*>(vd + half * L::kSboV) = make_uint4(vq[0], vq[1], vq[2], vq[3]);
             }
           }
         }
