@@ -27,7 +27,7 @@
 //   leader p_full[b] (16)            : P[b] written over S[b] (so S[b] has been read) by all softmax warps
 //   both   k_empty[s], v_empty[s]    : the score / PV MMA of tile j has drained
 //   both   s_full[b], pv_done[b]     : S[b] holds tile j's scores / O += P V_hat of tile j finished
-//   local  pk_full[2] (256), xch[4] (64)
+//   local  pk_full[2] (8), xch[4] (64)
 //   leader qp_full (32): raw query tile and constant operand staged;  both qp_done: Q_cat accumulated
 //   leader q_full (16) : 1st phase Q_cat packed into tensor memory, 2nd phase output tile + Pi_v staged
 //   both   e_done      : back-rotated output tile accumulated
@@ -266,7 +266,7 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
       uint32_t count = 1;                                     // commit / bulk-copy / single-thread barriers
       if (i < 2 * kStages) count = kProducerArrivals;         // k_full, v_full
       else if (r == 6 || r == 7 || r == 14) count = kSoftmaxArrivals;  // p_full, q_full
-      else if (r == 8 || r == 9) count = kProducers;          // pk_full
+      else if (r == 8 || r == 9) count = kProducers / 32;     // pk_full: one arrival per producer warp
       else if (r >= 10 && r <= 13) count = 32 * (kSoftmax / kBM);      // xch
       else if (r == 15) count = kSoftmaxArrivals + 1;         // qp_full: + the peer's constant operand
       tc::mbar_init(bar0 + 8u * i, count);
@@ -652,7 +652,8 @@ attention_c2_kernel(const AttnArgs a, const PairArgs x, const int pair_heads) {
         rho_s[ps][p] = (rn[1] & 0xffffu) * 0x10001u;
       }
       if (p < kBN) nv_s[ps][p] = (rn[2] & 0xffffu) * 0x10001u;
-      tc::mbar_arrive(pk_full(ps));
+      __syncwarp();  // the warp's staged bytes are ordered before lane 0's arrival (one barrier update per warp, not 32)
+      if (lane == 0) tc::mbar_arrive(pk_full(ps));
       if (!(ok = tc::mbar_wait_or_abort(pk_full(ps), (j >> 1) & 1, abort_flag))) break;
       tr.mark(1, j);
       if (j + 1 < n_tiles) prefetch((j + 1) * kBN);
