@@ -12,10 +12,9 @@ class CompressedCacheMixin:
 
     def _attend_cached(self, q, k, v, past_key_values, attention_mask):
         """Generation with a persistent compressed cache (no counterpart in the reference, whose adapters run
-        with `use_cache = False`).  The HF cache object only keeps count of the positions (it is fed
-        one channel of each key and value, so that `cache_position` and the rotary or learned positions
-        advance as usual) and tells one
-        generation from the next: a cache object this layer has not seen starts a new sequence."""
+        with `use_cache = False`).  The HF cache object only keeps count of the positions (it is fed one channel
+        of each key and value, so that `cache_position` and the rotary or learned positions advance as usual)
+        and tells one generation from the next: a cache object this layer has not seen starts a new sequence."""
         import weakref
 
         from ..kv_cache import CompressedKVCache
